@@ -1,0 +1,115 @@
+/*
+ * b200fp8 — C ABI of the B200 (sm_100a) FP8 rowwise-scaled GEMM library.
+ *
+ *   Y[M,N] = bf16( (X_e4m3[M,K] · W_e4m3[N,K]^T) ⊙ x_scale[M] ⊗ w_scale[N]  (+ bias[N]) )     fp32 accumulation
+ *
+ * This is the boundary a TritonBench `fp8_gemm_rowwise` backend binds.  In the reference the
+ * same boundary is the call from a backend closure into FBGEMM:
+ *   tritonbench/operators/fp8_gemm_rowwise/operator.py:187-199  (`_triton`  -> matmul_fp8_row)
+ *   tritonbench/operators/fp8_gemm_rowwise/operator.py:201-217  (`_cutlass_or_ck` -> torch.ops.fbgemm.f8f8bf16_rowwise)
+ *   tritonbench/operators/fp8_gemm_rowwise/operator.py:219-235  (`_cublas` -> f8f8bf16_cublas + scale_fp8_row)
+ *
+ * Rules of the ABI
+ *   - plain pointers and sizes only; no C++ or torch types cross it;
+ *   - every function returns a b200fp8_status (0 = OK) and never exits or throws;
+ *   - the device-pointer entry points allocate nothing, never synchronise and enqueue all work
+ *     on the stream they are given, so a call can be captured in a CUDA graph (the reference
+ *     times this operator by graph replay: operator.py:156, components/do_bench/run.py:190-199);
+ *   - the caller owns every buffer, including the workspace.
+ */
+#ifndef B200FP8_H_
+#define B200FP8_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200FP8_ABI_VERSION 1
+
+typedef enum b200fp8_status {
+  B200FP8_OK = 0,
+  B200FP8_BAD_ARG = 1,               /* null pointer, non-positive size, leading dimension < row length */
+  B200FP8_UNSUPPORTED_ARCH = 2,      /* device is not compute capability 10.x */
+  B200FP8_UNSUPPORTED_ALIGNMENT = 3, /* the forced variant needs 16-byte aligned rows / pointers */
+  B200FP8_WORKSPACE_TOO_SMALL = 4,
+  B200FP8_LAUNCH_FAILED = 5,         /* a CUDA runtime / driver call failed; see b200fp8_last_cuda_error */
+  B200FP8_DEVICE_TIMEOUT = 6,        /* a bounded wait inside a kernel ran out (read by b200fp8_query_status) */
+  B200FP8_TOO_LARGE = 7              /* size beyond a stated maximum of the entry point */
+} b200fp8_status;
+
+/* `flags` bits 0-3: kernel variant.  0 lets the library choose from (M, N, K). */
+#define B200FP8_VARIANT_AUTO 0u
+#define B200FP8_VARIANT_TC_1CTA 1u   /* tcgen05 128x256x128 tiles, one CTA per tile                       */
+#define B200FP8_VARIANT_TC_2CTA 2u   /* tcgen05 256x256x128 tiles, cta_group::2 CTA pair per tile         */
+#define B200FP8_VARIANT_SKINNY 3u    /* M <= 128: swap-AB tcgen05 stream-K, W streamed once from HBM      */
+#define B200FP8_VARIANT_SIMT 4u      /* CUDA-core kernel, any alignment; slow, used as an on-GPU cross-check */
+#define B200FP8_VARIANT_MASK 0xFu
+#define B200FP8_FLAG_NO_TMA_STORE 0x10u /* tcgen05 variants: write Y with plain stores instead of TMA        */
+
+/* Size of the bytes at the start of every workspace that hold the device status word. */
+#define B200FP8_WORKSPACE_HEADER_BYTES 256u
+
+int b200fp8_abi_version(void);
+
+const char* b200fp8_status_string(int status);
+
+/* Last CUDA error code (cudaError_t / CUresult value) seen by this thread inside the library. */
+int b200fp8_last_cuda_error(void);
+
+/*
+ * Workspace a call with these sizes and flags needs, in bytes (always >= the header).
+ * The workspace must be zero when first used (b200fp8_workspace_init); the library leaves
+ * it zero after every call that completes, so one initialisation serves any number of calls.
+ * Replaces: the output/temporary allocation FBGEMM's wrappers do per call (operator.py:187-235).
+ */
+size_t b200fp8_workspace_bytes(int64_t M, int64_t N, int64_t K, uint32_t flags);
+
+/* Zero a workspace on `cuda_stream` (cudaMemsetAsync; capturable). */
+int b200fp8_workspace_init(void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/*
+ * The GEMM.  All pointers are device pointers on the current device.
+ *   xq [M,K] e4m3, row pitch ldx bytes;  wq [N,K] e4m3, row pitch ldw bytes (both K contiguous)
+ *   x_scale [M], w_scale [N] fp32;  bias_bf16 [N] or NULL;  y_bf16 [M,N] bf16, row pitch ldy elements.
+ * Replaces: the three backend calls cited at the top of this file.
+ */
+int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
+                         const void* bias_bf16, void* y_bf16, int64_t M, int64_t N, int64_t K, int64_t ldx,
+                         int64_t ldw, int64_t ldy, void* workspace, size_t workspace_bytes, uint32_t flags,
+                         void* cuda_stream);
+
+/*
+ * Read the device status word of a workspace.  Call after the stream has been synchronised.
+ * Returns B200FP8_OK or B200FP8_DEVICE_TIMEOUT; *device_status receives the raw word
+ * (code << 24 | site).  Replaces: the reference's exit-on-error helper macros
+ * (tritonbench/operators/mixed_gemm/kernels/helper.h:40-64) with a status code.
+ */
+int b200fp8_query_status(const void* workspace, uint32_t* device_status);
+
+/*
+ * Human-readable plan for a problem size: variant, tile, grid, pipeline depth, workspace.
+ * Writes a NUL-terminated string of at most n-1 characters.
+ * Replaces: the backend knobs the reference passes to FBGEMM (operator.py:187-199).
+ */
+int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char* buf, size_t n);
+
+/*
+ * Host-buffer form, the call a host program without its own device memory makes:
+ * inputs and output live in host memory (pinned for full PCIe speed), device staging
+ * buffers belong to the context.  One call = copy in, GEMM, copy out, synchronise.
+ * Replaces: `input_cast(.to(device))` + backend call + result read in
+ * tritonbench/utils/triton_op.py:846-850,1221-1232.
+ */
+typedef struct b200fp8_host_ctx b200fp8_host_ctx;
+int b200fp8_host_ctx_create(int64_t M, int64_t N, int64_t K, uint32_t flags, b200fp8_host_ctx** out);
+int b200fp8_host_ctx_destroy(b200fp8_host_ctx* ctx);
+int b200fp8_gemm_rowwise_host(b200fp8_host_ctx* ctx, const void* xq, const void* wq, const float* x_scale,
+                              const float* w_scale, const void* bias_bf16, void* y_bf16);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200FP8_H_ */

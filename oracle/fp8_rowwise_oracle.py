@@ -1,0 +1,135 @@
+"""CPU oracle for the FP8 rowwise-scaled GEMM path.  TEST INFRASTRUCTURE ONLY.
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline / reference legs may import this
+module, and only as the checker or the timed CPU baseline.  Nothing under tritonbench_b200/ uses it.
+
+PARITY UNPINNED at the kernel boundary: the arithmetic of the reference's backends lives in the
+third-party package fbgemm_gpu (git submodule submodules/FBGEMM of the reference, .gitmodules:1-3,
+an empty directory in the mounted tree with no recorded commit; not installed), and the reference's
+own tests skip this operator wholesale (test/test_gpu/skip_tests_h100_pytorch.yaml:17-18), so there
+are no golden vectors for the GEMM to pin against.  What is pinned: the row quantiser below is checked
+against the reference's own `fp8_row_quantize` (imported from the reference tree by
+tests/golden/make_golden.py, outputs committed as fixtures), and the e4m3 decode table against
+torch.float8_e4m3fn for all 256 byte values.
+
+What this restates:
+  * `row_quantize_reference`  follows tritonbench/operators/fp8_gemm_rowwise/operator.py:130-145
+  * `row_quantize`            the benchmark recipe: scale = max(rowabsmax, 1e-12) / 448 in fp32
+  * `gemm_rowwise`            the fp32 dequantise-then-matmul torch form the operator keeps as its
+                              (commented) torch baseline, operator.py:237-246, with the scales applied
+                              to the operands in fp32 before the product, and the stock shims' bias
+                              add (operator.py:207-213) done in fp32 before the single bf16 rounding
+  * `flops`, `gbytes`         operator.py:248-271
+"""
+import math
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+E4M3_MAX = 448.0
+EPS = 1e-12
+
+
+def e4m3_decode_table() -> np.ndarray:
+    """float32 value of each of the 256 e4m3fn byte patterns, from the format definition:
+    1 sign, 4 exponent (bias 7), 3 mantissa bits; no infinities; S.1111.111 is NaN."""
+    out = np.zeros(256, dtype=np.float32)
+    for b in range(256):
+        sign = -1.0 if b & 0x80 else 1.0
+        e = (b >> 3) & 0xF
+        m = b & 0x7
+        if e == 0xF and m == 0x7:
+            v = math.nan
+        elif e == 0:
+            v = sign * (m / 8.0) * 2.0 ** (-6)
+        else:
+            v = sign * (1.0 + m / 8.0) * 2.0 ** (e - 7)
+        out[b] = v
+    return out
+
+
+_TABLE = None
+
+
+def decode_e4m3(q: torch.Tensor) -> torch.Tensor:
+    """e4m3 bytes (float8_e4m3fn or uint8 tensor) -> float32 through the table above."""
+    global _TABLE
+    if _TABLE is None:
+        _TABLE = torch.from_numpy(e4m3_decode_table())
+    idx = q.view(torch.uint8).to(torch.int64)
+    return _TABLE[idx]
+
+
+def row_quantize_reference(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """operator.py:136-145 — arithmetic in x's own dtype (bf16 in the reference's generator),
+    multiplier 448 / clamp(rowmax, 1e-12), fp16 inputs clamp the multiplier to 65504, clamp to
+    +-448, cast to e4m3 (round to nearest even), return the reciprocal multiplier as fp32."""
+    row_max = torch.max(torch.abs(x), dim=1).values
+    scale = E4M3_MAX / torch.clamp(row_max, EPS)
+    if x.dtype is torch.float16:
+        scale = torch.clamp(scale, max=torch.finfo(torch.float16).max)
+    xq = torch.clamp(x * scale[:, None], min=-E4M3_MAX, max=E4M3_MAX).to(torch.float8_e4m3fn)
+    return xq, scale.reciprocal().to(torch.float32)
+
+
+def row_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Benchmark recipe: fp32 input, scale = max(rowabsmax, 1e-12) / 448 (fp32), q = e4m3(clamp(x / scale))."""
+    x = x.to(torch.float32)
+    scale = torch.clamp(x.abs().amax(dim=1), min=EPS) / E4M3_MAX
+    xq = torch.clamp(x / scale[:, None], min=-E4M3_MAX, max=E4M3_MAX).to(torch.float8_e4m3fn)
+    return xq, scale
+
+
+def gemm_rowwise(
+    xq: torch.Tensor,
+    wq: torch.Tensor,
+    x_scale: torch.Tensor,
+    w_scale: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    keep_fp32: bool = False,
+) -> torch.Tensor:
+    """Y = bf16((float(xq) * x_scale[:, None]) @ (float(wq) * w_scale[:, None]).T (+ bias)) on CPU in fp32."""
+    x = decode_e4m3(xq.cpu()) * x_scale.cpu().to(torch.float32)[:, None]
+    w = decode_e4m3(wq.cpu()) * w_scale.cpu().to(torch.float32)[:, None]
+    y = x @ w.T
+    if bias is not None:
+        y = y + bias.cpu().to(torch.float32)[None, :]
+    return y if keep_fp32 else y.to(torch.bfloat16)
+
+
+def bf16_ulp(v: torch.Tensor) -> torch.Tensor:
+    """Spacing of bf16 numbers at |v|: 2^(floor(log2|v|) - 7); the smallest normal's ulp below that."""
+    a = v.abs().to(torch.float32).clamp(min=2.0 ** -126)
+    return torch.exp2(torch.floor(torch.log2(a)) - 7.0)
+
+
+def tolerance(ref_fp32: torch.Tensor) -> torch.Tensor:
+    """Per-element bound: 1 bf16 ulp of |ref| + 1e-2 * RMS(ref)."""
+    rms = ref_fp32.to(torch.float64).pow(2).mean().sqrt().to(torch.float32)
+    return bf16_ulp(ref_fp32) + 1e-2 * rms
+
+
+def compare(out_bf16: torch.Tensor, ref_bf16: torch.Tensor) -> dict:
+    """max |out - ref| against the tolerance, everything as float32 on CPU."""
+    out = out_bf16.detach().cpu().to(torch.float32)
+    ref = ref_bf16.detach().cpu().to(torch.float32)
+    tol = tolerance(ref)
+    diff = (out - ref).abs()
+    ratio = diff / tol
+    return {
+        "max_abs_diff": float(diff.max()),
+        "max_ratio": float(ratio.max()),
+        "mismatched": int((diff > 0).sum()),
+        "ok": bool((diff <= tol).all()) and bool(torch.isfinite(out).all()),
+    }
+
+
+def flops(m: int, n: int, k: int, bias: bool = False) -> int:
+    """operator.py:248-259"""
+    return 2 * m * n * k + (2 * m * n if bias else 0)
+
+
+def gbytes(m: int, n: int, k: int) -> float:
+    """operator.py:261-271: |a| + |b| + |c| in GB"""
+    return (m * k + n * k + 2 * m * n) / 1e9

@@ -1,0 +1,421 @@
+// C ABI of the library (declared in include/b200fp8.h): argument checks, the choice of kernel
+// variant, TMA descriptor encoding, workspace layout, and the host-buffer context.
+#include <cudaTypedefs.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+#include <new>
+
+#include "../../include/b200fp8.h"
+#include "kernels.h"
+
+namespace {
+
+using namespace b200fp8;
+
+thread_local int g_last_cuda_error = 0;
+
+struct DeviceInfo {
+  bool known = false;
+  int cc_major = 0;
+  int sm_count = 0;
+  int max_pair_clusters = 0;
+};
+
+std::mutex g_mutex;
+DeviceInfo g_devices[64];
+PFN_cuTensorMapEncodeTiled g_encode = nullptr;
+
+int note_cuda(cudaError_t e) {
+  g_last_cuda_error = static_cast<int>(e);
+  return e == cudaSuccess ? B200FP8_OK : B200FP8_LAUNCH_FAILED;
+}
+
+int device_info(DeviceInfo* out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return note_cuda(e);
+  if (dev < 0 || dev >= 64) return B200FP8_BAD_ARG;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceInfo& d = g_devices[dev];
+  if (!d.known) {
+    e = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return note_cuda(e);
+    e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return note_cuda(e);
+    d.max_pair_clusters = d.sm_count / 2;
+    d.known = true;
+  }
+  if (g_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess) return note_cuda(e);
+    if (qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+      g_last_cuda_error = static_cast<int>(cudaErrorSymbolNotFound);
+      return B200FP8_LAUNCH_FAILED;
+    }
+    g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(fn);
+  }
+  *out = d;
+  return B200FP8_OK;
+}
+
+// 2-D row-major tensor [rows, cols] with row pitch `pitch_bytes`; box {box_cols, box_rows};
+// 128-byte swizzle (box_cols * elem_bytes must be 128); out-of-range elements read as zero.
+int encode_2d(CUtensorMap* tm, CUtensorMapDataType dtype, int elem_bytes, const void* ptr, uint64_t rows,
+              uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows) {
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {pitch_bytes};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  (void)elem_bytes;
+  const CUresult r = g_encode(tm, dtype, 2, const_cast<void*>(ptr), dims, strides, box, elem_strides,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = static_cast<int>(r);
+    return B200FP8_LAUNCH_FAILED;
+  }
+  return B200FP8_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct Plan {
+  uint32_t variant;
+  bool tma_store;
+  int num_ctas;      // tcgen05 variants
+  int group_m;
+  SkinnyPlan skinny;  // skinny variant
+  size_t workspace_bytes;
+};
+
+// The tcgen05 kernels read X and W through TMA: rows must start on 16-byte boundaries.
+bool tma_loadable(int64_t K, int64_t ldx, int64_t ldw, const void* xq, const void* wq) {
+  (void)K;
+  return ldx % 16 == 0 && ldw % 16 == 0 && aligned16(xq) && aligned16(wq);
+}
+
+int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma_ok, bool y_tma_ok,
+              const DeviceInfo& dev, Plan* out) {
+  Plan pl = {};
+  uint32_t v = flags & B200FP8_VARIANT_MASK;
+  if (v > B200FP8_VARIANT_SIMT) return B200FP8_BAD_ARG;
+  if (v == B200FP8_VARIANT_AUTO) {
+    if (!operands_tma_ok) {
+      v = B200FP8_VARIANT_SIMT;
+    } else if (M <= SkinnyGeometry::kMaxTokens) {
+      v = B200FP8_VARIANT_SKINNY;
+    } else {
+      // a CTA pair per 256x256 tile halves the shared-memory fill per flop; keep single CTAs when
+      // the pair tiles could not occupy the SMs anyway
+      const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+      v = pair_tiles >= dev.sm_count / 2 ? B200FP8_VARIANT_TC_2CTA : B200FP8_VARIANT_TC_1CTA;
+    }
+  } else if (v != B200FP8_VARIANT_SIMT && !operands_tma_ok) {
+    return B200FP8_UNSUPPORTED_ALIGNMENT;
+  }
+  if (v == B200FP8_VARIANT_SKINNY && M > SkinnyGeometry::kMaxTokens) return B200FP8_BAD_ARG;
+  if (v == B200FP8_VARIANT_SKINNY && (N + SkinnyGeometry::kRowsW - 1) / SkinnyGeometry::kRowsW > SkinnyGeometry::kMaxTiles) {
+    if ((flags & B200FP8_VARIANT_MASK) != B200FP8_VARIANT_AUTO) return B200FP8_TOO_LARGE;
+    v = B200FP8_VARIANT_TC_1CTA;  // wider than the counter region covers: use the large-M kernel
+  }
+  pl.variant = v;
+  pl.tma_store = y_tma_ok && (flags & B200FP8_FLAG_NO_TMA_STORE) == 0;
+  pl.group_m = 8;
+  pl.workspace_bytes = B200FP8_WORKSPACE_HEADER_BYTES;
+  if (v == B200FP8_VARIANT_TC_1CTA) {
+    const int64_t tiles = ((M + 127) / 128) * ((N + 255) / 256);
+    pl.num_ctas = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
+  } else if (v == B200FP8_VARIANT_TC_2CTA) {
+    const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    const int64_t clusters = tiles < dev.max_pair_clusters ? tiles : dev.max_pair_clusters;
+    pl.num_ctas = static_cast<int>(2 * clusters);
+  } else if (v == B200FP8_VARIANT_SKINNY) {
+    pl.skinny = make_skinny_plan(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), dev.sm_count);
+    pl.workspace_bytes += pl.skinny.counter_bytes;
+    pl.workspace_bytes = (pl.workspace_bytes + 255) & ~static_cast<size_t>(255);
+    pl.workspace_bytes += pl.skinny.partial_bytes;
+  }
+  *out = pl;
+  return B200FP8_OK;
+}
+
+int check_sizes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return B200FP8_BAD_ARG;
+  if (M > 0x7FFFFF00ll || N > 0x7FFFFF00ll || K > 0x7FFFFF00ll) return B200FP8_TOO_LARGE;
+  return B200FP8_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200fp8_abi_version(void) { return B200FP8_ABI_VERSION; }
+
+const char* b200fp8_status_string(int status) {
+  switch (status) {
+    case B200FP8_OK: return "ok";
+    case B200FP8_BAD_ARG: return "bad argument";
+    case B200FP8_UNSUPPORTED_ARCH: return "device is not compute capability 10.x (B200)";
+    case B200FP8_UNSUPPORTED_ALIGNMENT: return "operand rows are not 16-byte aligned for the requested variant";
+    case B200FP8_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case B200FP8_LAUNCH_FAILED: return "CUDA call failed";
+    case B200FP8_DEVICE_TIMEOUT: return "a bounded wait inside the kernel timed out";
+    case B200FP8_TOO_LARGE: return "size exceeds the supported maximum";
+    default: return "unknown status";
+  }
+}
+
+int b200fp8_last_cuda_error(void) { return g_last_cuda_error; }
+
+size_t b200fp8_workspace_bytes(int64_t M, int64_t N, int64_t K, uint32_t flags) {
+  if (check_sizes(M, N, K) != B200FP8_OK) return 0;
+  DeviceInfo dev;
+  if (device_info(&dev) != B200FP8_OK) {
+    // no usable device: size for the largest B200 configuration so that callers can still plan
+    dev.sm_count = 148;
+    dev.max_pair_clusters = 74;
+  }
+  Plan pl;
+  if (make_plan(M, N, K, flags, true, true, dev, &pl) != B200FP8_OK) return 0;
+  return pl.workspace_bytes;
+}
+
+int b200fp8_workspace_init(void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (workspace == nullptr || workspace_bytes < B200FP8_WORKSPACE_HEADER_BYTES) return B200FP8_BAD_ARG;
+  return note_cuda(cudaMemsetAsync(workspace, 0, workspace_bytes, static_cast<cudaStream_t>(cuda_stream)));
+}
+
+int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
+                         const void* bias_bf16, void* y_bf16, int64_t M, int64_t N, int64_t K, int64_t ldx,
+                         int64_t ldw, int64_t ldy, void* workspace, size_t workspace_bytes, uint32_t flags,
+                         void* cuda_stream) {
+  if (xq == nullptr || wq == nullptr || x_scale == nullptr || w_scale == nullptr || y_bf16 == nullptr ||
+      workspace == nullptr) {
+    return B200FP8_BAD_ARG;
+  }
+  int st = check_sizes(M, N, K);
+  if (st != B200FP8_OK) return st;
+  if (ldx < K || ldw < K || ldy < N) return B200FP8_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200FP8_BAD_ARG;
+
+  DeviceInfo dev;
+  st = device_info(&dev);
+  if (st != B200FP8_OK) return st;
+  if (dev.cc_major != 10) return B200FP8_UNSUPPORTED_ARCH;
+
+  const bool operands_ok = tma_loadable(K, ldx, ldw, xq, wq);
+  const bool y_ok = (ldy % 8 == 0) && aligned16(y_bf16);
+  Plan pl;
+  st = make_plan(M, N, K, flags, operands_ok, y_ok, dev, &pl);
+  if (st != B200FP8_OK) return st;
+  if (workspace_bytes < pl.workspace_bytes) return B200FP8_WORKSPACE_TOO_SMALL;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  uint32_t* status_word = static_cast<uint32_t*>(workspace);
+  const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(bias_bf16);
+  __nv_bfloat16* y = static_cast<__nv_bfloat16*>(y_bf16);
+
+  if (pl.variant == B200FP8_VARIANT_SIMT) {
+    SimtParams sp = {static_cast<const uint8_t*>(xq), static_cast<const uint8_t*>(wq), x_scale, w_scale, bias, y,
+                     static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), ldx, ldw, ldy};
+    return note_cuda(launch_gemm_simt(sp, stream));
+  }
+
+  if (pl.variant == B200FP8_VARIANT_SKINNY) {
+    CUtensorMap tm_w, tm_x;
+    st = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, N, K, ldw, SkinnyGeometry::kBlockK,
+                   SkinnyGeometry::kRowsW);
+    if (st != B200FP8_OK) return st;
+    st = encode_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, M, K, ldx, SkinnyGeometry::kBlockK,
+                   static_cast<uint32_t>(pl.skinny.tokens_pad));
+    if (st != B200FP8_OK) return st;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    size_t off = B200FP8_WORKSPACE_HEADER_BYTES;
+    SkinnyParams kp = {};
+    kp.x_scale = x_scale;
+    kp.w_scale = w_scale;
+    kp.bias = bias;
+    kp.y = y;
+    kp.M = static_cast<int>(M);
+    kp.N = static_cast<int>(N);
+    kp.K = static_cast<int>(K);
+    kp.ldy = ldy;
+    kp.counters = reinterpret_cast<uint32_t*>(ws + off);
+    off = (off + pl.skinny.counter_bytes + 255) & ~static_cast<size_t>(255);
+    kp.partials = reinterpret_cast<float*>(ws + off);
+    kp.status = status_word;
+    return note_cuda(launch_gemm_skinny(tm_w, tm_x, kp, pl.skinny, stream));
+  }
+
+  const int cta_group = pl.variant == B200FP8_VARIANT_TC_2CTA ? 2 : 1;
+  CUtensorMap tm_x, tm_w, tm_y;
+  memset(&tm_y, 0, sizeof(tm_y));
+  st = encode_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, M, K, ldx, TcGeometry::kBlockK, TcGeometry::kBlockM);
+  if (st != B200FP8_OK) return st;
+  st = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, N, K, ldw, TcGeometry::kBlockK,
+                 TcGeometry::kBlockN / cta_group);
+  if (st != B200FP8_OK) return st;
+  if (pl.tma_store) {
+    st = encode_2d(&tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, M, N, ldy * 2, TcGeometry::kStoreCols,
+                   TcGeometry::kStoreRows);
+    if (st != B200FP8_OK) return st;
+  }
+  TcParams tp = {};
+  tp.x_scale = x_scale;
+  tp.w_scale = w_scale;
+  tp.bias = bias;
+  tp.y = y;
+  tp.M = static_cast<int>(M);
+  tp.N = static_cast<int>(N);
+  tp.K = static_cast<int>(K);
+  tp.ldy = ldy;
+  tp.use_tma_store = pl.tma_store ? 1 : 0;
+  tp.group_m = pl.group_m;
+  tp.status = status_word;
+  if (cta_group == 2) return note_cuda(launch_gemm_tc<2>(tm_x, tm_w, tm_y, tp, pl.num_ctas, stream));
+  return note_cuda(launch_gemm_tc<1>(tm_x, tm_w, tm_y, tp, pl.num_ctas, stream));
+}
+
+int b200fp8_query_status(const void* workspace, uint32_t* device_status) {
+  if (workspace == nullptr) return B200FP8_BAD_ARG;
+  uint32_t word = 0;
+  const cudaError_t e = cudaMemcpy(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return note_cuda(e);
+  if (device_status != nullptr) *device_status = word;
+  return (word >> 24) == kDevTimeout ? B200FP8_DEVICE_TIMEOUT : B200FP8_OK;
+}
+
+int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char* buf, size_t n) {
+  if (buf == nullptr || n == 0) return B200FP8_BAD_ARG;
+  int st = check_sizes(M, N, K);
+  if (st != B200FP8_OK) return st;
+  DeviceInfo dev;
+  if (device_info(&dev) != B200FP8_OK) {
+    dev.sm_count = 148;
+    dev.max_pair_clusters = 74;
+  }
+  Plan pl;
+  st = make_plan(M, N, K, flags, true, true, dev, &pl);
+  if (st != B200FP8_OK) return st;
+  switch (pl.variant) {
+    case B200FP8_VARIANT_TC_1CTA:
+      snprintf(buf, n, "tc_1cta tile=128x256x128 stages=%d ctas=%d group_m=%d smem=%d workspace=%zu",
+               TcConfig<1>::kStages, pl.num_ctas, pl.group_m, TcConfig<1>::kSmemBytes, pl.workspace_bytes);
+      break;
+    case B200FP8_VARIANT_TC_2CTA:
+      snprintf(buf, n, "tc_2cta tile=256x256x128 stages=%d ctas=%d group_m=%d smem=%d workspace=%zu",
+               TcConfig<2>::kStages, pl.num_ctas, pl.group_m, TcConfig<2>::kSmemBytes, pl.workspace_bytes);
+      break;
+    case B200FP8_VARIANT_SKINNY:
+      snprintf(buf, n,
+               "skinny swap-AB stream-K tile=128(W rows)x%d(tokens)x128 stages=%d ctas=%d units_per_cta=%d "
+               "segs_per_cta=%d smem=%zu workspace=%zu",
+               pl.skinny.tokens_pad, pl.skinny.stages, pl.skinny.num_ctas, pl.skinny.units_per_cta,
+               pl.skinny.segs_per_cta, pl.skinny.smem_bytes, pl.workspace_bytes);
+      break;
+    default:
+      snprintf(buf, n, "simt tile=64x64x32 workspace=%zu", pl.workspace_bytes);
+      break;
+  }
+  return B200FP8_OK;
+}
+
+// ------------------------------------ host-buffer context ------------------------------------
+struct b200fp8_host_ctx {
+  int64_t M, N, K;
+  uint32_t flags;
+  cudaStream_t stream;
+  uint8_t* d_x;
+  uint8_t* d_w;
+  float* d_xs;
+  float* d_ws;
+  __nv_bfloat16* d_bias;
+  __nv_bfloat16* d_y;
+  void* d_workspace;
+  size_t workspace_bytes;
+  uint32_t* h_status;  // pinned
+};
+
+int b200fp8_host_ctx_destroy(b200fp8_host_ctx* c) {
+  if (c == nullptr) return B200FP8_OK;
+  if (c->stream) cudaStreamSynchronize(c->stream);
+  cudaFree(c->d_x);
+  cudaFree(c->d_w);
+  cudaFree(c->d_xs);
+  cudaFree(c->d_ws);
+  cudaFree(c->d_bias);
+  cudaFree(c->d_y);
+  cudaFree(c->d_workspace);
+  if (c->h_status) cudaFreeHost(c->h_status);
+  if (c->stream) cudaStreamDestroy(c->stream);
+  delete c;
+  return B200FP8_OK;
+}
+
+int b200fp8_host_ctx_create(int64_t M, int64_t N, int64_t K, uint32_t flags, b200fp8_host_ctx** out) {
+  if (out == nullptr) return B200FP8_BAD_ARG;
+  *out = nullptr;
+  int st = check_sizes(M, N, K);
+  if (st != B200FP8_OK) return st;
+  DeviceInfo dev;
+  st = device_info(&dev);
+  if (st != B200FP8_OK) return st;
+  if (dev.cc_major != 10) return B200FP8_UNSUPPORTED_ARCH;
+  b200fp8_host_ctx* c = new (std::nothrow) b200fp8_host_ctx();
+  if (c == nullptr) return B200FP8_BAD_ARG;
+  memset(c, 0, sizeof(*c));
+  c->M = M;
+  c->N = N;
+  c->K = K;
+  c->flags = flags;
+  c->workspace_bytes = b200fp8_workspace_bytes(M, N, K, flags);
+  cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_x, static_cast<size_t>(M) * K);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_w, static_cast<size_t>(N) * K);
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_xs, static_cast<size_t>(M) * sizeof(float));
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_ws, static_cast<size_t>(N) * sizeof(float));
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_bias, static_cast<size_t>(N) * sizeof(__nv_bfloat16));
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_y, static_cast<size_t>(M) * N * sizeof(__nv_bfloat16));
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_workspace, c->workspace_bytes);
+  if (e == cudaSuccess) e = cudaMallocHost(&c->h_status, sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemsetAsync(c->d_workspace, 0, c->workspace_bytes, c->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+  if (e != cudaSuccess || c->workspace_bytes == 0) {
+    b200fp8_host_ctx_destroy(c);
+    return e != cudaSuccess ? note_cuda(e) : B200FP8_BAD_ARG;
+  }
+  *out = c;
+  return B200FP8_OK;
+}
+
+int b200fp8_gemm_rowwise_host(b200fp8_host_ctx* c, const void* xq, const void* wq, const float* x_scale,
+                              const float* w_scale, const void* bias_bf16, void* y_bf16) {
+  if (c == nullptr || xq == nullptr || wq == nullptr || x_scale == nullptr || w_scale == nullptr ||
+      y_bf16 == nullptr) {
+    return B200FP8_BAD_ARG;
+  }
+  const size_t M = static_cast<size_t>(c->M), N = static_cast<size_t>(c->N), K = static_cast<size_t>(c->K);
+  cudaError_t e = cudaMemcpyAsync(c->d_x, xq, M * K, cudaMemcpyHostToDevice, c->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(c->d_w, wq, N * K, cudaMemcpyHostToDevice, c->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(c->d_xs, x_scale, M * sizeof(float), cudaMemcpyHostToDevice, c->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(c->d_ws, w_scale, N * sizeof(float), cudaMemcpyHostToDevice, c->stream);
+  if (e == cudaSuccess && bias_bf16 != nullptr) {
+    e = cudaMemcpyAsync(c->d_bias, bias_bf16, N * sizeof(__nv_bfloat16), cudaMemcpyHostToDevice, c->stream);
+  }
+  if (e != cudaSuccess) return note_cuda(e);
+  const int st = b200fp8_gemm_rowwise(c->d_x, c->d_w, c->d_xs, c->d_ws, bias_bf16 != nullptr ? c->d_bias : nullptr,
+                                      c->d_y, c->M, c->N, c->K, c->K, c->K, c->N, c->d_workspace,
+                                      c->workspace_bytes, c->flags, c->stream);
+  if (st != B200FP8_OK) return st;
+  e = cudaMemcpyAsync(y_bf16, c->d_y, M * N * sizeof(__nv_bfloat16), cudaMemcpyDeviceToHost, c->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(c->h_status, c->d_workspace, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+  if (e != cudaSuccess) return note_cuda(e);
+  return (*c->h_status >> 24) == kDevTimeout ? B200FP8_DEVICE_TIMEOUT : B200FP8_OK;
+}
+
+}  // extern "C"

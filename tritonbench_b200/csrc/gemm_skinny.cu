@@ -1,0 +1,312 @@
+// Skinny-M (decode, M <= 128) FP8 rowwise GEMM for sm_100a.  The work is bound by streaming
+// W[N,K] from HBM exactly once, so the kernel is organised around that stream:
+//
+//   * swap-AB: a tile is 128 rows of W (the MMA M side, one TMEM lane each) against all tokens
+//     (MMA N = M rounded up to 16), so the tensor core consumes W at the rate TMA delivers it and
+//     CUDA cores never touch the operands;
+//   * stream-K: the (tile, k-block) space is cut into equal runs of consecutive units, one run per
+//     CTA, so every SM streams the same number of W bytes whatever N/128 is relative to the SM count;
+//   * a tile whose K range is split over several CTAs is finished by whichever CTA arrives last:
+//     each writes its fp32 partial sums to a slot in the workspace, bumps a per-(tile, lane quarter)
+//     counter, and the last one adds the slots in ascending CTA order (a fixed order, so the result
+//     does not depend on who is last), applies the scales and writes bf16.  No CTA waits for another.
+//
+// Warp roles are those of the large-M kernel: warp 0 TMA producer, warp 1 TMEM owner + MMA issuer,
+// warps 2-5 epilogue.  All mbarrier waits are bounded.
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace b200fp8 {
+
+SkinnyPlan make_skinny_plan(int M, int N, int K, int sm_count) {
+  using G = SkinnyGeometry;
+  SkinnyPlan pl = {};
+  pl.tokens_pad = ((M + 15) / 16) * 16;
+  if (pl.tokens_pad < 16) pl.tokens_pad = 16;
+  const int stage_bytes = G::kBytesA + pl.tokens_pad * G::kBlockK;
+  pl.stages = (G::kSmemBudget - G::kBarBytes - 1024) / stage_bytes;
+  if (pl.stages > G::kMaxStages) pl.stages = G::kMaxStages;
+  pl.tiles = (N + G::kRowsW - 1) / G::kRowsW;
+  pl.kblocks = (K + G::kBlockK - 1) / G::kBlockK;
+  const long long total = static_cast<long long>(pl.tiles) * pl.kblocks;
+  long long per = (total + sm_count - 1) / sm_count;
+  const long long floor_units = pl.kblocks < 4 ? pl.kblocks : 4;  // do not cut K finer than 512 bytes
+  if (per < floor_units) per = floor_units;
+  pl.units_per_cta = static_cast<int>(per);
+  pl.num_ctas = static_cast<int>((total + per - 1) / per);
+  pl.segs_per_cta = (pl.units_per_cta + pl.kblocks - 1) / pl.kblocks + 1;
+  pl.smem_bytes = static_cast<size_t>(pl.stages) * stage_bytes + G::kBarBytes + 1024;
+  pl.partial_bytes =
+      static_cast<size_t>(pl.num_ctas) * pl.segs_per_cta * pl.tokens_pad * G::kRowsW * sizeof(float);
+  pl.counter_bytes = G::kCounterRegionBytes;
+  return pl;
+}
+
+namespace {
+
+enum WaitSite : uint32_t {
+  kSiteProducerEmpty = 0x201,
+  kSiteMmaTmemEmpty = 0x202,
+  kSiteMmaFull = 0x203,
+  kSiteEpiTmemFull = 0x204,
+};
+
+struct Segment {
+  int tile;
+  int kb0;
+  int kb1;
+};
+
+// The run of units [u, u_end) starts with a segment of tile u / kblocks.
+__device__ __forceinline__ Segment first_segment(long long u, long long u_end, int kblocks) {
+  Segment s;
+  s.tile = static_cast<int>(u / kblocks);
+  s.kb0 = static_cast<int>(u - static_cast<long long>(s.tile) * kblocks);
+  const long long left = u_end - u;
+  s.kb1 = (s.kb0 + left < kblocks) ? static_cast<int>(s.kb0 + left) : kblocks;
+  return s;
+}
+
+__global__ void __launch_bounds__(SkinnyGeometry::kThreads, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                   const SkinnyParams p, const int tokens_pad, const int stages, const int kblocks,
+                   const int units_per_cta, const int segs_per_cta, const long long total_units) {
+  using G = SkinnyGeometry;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw_addr);
+
+  const int bytes_b = tokens_pad * G::kBlockK;
+  const uint32_t smem_a = base;
+  const uint32_t smem_b = smem_a + stages * G::kBytesA;
+  const uint32_t bars = smem_b + stages * bytes_b;
+  const uint32_t bar_full = bars;                       // [stages]
+  const uint32_t bar_empty = bars + 8 * stages;         // [stages]
+  const uint32_t bar_tmem_full = bars + 16 * stages;    // [2]
+  const uint32_t bar_tmem_empty = bar_tmem_full + 16;   // [2]
+  const uint32_t tmem_slot = bar_tmem_empty + 16;
+  uint8_t* tail_ptr = base_ptr + (tmem_slot - base);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(tail_ptr);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tail_ptr + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const long long u_begin = static_cast<long long>(blockIdx.x) * units_per_cta;
+  const long long u_stop = u_begin + units_per_cta < total_units ? u_begin + units_per_cta : total_units;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tmem_full + 8 * b, 1);
+      mbar_init(bar_tmem_empty + 8 * b, 4);
+    }
+    *abort_flag = 0u;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tm_w);
+    prefetch_tensormap(&tm_x);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(tmem_slot, 256);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      const uint32_t tx_bytes = static_cast<uint32_t>(G::kBytesA + bytes_b);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      long long u = u_begin;
+      while (u < u_stop && ok) {
+        const Segment sg = first_segment(u, u_stop, kblocks);
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+          ok = mbar_wait<false>(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty);
+          if (!ok) break;
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_arrive_expect_tx(full, tx_bytes);
+          tma_load_2d(smem_a + stage * G::kBytesA, &tm_w, full, kb * G::kBlockK, sg.tile * G::kRowsW);
+          tma_load_2d(smem_b + stage * bytes_b, &tm_x, full, kb * G::kBlockK, 0);
+          if (++stage == static_cast<uint32_t>(stages)) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        u += sg.kb1 - sg.kb0;
+      }
+      if (!ok) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------- MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc_e4m3(G::kRowsW, static_cast<uint32_t>(tokens_pad));
+      uint32_t stage = 0, phase = 0;
+      uint32_t seg = 0;
+      bool ok = true;
+      long long u = u_begin;
+      while (u < u_stop && ok) {
+        const Segment sg = first_segment(u, u_stop, kblocks);
+        const uint32_t buf = seg & 1u;
+        const uint32_t use = (seg >> 1) & 1u;
+        ok = mbar_wait<false>(bar_tmem_empty + 8 * buf, use ^ 1u, abort_flag, p.status, kSiteMmaTmemEmpty);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * G::kMaxTokens;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+          ok = mbar_wait<false>(bar_full + 8 * stage, phase, abort_flag, p.status, kSiteMmaFull);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint64_t a_desc = smem_desc_k_sw128(smem_a + stage * G::kBytesA);
+          const uint64_t b_desc = smem_desc_k_sw128(smem_b + stage * bytes_b);
+#pragma unroll
+          for (int k = 0; k < G::kBlockK / 32; ++k) {
+            tc_mma_f8<1>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(bar_empty + 8 * stage);
+          if (++stage == static_cast<uint32_t>(stages)) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit(bar_tmem_full + 8 * buf);
+        u += sg.kb1 - sg.kb0;
+        ++seg;
+      }
+    }
+  } else {
+    // ---------------------------------- epilogue ---------------------------------
+    const int quarter = warp & 3;
+    const int lane_row = quarter * 32 + lane;  // row of the 128-row W tile = TMEM lane
+    const long long first_tile_here = u_begin / kblocks;
+    uint32_t seg = 0;
+    bool ok = true;
+    long long u = u_begin;
+    while (u < u_stop && ok) {
+      const Segment sg = first_segment(u, u_stop, kblocks);
+      const uint32_t buf = seg & 1u;
+      const uint32_t use = (seg >> 1) & 1u;
+      const int n = sg.tile * G::kRowsW + lane_row;  // output column
+      const bool full_k = sg.kb0 == 0 && sg.kb1 == kblocks;
+      const bool n_ok = n < p.N;
+      const float ws = n_ok ? __ldg(p.w_scale + n) : 0.0f;
+      const float bias = (n_ok && p.bias != nullptr) ? __bfloat162float(p.bias[n]) : 0.0f;
+      float* slot = p.partials +
+                    (static_cast<size_t>(blockIdx.x) * segs_per_cta + (sg.tile - first_tile_here)) *
+                        (static_cast<size_t>(tokens_pad) * G::kRowsW);
+
+      ok = mbar_wait<false>(bar_tmem_full + 8 * buf, use, abort_flag, p.status, kSiteEpiTmemFull);
+      ok = __all_sync(0xffffffffu, ok) != 0;
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * G::kMaxTokens;
+
+      for (int c = 0; c < tokens_pad; c += 16) {
+        uint32_t acc[16];
+        tmem_ld_32x16(t_addr + c, acc);
+        tmem_ld_wait();
+        if (full_k) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = c + j;
+            if (m < p.M && n_ok) {
+              const float v = __uint_as_float(acc[j]) * (__ldg(p.x_scale + m) * ws) + bias;
+              p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16_rn(v);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = c + j;
+            if (m < p.M) slot[static_cast<size_t>(m) * G::kRowsW + lane_row] = __uint_as_float(acc[j]);
+          }
+        }
+      }
+      // accumulator read: hand the TMEM buffer back
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * buf);
+
+      if (!full_k) {
+        // publish this warp's part of the slot, then see whether every other part is already there
+        const long long tile_u0 = static_cast<long long>(sg.tile) * kblocks;
+        const int cta_first = static_cast<int>(tile_u0 / units_per_cta);
+        const int cta_last = static_cast<int>((tile_u0 + kblocks - 1) / units_per_cta);
+        const uint32_t parts = static_cast<uint32_t>(cta_last - cta_first + 1);
+        __threadfence();
+        __syncwarp();
+        uint32_t seen = 0;
+        if (lane == 0) seen = atomicAdd(p.counters + sg.tile * 4 + quarter, 1u);
+        seen = __shfl_sync(0xffffffffu, seen, 0);
+        if (seen == parts - 1u) {
+          __threadfence();
+          if (n_ok) {
+#pragma unroll 4
+            for (int m = 0; m < p.M; ++m) {
+              float sum = 0.0f;
+              for (int cta = cta_first; cta <= cta_last; ++cta) {
+                const long long their_first = static_cast<long long>(cta) * units_per_cta / kblocks;
+                const float* src = p.partials +
+                                   (static_cast<size_t>(cta) * segs_per_cta + (sg.tile - their_first)) *
+                                       (static_cast<size_t>(tokens_pad) * G::kRowsW) +
+                                   static_cast<size_t>(m) * G::kRowsW + lane_row;
+                sum += __ldcg(src);
+              }
+              const float v = sum * (__ldg(p.x_scale + m) * ws) + bias;
+              p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16_rn(v);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) p.counters[sg.tile * 4 + quarter] = 0u;  // leave the workspace zero
+        }
+      }
+      u += sg.kb1 - sg.kb0;
+      ++seg;
+    }
+  }
+
+  // ------------------------------------ common exit ------------------------------------
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) {
+    tmem_dealloc<1>(tmem_base, 256);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_skinny(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const SkinnyParams& p,
+                               const SkinnyPlan& plan, cudaStream_t stream) {
+  static size_t configured_bytes[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 64 && configured_bytes[dev] < plan.smem_bytes) {
+    err = cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               SkinnyGeometry::kSmemBudget);
+    if (err != cudaSuccess) return err;
+    configured_bytes[dev] = SkinnyGeometry::kSmemBudget;
+  }
+  const long long total = static_cast<long long>(plan.tiles) * plan.kblocks;
+  gemm_skinny_kernel<<<plan.num_ctas, SkinnyGeometry::kThreads, plan.smem_bytes, stream>>>(
+      tm_w, tm_x, p, plan.tokens_pad, plan.stages, plan.kblocks, plan.units_per_cta, plan.segs_per_cta, total);
+  return cudaGetLastError();
+}
+
+}  // namespace b200fp8

@@ -1,0 +1,115 @@
+// Internal launch interface between the C-ABI layer (api.cu) and the kernel files.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200fp8 {
+
+// Device status word (first word of every workspace): code << 24 | site of the wait that gave up.
+constexpr uint32_t kDevOk = 0u;
+constexpr uint32_t kDevTimeout = 1u;
+
+// --------------------------- large-M tcgen05 kernel (gemm_tc.cu) ---------------------------
+struct TcGeometry {
+  static constexpr int kBlockM = 128;    // rows of X per CTA (TMEM lanes)
+  static constexpr int kBlockN = 256;    // columns of Y per tile (MMA N)
+  static constexpr int kBlockK = 128;    // bytes (= e4m3 elements) of K per pipeline stage
+  static constexpr int kStoreCols = 64;  // bf16 columns per TMA-store box (128 bytes)
+  static constexpr int kStoreRows = 32;  // rows per TMA-store box (one epilogue warp)
+  static constexpr int kThreads = 192;   // warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue
+};
+
+template <int kCtaGroup>
+struct TcConfig : TcGeometry {
+  static constexpr int kRowsW = kBlockN / kCtaGroup;                  // W rows each CTA loads per stage
+  static constexpr int kBytesA = kBlockM * kBlockK;                   // 16 KiB
+  static constexpr int kBytesB = kRowsW * kBlockK;                    // 32 KiB / 16 KiB
+  static constexpr int kStages = kCtaGroup == 1 ? 4 : 6;              // 192 KiB of operand ring either way
+  static constexpr int kStageTxBytes = (kBytesA + kBytesB) * kCtaGroup;  // bytes credited to one full barrier
+  static constexpr int kEpiBytes = 4 * 2 * kStoreRows * kStoreCols * 2;  // 4 warps x 2 buffers x 4 KiB
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSmemBytes = kStages * (kBytesA + kBytesB) + kEpiBytes + kBarBytes + 1024;
+  static constexpr int kTileM = kBlockM * kCtaGroup;  // rows of Y per (cluster) tile
+};
+
+struct TcParams {
+  const float* x_scale;
+  const float* w_scale;
+  const __nv_bfloat16* bias;  // may be null
+  __nv_bfloat16* y;
+  int M, N, K;
+  long long ldy;       // elements
+  int use_tma_store;   // 0: plain predicated stores
+  int group_m;         // tile-rasterisation group height (tiles)
+  uint32_t* status;    // device status word
+};
+
+template <int kCtaGroup>
+cudaError_t launch_gemm_tc(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
+                           const TcParams& p, int num_ctas, cudaStream_t stream);
+
+// ------------------------ skinny-M stream-K kernel (gemm_skinny.cu) ------------------------
+struct SkinnyGeometry {
+  static constexpr int kRowsW = 128;   // W rows per tile (MMA M, TMEM lanes)
+  static constexpr int kBlockK = 128;  // bytes of K per stage
+  static constexpr int kMaxTokens = 128;
+  static constexpr int kThreads = 192;
+  static constexpr int kBytesA = kRowsW * kBlockK;  // 16 KiB of W per stage
+  static constexpr int kBarBytes = 512;
+  static constexpr int kMaxStages = 12;
+  // The arrival counters occupy a region of fixed size right after the workspace header, whatever
+  // N is, so that a workspace left zero by one problem size is still zero where the next size
+  // (with a different number of tiles) looks for its counters.
+  static constexpr int kMaxTiles = 16384;  // N <= 2,097,152
+  static constexpr size_t kCounterRegionBytes = static_cast<size_t>(kMaxTiles) * 4 * sizeof(uint32_t);
+  static constexpr int kSmemBudget = 220 * 1024;
+};
+
+struct SkinnyPlan {
+  int tokens_pad;    // M rounded up to 16: MMA N and rows of the X box
+  int stages;        // pipeline depth
+  int num_ctas;      // grid
+  int tiles;         // ceil(N / 128)
+  int kblocks;       // ceil(K / 128)
+  int units_per_cta; // consecutive (tile, k-block) units each CTA owns
+  int segs_per_cta;  // upper bound on tile segments per CTA (partial-sum slots)
+  size_t smem_bytes;
+  size_t partial_bytes;  // fp32 partial sums
+  size_t counter_bytes;  // fixed-size region of per (tile, lane quarter) arrival counters
+};
+
+SkinnyPlan make_skinny_plan(int M, int N, int K, int sm_count);
+
+struct SkinnyParams {
+  const float* x_scale;
+  const float* w_scale;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* y;
+  int M, N, K;
+  long long ldy;
+  float* partials;     // [num_ctas * segs_per_cta][tokens_pad][128] fp32
+  uint32_t* counters;  // [tiles * 4], zero on entry, zero again on exit
+  uint32_t* status;
+};
+
+cudaError_t launch_gemm_skinny(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const SkinnyParams& p,
+                               const SkinnyPlan& plan, cudaStream_t stream);
+
+// ------------------------------ CUDA-core kernel (gemm_simt.cu) -----------------------------
+struct SimtParams {
+  const uint8_t* xq;
+  const uint8_t* wq;
+  const float* x_scale;
+  const float* w_scale;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* y;
+  int M, N, K;
+  long long ldx, ldw, ldy;
+};
+
+cudaError_t launch_gemm_simt(const SimtParams& p, cudaStream_t stream);
+
+}  // namespace b200fp8

@@ -1,0 +1,176 @@
+"""PyTorch-facing wrapper of the C ABI: tensors in, bf16 tensor out, work enqueued on the current
+CUDA stream.  PyTorch supplies device memory and streams only; the arithmetic is the library's.
+
+Mirrors the call the reference backends make,
+`triton_fp8_row(xq, wq, x_scale, w_scale, bias=...)` / `torch.ops.fbgemm.f8f8bf16_rowwise(...)`
+(tritonbench/operators/fp8_gemm_rowwise/operator.py:187-217): same argument order and meaning,
+a fresh bf16 [M, N] tensor as the result.
+"""
+from typing import Callable, Dict, Optional, Tuple
+
+import torch
+
+from . import lib as _lib
+
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (the library has no CPU path)")
+
+
+def get_workspace(device: torch.device, nbytes: int, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """Zero-initialised workspace for (device, stream); grown, never shrunk.  Calls that share a
+    workspace must be ordered on one stream, which is why it is keyed by stream."""
+    stream = stream or torch.cuda.current_stream(device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream.cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        size = max(nbytes, _lib.WORKSPACE_HEADER_BYTES)
+        ws = torch.zeros(size, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def workspace_bytes(m: int, n: int, k: int, flags: int = 0) -> int:
+    nbytes = _lib.load().b200fp8_workspace_bytes(m, n, k, flags)
+    if nbytes == 0:
+        raise ValueError(f"no plan for M={m} N={n} K={k} flags={flags:#x}")
+    return nbytes
+
+
+def _flags(variant: str, tma_store: bool) -> int:
+    if variant not in _lib.VARIANTS:
+        raise ValueError(f"unknown variant {variant!r}; one of {sorted(_lib.VARIANTS)}")
+    return _lib.VARIANTS[variant] | (0 if tma_store else _lib.FLAG_NO_TMA_STORE)
+
+
+def fp8_gemm_rowwise(
+    xq: torch.Tensor,
+    wq: torch.Tensor,
+    x_scale: torch.Tensor,
+    w_scale: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    variant: str = "auto",
+    tma_store: bool = True,
+    workspace: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Y = bf16((xq @ wq.T) * x_scale[:, None] * w_scale[None, :] (+ bias)), fp32 accumulation.
+
+    xq [M, K] and wq [N, K] are float8_e4m3fn (or uint8 holding e4m3 bytes) with K contiguous;
+    x_scale [M], w_scale [N] float32; bias [N] bfloat16 or None.  Asynchronous on the current stream.
+    """
+    for t, name in ((xq, "xq"), (wq, "wq"), (x_scale, "x_scale"), (w_scale, "w_scale")):
+        _require_cuda(t, name)
+    if xq.dim() != 2 or wq.dim() != 2 or xq.shape[1] != wq.shape[1]:
+        raise ValueError(f"xq {tuple(xq.shape)} and wq {tuple(wq.shape)} must be [M, K] and [N, K]")
+    if xq.element_size() != 1 or wq.element_size() != 1:
+        raise ValueError("xq and wq must hold one byte per element (float8_e4m3fn)")
+    if xq.stride(1) != 1 or wq.stride(1) != 1:
+        raise ValueError("xq and wq must have K contiguous")
+    m, k = xq.shape
+    n = wq.shape[0]
+    if x_scale.dtype != torch.float32 or w_scale.dtype != torch.float32:
+        raise ValueError("scales must be float32")
+    if x_scale.numel() != m or w_scale.numel() != n:
+        raise ValueError("x_scale must have M elements and w_scale N elements")
+    x_scale = x_scale.contiguous()
+    w_scale = w_scale.contiguous()
+    if bias is not None:
+        _require_cuda(bias, "bias")
+        if bias.dtype != torch.bfloat16 or bias.numel() != n:
+            raise ValueError("bias must be bfloat16 with N elements")
+        bias = bias.contiguous()
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=xq.device)
+    elif out.dtype != torch.bfloat16 or tuple(out.shape) != (m, n) or out.stride(1) != 1:
+        raise ValueError("out must be bfloat16 [M, N] with N contiguous")
+
+    flags = _flags(variant, tma_store)
+    lib = _lib.load()
+    if workspace is None:
+        workspace = get_workspace(xq.device, workspace_bytes(m, n, k, flags))
+    stream = torch.cuda.current_stream(xq.device).cuda_stream
+    status = lib.b200fp8_gemm_rowwise(
+        xq.data_ptr(), wq.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(),
+        bias.data_ptr() if bias is not None else None, out.data_ptr(),
+        m, n, k, xq.stride(0), wq.stride(0), out.stride(0),
+        workspace.data_ptr(), workspace.numel(), flags, stream,
+    )
+    _lib.check(status, f"b200fp8_gemm_rowwise(M={m}, N={n}, K={k}, variant={variant})")
+    return out
+
+
+def make_gemm_fn(xq, wq, x_scale, w_scale, bias=None, variant: str = "auto", reuse_out: bool = False) -> Callable:
+    """Zero-argument closure in the shape the TritonBench harness wants from a backend
+    (triton_op.py:765-785).  The workspace is allocated here, outside any timed or captured
+    region; each call of the closure only enqueues the kernel."""
+    m, k = xq.shape
+    n = wq.shape[0]
+    flags = _flags(variant, True)
+    ws = get_workspace(xq.device, workspace_bytes(m, n, k, flags))
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=xq.device) if reuse_out else None
+
+    def fn():
+        return fp8_gemm_rowwise(xq, wq, x_scale, w_scale, bias, out=out, variant=variant, workspace=ws)
+
+    return fn
+
+
+def check_device_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any kernel recorded a timed-out wait in a workspace."""
+    torch.cuda.synchronize(device)
+    lib = _lib.load()
+    import ctypes
+
+    for ws in list(_workspaces.values()):
+        word = ctypes.c_uint32(0)
+        status = lib.b200fp8_query_status(ws.data_ptr(), ctypes.byref(word))
+        if status != _lib.OK:
+            ws.zero_()
+            _lib.check(status, f"device status word {word.value:#010x}")
+
+
+class HostGemm:
+    """Host-buffer GEMM: inputs and output are CPU tensors (pin them for full PCIe speed);
+    every call copies in, runs the kernel, copies out and synchronises."""
+
+    def __init__(self, m: int, n: int, k: int, variant: str = "auto"):
+        import ctypes
+
+        self.shape = (m, n, k)
+        self._ctx = ctypes.c_void_p()
+        self._lib = _lib.load()
+        _lib.check(
+            self._lib.b200fp8_host_ctx_create(m, n, k, _flags(variant, True), ctypes.byref(self._ctx)),
+            "b200fp8_host_ctx_create",
+        )
+
+    def __call__(self, xq, wq, x_scale, w_scale, bias=None, out=None) -> torch.Tensor:
+        m, n, k = self.shape
+        for t in (xq, wq, x_scale, w_scale):
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError("HostGemm takes contiguous CPU tensors")
+        if tuple(xq.shape) != (m, k) or tuple(wq.shape) != (n, k):
+            raise ValueError("shape differs from the context's")
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.bfloat16, pin_memory=True)
+        status = self._lib.b200fp8_gemm_rowwise_host(
+            self._ctx, xq.data_ptr(), wq.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(),
+            bias.data_ptr() if bias is not None else None, out.data_ptr(),
+        )
+        _lib.check(status, "b200fp8_gemm_rowwise_host")
+        return out
+
+    def close(self) -> None:
+        if self._ctx:
+            self._lib.b200fp8_host_ctx_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
