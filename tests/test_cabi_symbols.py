@@ -1,0 +1,87 @@
+"""The C-ABI library loads without a GPU, exports every function include/b200fp8.h declares, and
+answers the calls that need no device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from tritonbench_b200 import lib
+from tritonbench_b200.csrc import build as csrc_build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "b200fp8.h")
+
+
+@pytest.fixture(scope="module")
+def cdll():
+    if not os.path.exists(lib.LIB_PATH):
+        csrc_build.build()
+    return lib.load()
+
+
+def _declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200fp8_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_and_binding_list_the_same_functions():
+    assert _declared_functions() == sorted(lib.EXPORTED_SYMBOLS)
+
+
+def test_every_declared_symbol_is_exported(cdll):
+    for name in _declared_functions():
+        assert hasattr(cdll, name), name
+
+
+def test_abi_version_and_status_strings(cdll):
+    assert cdll.b200fp8_abi_version() == 1
+    seen = {lib.status_string(s) for s in range(8)}
+    assert len(seen) == 8 and "ok" in seen
+    assert lib.status_string(99) == "unknown status"
+
+
+def test_null_pointers_and_bad_sizes_are_rejected_before_any_device_work(cdll):
+    one = ctypes.create_string_buffer(512)
+    p = ctypes.addressof(one)
+    f = cdll.b200fp8_gemm_rowwise
+    assert f(None, p, p, p, None, p, 1, 1, 16, 16, 16, 8, p, 512, 0, None) == lib.BAD_ARG
+    assert f(p, p, p, p, None, p, 0, 1, 16, 16, 16, 8, p, 512, 0, None) == lib.BAD_ARG
+    assert f(p, p, p, p, None, p, 1, 1, 16, 8, 16, 8, p, 512, 0, None) == lib.BAD_ARG  # ldx < K
+    assert f(p, p, p, p, None, p, 1 << 40, 1, 16, 16, 16, 8, p, 512, 0, None) == lib.TOO_LARGE
+    assert cdll.b200fp8_workspace_init(None, 1024, None) == lib.BAD_ARG
+    assert cdll.b200fp8_query_status(None, None) == lib.BAD_ARG
+
+
+def test_workspace_sizes_and_plans_need_no_device(cdll):
+    assert cdll.b200fp8_workspace_bytes(8192, 8192, 8192, 0) == lib.WORKSPACE_HEADER_BYTES
+    skinny = cdll.b200fp8_workspace_bytes(16, 28672, 8192, 0)
+    assert skinny > 256 * 1024  # counters + partial sums
+    assert cdll.b200fp8_workspace_bytes(0, 1, 1, 0) == 0
+    assert cdll.b200fp8_workspace_bytes(256, 256, 256, lib.VARIANT_SKINNY) == 0  # M > 128
+    assert lib.describe_plan(8192, 8192, 8192).startswith("tc_2cta")
+    assert lib.describe_plan(300, 512, 512).startswith("tc_1cta")
+    assert lib.describe_plan(16, 28672, 8192).startswith("skinny")
+    assert lib.describe_plan(16, 28672, 8192, lib.VARIANT_SIMT).startswith("simt")
+
+
+def test_check_maps_statuses_to_python_exceptions(cdll):
+    lib.check(lib.OK, "x")
+    with pytest.raises(NotImplementedError):
+        lib.check(lib.UNSUPPORTED_ALIGNMENT, "x")
+    with pytest.raises(lib.B200Fp8Error) as e:
+        lib.check(lib.DEVICE_TIMEOUT, "x")
+    assert e.value.status == lib.DEVICE_TIMEOUT
+
+
+def test_no_load_in_the_library_uses_cluster_multicast():
+    # no TMA / bulk LOAD in this library may carry cluster multicast; the only multicast token
+    # allowed is on tcgen05.commit (an mbarrier arrive)
+    src_dir = os.path.join(ROOT, "tritonbench_b200", "csrc")
+    for name in os.listdir(src_dir):
+        if not name.endswith((".cu", ".cuh", ".h")):
+            continue
+        for line in open(os.path.join(src_dir, name)):
+            if "multicast" in line and "cp.async" in line:
+                raise AssertionError(f"{name}: {line.strip()}")

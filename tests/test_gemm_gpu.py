@@ -1,0 +1,322 @@
+"""Parity of the CUDA path against the oracle, through the C ABI (tritonbench_b200.ops is a thin
+ctypes wrapper).  Tolerance everywhere: max |out - ref| <= 1 bf16 ulp of |ref| + 1e-2 * RMS(ref)
+(oracle.fp8_rowwise_oracle.tolerance), the bound the benchmark specification states."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import fp8_rowwise_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TC_VARIANTS = ("tc_1cta", "tc_2cta")
+
+
+def _ops():
+    from tritonbench_b200 import ops
+
+    return ops
+
+
+def _gpu(*ts):
+    return [t.cuda() if t is not None else None for t in ts]
+
+
+def _run(variant, xq, wq, xs, ws, bias=None, **kw):
+    ops = _ops()
+    y = ops.fp8_gemm_rowwise(*_gpu(xq, wq, xs, ws), bias=bias.cuda() if bias is not None else None, variant=variant, **kw)
+    ops.check_device_status()
+    return y
+
+
+def _assert_close(y, ref, what=""):
+    res = orc.compare(y, ref)
+    assert res["ok"], f"{what}: {res}"
+    return res
+
+
+def _inputs(m, n, k, seed=0, dist="normal", w_std=1.0):
+    from tritonbench_b200 import quantize
+
+    return quantize.make_inputs(m, n, k, device="cpu", x_seed=seed, dist=dist, w_std=w_std)
+
+
+def _bf16(bits):
+    return torch.from_numpy(bits.astype(np.int16)).view(torch.bfloat16)
+
+
+# ------------------------------------------------------------------ golden fixtures
+@pytest.mark.parametrize("variant", ["auto", "tc_1cta", "tc_2cta", "skinny", "simt"])
+@pytest.mark.parametrize("fixture", ["config1_seed0_128x256x512.npz", "ref_quantizer_bf16_128x256x512.npz"])
+def test_golden_fixture(cuda_device, golden_dir, variant, fixture):
+    d = np.load(os.path.join(golden_dir, fixture))
+    xq, wq = torch.from_numpy(d["xq"]).view(torch.float8_e4m3fn), torch.from_numpy(d["wq"]).view(torch.float8_e4m3fn)
+    xs, ws = torch.from_numpy(d["x_scale"]), torch.from_numpy(d["w_scale"])
+    y = _run(variant, xq, wq, xs, ws)
+    _assert_close(y, _bf16(d["y_bf16"]), f"{variant} {fixture}")
+
+
+# ------------------------------------------------------------------ ragged / tail shapes
+TAIL_SHAPES = [
+    (1, 8, 16), (129, 257, 144), (130, 264, 400), (255, 1001, 1040), (777, 1024, 2048), (300, 520, 3584),
+    (513, 768, 128), (256, 512, 16), (1000, 5120, 512),
+]
+
+
+@pytest.mark.parametrize("variant", TC_VARIANTS)
+@pytest.mark.parametrize("shape", TAIL_SHAPES)
+def test_tile_tails_large_m_kernels(cuda_device, variant, shape):
+    m, n, k = shape
+    xq, wq, xs, ws = _inputs(m, n, k, seed=m + n + k)
+    ref = orc.gemm_rowwise(xq, wq, xs, ws)
+    _assert_close(_run(variant, xq, wq, xs, ws), ref, f"{variant} {shape}")
+    _assert_close(_run(variant, xq, wq, xs, ws, tma_store=False), ref, f"{variant} {shape} plain stores")
+
+
+SKINNY_SHAPES = [
+    (1, 8, 16), (1, 256, 512), (3, 1000, 1040), (8, 2304, 2304), (16, 1024, 1024), (17, 520, 400), (33, 4096, 2304),
+    (64, 4096, 2048), (100, 1000, 4096), (128, 2304, 6656), (127, 129, 144),
+]
+
+
+@pytest.mark.parametrize("shape", SKINNY_SHAPES)
+def test_skinny_kernel_shapes(cuda_device, shape):
+    m, n, k = shape
+    xq, wq, xs, ws = _inputs(m, n, k, seed=7 * m + n)
+    ref = orc.gemm_rowwise(xq, wq, xs, ws)
+    _assert_close(_run("skinny", xq, wq, xs, ws), ref, f"skinny {shape}")
+
+
+def test_skinny_workspace_survives_changes_of_geometry(cuda_device):
+    """One workspace, problem sizes with different tile counts back to back: the counters a call
+    leaves behind must still be zero where the next call looks for its own."""
+    ops = _ops()
+    ws_bytes = max(ops.workspace_bytes(m, n, k) for (m, n, k) in SKINNY_SHAPES)
+    workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
+    for rep in range(2):
+        for (m, n, k) in [(64, 4096, 2048), (1, 8192, 4096), (100, 1000, 4096), (8, 2304, 2304), (16, 1024, 1024)]:
+            xq, wq, xs, wsc = _inputs(m, n, k, seed=rep)
+            y = ops.fp8_gemm_rowwise(*_gpu(xq, wq, xs, wsc), variant="skinny", workspace=workspace)
+            _assert_close(y, orc.gemm_rowwise(xq, wq, xs, wsc), f"skinny {(m, n, k)} rep {rep}")
+    torch.cuda.synchronize()
+    assert int(workspace[: 256 + 262144].to(torch.int64).sum()) == 0  # status word and counters are zero again
+
+
+# ------------------------------------------------------------------ benchmark configurations
+@pytest.mark.parametrize("m", [1, 16, 64, 128])
+def test_config3_decode_shapes(cuda_device, m):
+    xq, wq, xs, ws = _inputs(m, 28672, 8192, seed=0, w_std=0.02)
+    ref = orc.gemm_rowwise(xq, wq, xs, ws)
+    res = _assert_close(_run("auto", xq, wq, xs, ws), ref, f"decode M={m}")
+    assert res["max_ratio"] < 0.9
+
+
+@pytest.mark.parametrize("shape", [(1000, 5120, 3584), (3000, 7168, 2048), (4096, 14336, 4096), (777, 1024, 8192)])
+def test_config5_irregular_student_t(cuda_device, shape):
+    m, n, k = shape
+    xq, wq, xs, ws = _inputs(m, n, k, seed=0, dist="student_t3")
+    ref32 = orc.gemm_rowwise(xq, wq, xs, ws, keep_fp32=True)
+    ref = ref32.to(torch.bfloat16)
+    for variant in ("auto",) + TC_VARIANTS:
+        y = _run(variant, xq, wq, xs, ws)
+        _assert_close(y, ref, f"{variant} {shape}")
+        # stricter, per row: heavy rows must not hide errors in light rows behind the global RMS
+        yf, rf = y.float().cpu(), ref.float()
+        row_rms = ref32.pow(2).mean(dim=1, keepdim=True).sqrt()
+        assert bool(((yf - rf).abs() <= orc.bf16_ulp(rf) + 1e-2 * row_rms).all()), f"{variant} {shape} per-row bound"
+
+
+def test_config2_square_8192_against_oracle_rows_and_cuda_core_kernel(cuda_device):
+    m = n = k = 8192
+    from tritonbench_b200 import quantize
+
+    xq, wq, xs, ws = quantize.make_inputs(m, n, k, device="cuda", x_seed=0)
+    ops = _ops()
+    y2 = ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="tc_2cta")
+    y1 = ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="tc_1cta")
+    ya = ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="auto")
+    ysimt = ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="simt")
+    ops.check_device_status()
+    assert torch.equal(ya, y2)  # auto picks the CTA-pair kernel here
+    # every element against the CUDA-core kernel (independent data path, fp32 FMA in ascending k)
+    rms = ysimt.float().pow(2).mean().sqrt()
+    for y in (y1, y2):
+        diff = (y.float() - ysimt.float()).abs()
+        ulp = torch.exp2(torch.floor(torch.log2(ysimt.float().abs().clamp(min=2.0 ** -126))) - 7.0)
+        assert bool((diff <= ulp + 1e-2 * rms).all())
+    # 512 rows against the CPU oracle (first tile, last tile, and a seeded sample)
+    g = torch.Generator().manual_seed(0)
+    rows = torch.cat([torch.arange(0, 128), torch.arange(m - 128, m), torch.randperm(m, generator=g)[:256]])
+    ref = orc.gemm_rowwise(xq[rows.cuda()].cpu(), wq.cpu(), xs[rows.cuda()].cpu(), ws.cpu())
+    for y in (y1, y2):
+        _assert_close(y[rows.cuda()], ref, "8192^3 row sample")
+
+
+def test_full_size_properties_permutation_and_power_of_two_scaling(cuda_device):
+    """Size-independent properties at the full 8192^3 size: a row of Y depends only on its row of X
+    (bit-exact under a permutation of rows), and multiplying a scale by a power of two multiplies
+    the output by exactly that power."""
+    m = n = k = 8192
+    from tritonbench_b200 import quantize
+
+    xq, wq, xs, ws = quantize.make_inputs(m, n, k, device="cuda", x_seed=1)
+    ops = _ops()
+    y = ops.fp8_gemm_rowwise(xq, wq, xs, ws)
+    perm = torch.randperm(m, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
+    yp = ops.fp8_gemm_rowwise(xq.view(torch.uint8)[perm].view(torch.float8_e4m3fn), wq, xs[perm], ws)
+    assert torch.equal(yp, y[perm])
+    y4 = ops.fp8_gemm_rowwise(xq, wq, xs * 4.0, ws * 0.5)
+    assert torch.equal(y4.float(), y.float() * 2.0)
+    again = ops.fp8_gemm_rowwise(xq, wq, xs, ws)
+    assert torch.equal(again, y)
+    ops.check_device_status()
+
+
+def test_config4_prefill_shard_shape_on_one_gpu(cuda_device):
+    """The whole M=65536 prefill problem on one GPU: sampled rows of every 8192-row shard against
+    the oracle (the shards are what the ranks of the sharded run compute)."""
+    from tritonbench_b200 import dist, quantize
+
+    n = k = 8192
+    wq, ws = quantize.make_quantized(n, k, seed=dist.W_SEED, device="cuda")
+    ops = _ops()
+    for rank in (0, 3, 7):
+        xq, xs = quantize.make_quantized(8192, k, seed=dist.shard_seed(rank), device="cuda")
+        y = ops.fp8_gemm_rowwise(xq, wq, xs, ws)
+        rows = torch.arange(rank * 16, 8192, 128, device="cuda")
+        ref = orc.gemm_rowwise(xq[rows].cpu(), wq.cpu(), xs[rows].cpu(), ws.cpu())
+        _assert_close(y[rows], ref, f"prefill shard {rank}")
+    ops.check_device_status()
+
+
+def test_reference_builtin_decode_shapes(cuda_device, golden_dir):
+    shapes = np.load(os.path.join(golden_dir, "ref_builtin_shapes.npz"))["shapes"]
+    for (m, n, k) in shapes:
+        if m > 128:
+            continue
+        xq, wq, xs, ws = _inputs(int(m), int(n), int(k), seed=int(m))
+        _assert_close(_run("auto", xq, wq, xs, ws), orc.gemm_rowwise(xq, wq, xs, ws), f"builtin {(m, n, k)}")
+
+
+# ------------------------------------------------------------------ options and edge cases
+@pytest.mark.parametrize("variant,shape", [("tc_1cta", (300, 520, 400)), ("tc_2cta", (513, 1001, 256)), ("skinny", (17, 520, 400)), ("simt", (50, 70, 90))])
+def test_bias(cuda_device, variant, shape):
+    m, n, k = shape
+    xq, wq, xs, ws = _inputs(m, n, k, seed=3)
+    bias = (torch.randn(n, generator=torch.Generator().manual_seed(4)) * 30).to(torch.bfloat16)
+    _assert_close(_run(variant, xq, wq, xs, ws, bias=bias), orc.gemm_rowwise(xq, wq, xs, ws, bias), f"{variant} bias")
+
+
+def test_unaligned_k_falls_to_cuda_core_kernel_and_forced_variants_refuse(cuda_device):
+    m, n, k = 70, 90, 130  # rows of 130 bytes cannot start on 16-byte boundaries
+    xq, wq, xs, ws = _inputs(m, n, k, seed=8)
+    _assert_close(_run("auto", xq, wq, xs, ws), orc.gemm_rowwise(xq, wq, xs, ws), "auto -> simt")
+    for variant in TC_VARIANTS + ("skinny",):
+        with pytest.raises(NotImplementedError):
+            _run(variant, xq, wq, xs, ws)
+
+
+def test_row_pitch_larger_than_k_and_strided_output(cuda_device):
+    ops = _ops()
+    m, n, k = 260, 520, 384
+    xq, wq, xs, ws = _inputs(m, n, k, seed=2)
+    ref = orc.gemm_rowwise(xq, wq, xs, ws)
+    big_x = torch.zeros((m, k + 128), dtype=torch.uint8, device="cuda")
+    big_w = torch.zeros((n, k + 256), dtype=torch.uint8, device="cuda")
+    big_x[:, :k] = xq.view(torch.uint8).cuda()
+    big_w[:, :k] = wq.view(torch.uint8).cuda()
+    out_big = torch.zeros((m, n + 8), dtype=torch.bfloat16, device="cuda")
+    for variant in TC_VARIANTS:
+        out_big.zero_()
+        y = ops.fp8_gemm_rowwise(big_x[:, :k], big_w[:, :k], xs.cuda(), ws.cuda(), out=out_big[:, :n], variant=variant)
+        _assert_close(y, ref, f"{variant} pitched")
+        assert float(out_big[:, n:].abs().max()) == 0.0  # nothing written past N
+    ops.check_device_status()
+
+
+def test_extreme_scales_and_zero_rows(cuda_device):
+    m, n, k = 130, 264, 256
+    xq, wq, xs, ws = _inputs(m, n, k, seed=6)
+    xq = xq.clone()
+    xq.view(torch.uint8)[5] = 0
+    xs = xs.clone()
+    xs[5] = 1e-12 / 448.0
+    xs[6] = 3.0e4
+    ws = ws.clone()
+    ws[9] = 1e-20
+    ref = orc.gemm_rowwise(xq, wq, xs, ws)
+    for variant in TC_VARIANTS + ("simt",):
+        y = _run(variant, xq, wq, xs, ws)
+        _assert_close(y, ref, f"{variant} extreme scales")
+        assert float(y[5].abs().max()) == 0.0
+
+
+def test_saturated_operands_all_448(cuda_device):
+    m, n, k = 128, 256, 4096
+    xq = torch.full((m, k), 0x7E, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    wq = torch.full((n, k), 0xFE, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    xs = torch.ones(m)
+    ws = torch.ones(n)
+    ref = orc.gemm_rowwise(xq, wq, xs, ws)
+    assert float(ref[0, 0]) == float(torch.tensor(-448.0 * 448.0 * k).to(torch.bfloat16))
+    for variant in TC_VARIANTS + ("skinny",):
+        assert torch.equal(_run(variant, xq, wq, xs, ws).cpu(), ref)
+
+
+def test_status_codes_for_bad_calls(cuda_device):
+    from tritonbench_b200 import lib
+
+    ops = _ops()
+    xq, wq, xs, ws = _gpu(*_inputs(16, 1024, 1024))
+    tiny = torch.zeros(256, dtype=torch.uint8, device="cuda")
+    with pytest.raises(lib.B200Fp8Error) as e:
+        ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="skinny", workspace=tiny)
+    assert e.value.status == lib.WORKSPACE_TOO_SMALL
+    x2, w2, xs2, ws2 = _gpu(*_inputs(200, 256, 256))
+    with pytest.raises(ValueError):
+        ops.workspace_bytes(200, 256, 256, lib.VARIANT_SKINNY)
+    with pytest.raises(ValueError):
+        ops.fp8_gemm_rowwise(x2, w2, xs2[:10], ws2)
+    with pytest.raises(ValueError):
+        ops.fp8_gemm_rowwise(x2.cpu(), w2, xs2, ws2)
+
+
+def test_call_is_capturable_in_a_cuda_graph(cuda_device):
+    """The reference times this operator by CUDA-graph replay; the call must allocate nothing and
+    never synchronise.  Captured and replayed results equal the eager ones bit for bit."""
+    ops = _ops()
+    for variant, shape in (("tc_2cta", (512, 1024, 1024)), ("tc_1cta", (300, 520, 400)), ("skinny", (16, 4096, 2048))):
+        xq, wq, xs, ws = _gpu(*_inputs(*shape, seed=1))
+        fn = ops.make_gemm_fn(xq, wq, xs, ws, variant=variant, reuse_out=True)
+        eager = fn().clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn_side = ops.make_gemm_fn(xq, wq, xs, ws, variant=variant, reuse_out=True)
+            fn_side()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                out = fn_side()
+        out.zero_()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager), variant
+    ops.check_device_status()
+
+
+def test_host_buffer_entry_point(cuda_device):
+    ops = _ops()
+    for variant, shape in (("auto", (384, 768, 512)), ("auto", (16, 2304, 2048))):
+        m, n, k = shape
+        xq, wq, xs, ws = _inputs(m, n, k, seed=12)
+        bias = torch.randn(n).to(torch.bfloat16)
+        hg = ops.HostGemm(m, n, k, variant=variant)
+        pinned = [t.contiguous().pin_memory() for t in (xq.view(torch.uint8), wq.view(torch.uint8), xs, ws)]
+        y = hg(*pinned)
+        _assert_close(y, orc.gemm_rowwise(xq, wq, xs, ws), f"host {shape}")
+        yb = hg(*pinned, bias=bias.pin_memory())
+        _assert_close(yb, orc.gemm_rowwise(xq, wq, xs, ws, bias), f"host bias {shape}")
+        hg.close()

@@ -2,6 +2,7 @@
 // variant, TMA descriptor encoding, workspace layout, and the host-buffer context.
 #include <cudaTypedefs.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -15,6 +16,9 @@ namespace {
 using namespace b200fp8;
 
 thread_local int g_last_cuda_error = 0;
+#ifdef B200FP8_DEBUG_KNOBS
+unsigned long long* g_debug_trace = nullptr;
+#endif
 
 struct DeviceInfo {
   bool known = false;
@@ -153,6 +157,10 @@ int check_sizes(int64_t M, int64_t N, int64_t K) {
 
 extern "C" {
 
+#ifdef B200FP8_DEBUG_KNOBS
+void b200fp8_debug_set_trace(void* p) { g_debug_trace = static_cast<unsigned long long*>(p); }
+#endif
+
 int b200fp8_abi_version(void) { return B200FP8_ABI_VERSION; }
 
 const char* b200fp8_status_string(int status) {
@@ -248,6 +256,9 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
     off = (off + pl.skinny.counter_bytes + 255) & ~static_cast<size_t>(255);
     kp.partials = reinterpret_cast<float*>(ws + off);
     kp.status = status_word;
+#ifdef B200FP8_DEBUG_KNOBS
+    kp.trace = g_debug_trace;
+#endif
     return note_cuda(launch_gemm_skinny(tm_w, tm_x, kp, pl.skinny, stream));
   }
 
@@ -276,6 +287,9 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
   tp.use_tma_store = pl.tma_store ? 1 : 0;
   tp.group_m = pl.group_m;
   tp.status = status_word;
+#ifdef B200FP8_DEBUG_KNOBS
+  tp.debug = getenv("B200FP8_DEBUG") ? atoi(getenv("B200FP8_DEBUG")) : 0;
+#endif
   if (cta_group == 2) return note_cuda(launch_gemm_tc<2>(tm_x, tm_w, tm_y, tp, pl.num_ctas, stream));
   return note_cuda(launch_gemm_tc<1>(tm_x, tm_w, tm_y, tp, pl.num_ctas, stream));
 }

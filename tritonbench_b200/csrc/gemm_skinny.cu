@@ -53,17 +53,59 @@ enum WaitSite : uint32_t {
 
 struct Segment {
   int tile;
+  int slot;  // index of the segment inside this CTA's run (selects the partial-sum slot)
   int kb0;
   int kb1;
 };
 
-// The run of units [u, u_end) starts with a segment of tile u / kblocks.
-__device__ __forceinline__ Segment first_segment(long long u, long long u_end, int kblocks) {
+// One CTA's run of consecutive units [u_begin, u_stop) cut at tile boundaries.  Segments that
+// cover only part of a tile's K range are processed FIRST (the one at the end of the run, then
+// the one at its start), the whole tiles after them: the cross-CTA fix-up of a split tile then
+// happens early, hidden behind the streaming of the remaining tiles, instead of at the very end
+// of the kernel where nothing overlaps it.
+struct Run {
+  long long u_begin;
+  long long u_stop;
+  int kblocks;
+  int first_tile;
+  int count;
+  bool tail_first;  // last segment is partial and goes first
+  bool head_next;   // first segment is partial (and is not that same segment)
+};
+
+__device__ __forceinline__ Run make_run(long long u_begin, long long u_stop, int kblocks) {
+  Run r;
+  r.u_begin = u_begin;
+  r.u_stop = u_stop;
+  r.kblocks = kblocks;
+  r.first_tile = static_cast<int>(u_begin / kblocks);
+  r.count = u_stop > u_begin ? static_cast<int>((u_stop - 1) / kblocks) - r.first_tile + 1 : 0;
+  r.tail_first = r.count > 0 && (u_stop % kblocks) != 0;
+  r.head_next = r.count > 0 && (u_begin % kblocks) != 0 && !(r.tail_first && r.count == 1);
+  return r;
+}
+
+// i-th segment in processing order
+__device__ __forceinline__ Segment run_segment(const Run& r, int i) {
+  int j;  // position in the run
+  int pos = 0;
+  if (r.tail_first && i == 0) {
+    j = r.count - 1;
+  } else {
+    pos += r.tail_first ? 1 : 0;
+    if (r.head_next && i == pos) {
+      j = 0;
+    } else {
+      pos += r.head_next ? 1 : 0;
+      j = (r.head_next ? 1 : 0) + (i - pos);
+    }
+  }
   Segment s;
-  s.tile = static_cast<int>(u / kblocks);
-  s.kb0 = static_cast<int>(u - static_cast<long long>(s.tile) * kblocks);
-  const long long left = u_end - u;
-  s.kb1 = (s.kb0 + left < kblocks) ? static_cast<int>(s.kb0 + left) : kblocks;
+  s.slot = j;
+  s.tile = r.first_tile + j;
+  const long long tile_u0 = static_cast<long long>(s.tile) * r.kblocks;
+  s.kb0 = r.u_begin > tile_u0 ? static_cast<int>(r.u_begin - tile_u0) : 0;
+  s.kb1 = r.u_stop < tile_u0 + r.kblocks ? static_cast<int>(r.u_stop - tile_u0) : r.kblocks;
   return s;
 }
 
@@ -73,10 +115,16 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                    const int units_per_cta, const int segs_per_cta, const long long total_units) {
   using G = SkinnyGeometry;
 
+#ifdef B200FP8_DEBUG_KNOBS
+#define SK_TRACE(i) do { if (p.trace) p.trace[blockIdx.x * 8 + (i)] = globaltimer_ns(); } while (0)
+#else
+#define SK_TRACE(i) do {} while (0)
+#endif
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw_addr);
+  if (threadIdx.x == 0) SK_TRACE(0);
 
   const int bytes_b = tokens_pad * G::kBlockK;
   const uint32_t smem_a = base;
@@ -96,6 +144,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
   const long long u_begin = static_cast<long long>(blockIdx.x) * units_per_cta;
   const long long u_stop = u_begin + units_per_cta < total_units ? u_begin + units_per_cta : total_units;
+  const Run run = make_run(u_begin, u_stop, kblocks);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -121,6 +170,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  if (threadIdx.x == 0) SK_TRACE(1);
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
@@ -128,9 +178,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       const uint32_t tx_bytes = static_cast<uint32_t>(G::kBytesA + bytes_b);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      long long u = u_begin;
-      while (u < u_stop && ok) {
-        const Segment sg = first_segment(u, u_stop, kblocks);
+      for (int i = 0; i < run.count && ok; ++i) {
+        const Segment sg = run_segment(run, i);
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           ok = mbar_wait<false>(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty);
           if (!ok) break;
@@ -143,7 +192,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             phase ^= 1u;
           }
         }
-        u += sg.kb1 - sg.kb0;
       }
       if (!ok) {
         const unsigned long long t0 = globaltimer_ns();
@@ -155,13 +203,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (lane == 0) {
       const uint32_t idesc = instr_desc_e4m3(G::kRowsW, static_cast<uint32_t>(tokens_pad));
       uint32_t stage = 0, phase = 0;
-      uint32_t seg = 0;
       bool ok = true;
-      long long u = u_begin;
-      while (u < u_stop && ok) {
-        const Segment sg = first_segment(u, u_stop, kblocks);
-        const uint32_t buf = seg & 1u;
-        const uint32_t use = (seg >> 1) & 1u;
+      for (int i = 0; i < run.count && ok; ++i) {
+        const Segment sg = run_segment(run, i);
+        const uint32_t buf = static_cast<uint32_t>(i) & 1u;
+        const uint32_t use = (static_cast<uint32_t>(i) >> 1) & 1u;
         ok = mbar_wait<false>(bar_tmem_empty + 8 * buf, use ^ 1u, abort_flag, p.status, kSiteMmaTmemEmpty);
         if (!ok) break;
         tc_fence_after_sync();
@@ -169,6 +215,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           ok = mbar_wait<false>(bar_full + 8 * stage, phase, abort_flag, p.status, kSiteMmaFull);
           if (!ok) break;
+          if (i == 0 && kb == sg.kb0) SK_TRACE(2);
           tc_fence_after_sync();
           const uint64_t a_desc = smem_desc_k_sw128(smem_a + stage * G::kBytesA);
           const uint64_t b_desc = smem_desc_k_sw128(smem_b + stage * bytes_b);
@@ -184,30 +231,25 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
         if (!ok) break;
         tc_commit(bar_tmem_full + 8 * buf);
-        u += sg.kb1 - sg.kb0;
-        ++seg;
       }
+      SK_TRACE(3);
     }
   } else {
     // ---------------------------------- epilogue ---------------------------------
     const int quarter = warp & 3;
     const int lane_row = quarter * 32 + lane;  // row of the 128-row W tile = TMEM lane
-    const long long first_tile_here = u_begin / kblocks;
-    uint32_t seg = 0;
+    const size_t slot_floats = static_cast<size_t>(tokens_pad) * G::kRowsW;
     bool ok = true;
-    long long u = u_begin;
-    while (u < u_stop && ok) {
-      const Segment sg = first_segment(u, u_stop, kblocks);
-      const uint32_t buf = seg & 1u;
-      const uint32_t use = (seg >> 1) & 1u;
+    for (int i = 0; i < run.count && ok; ++i) {
+      const Segment sg = run_segment(run, i);
+      const uint32_t buf = static_cast<uint32_t>(i) & 1u;
+      const uint32_t use = (static_cast<uint32_t>(i) >> 1) & 1u;
       const int n = sg.tile * G::kRowsW + lane_row;  // output column
       const bool full_k = sg.kb0 == 0 && sg.kb1 == kblocks;
       const bool n_ok = n < p.N;
       const float ws = n_ok ? __ldg(p.w_scale + n) : 0.0f;
       const float bias = (n_ok && p.bias != nullptr) ? __bfloat162float(p.bias[n]) : 0.0f;
-      float* slot = p.partials +
-                    (static_cast<size_t>(blockIdx.x) * segs_per_cta + (sg.tile - first_tile_here)) *
-                        (static_cast<size_t>(tokens_pad) * G::kRowsW);
+      float* slot = p.partials + (static_cast<size_t>(blockIdx.x) * segs_per_cta + sg.slot) * slot_floats;
 
       ok = mbar_wait<false>(bar_tmem_full + 8 * buf, use, abort_flag, p.status, kSiteEpiTmemFull);
       ok = __all_sync(0xffffffffu, ok) != 0;
@@ -254,29 +296,38 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         seen = __shfl_sync(0xffffffffu, seen, 0);
         if (seen == parts - 1u) {
           __threadfence();
-          if (n_ok) {
-#pragma unroll 4
-            for (int m = 0; m < p.M; ++m) {
-              float sum = 0.0f;
-              for (int cta = cta_first; cta <= cta_last; ++cta) {
-                const long long their_first = static_cast<long long>(cta) * units_per_cta / kblocks;
-                const float* src = p.partials +
-                                   (static_cast<size_t>(cta) * segs_per_cta + (sg.tile - their_first)) *
-                                       (static_cast<size_t>(tokens_pad) * G::kRowsW) +
-                                   static_cast<size_t>(m) * G::kRowsW + lane_row;
-                sum += __ldcg(src);
+          // Eight tokens at a time, so that eight independent loads per part are in flight; the
+          // parts of one element are still added in ascending CTA order.
+          for (int m0 = 0; m0 < p.M; m0 += 8) {
+            float sum[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) sum[j] = 0.0f;
+            for (int cta = cta_first; cta <= cta_last; ++cta) {
+              const long long their_first = static_cast<long long>(cta) * units_per_cta / kblocks;
+              const float* src = p.partials +
+                                 (static_cast<size_t>(cta) * segs_per_cta + (sg.tile - their_first)) * slot_floats +
+                                 static_cast<size_t>(m0) * G::kRowsW + lane_row;
+              float part[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) part[j] = __ldcg(src + j * G::kRowsW);  // rows >= M: unused padding
+#pragma unroll
+              for (int j = 0; j < 8; ++j) sum[j] += part[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int m = m0 + j;
+              if (m < p.M && n_ok) {
+                const float v = sum[j] * (__ldg(p.x_scale + m) * ws) + bias;
+                p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16_rn(v);
               }
-              const float v = sum * (__ldg(p.x_scale + m) * ws) + bias;
-              p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16_rn(v);
             }
           }
           __syncwarp();
           if (lane == 0) p.counters[sg.tile * 4 + quarter] = 0u;  // leave the workspace zero
         }
       }
-      u += sg.kb1 - sg.kb0;
-      ++seg;
     }
+    if (quarter == 0 && lane == 0) SK_TRACE(4);
   }
 
   // ------------------------------------ common exit ------------------------------------
@@ -287,6 +338,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   if (warp == 1) {
     tmem_dealloc<1>(tmem_base, 256);
   }
+  if (threadIdx.x == 32) SK_TRACE(5);
 }
 
 }  // namespace

@@ -45,6 +45,9 @@ struct TcParams {
   int use_tma_store;   // 0: plain predicated stores
   int group_m;         // tile-rasterisation group height (tiles)
   uint32_t* status;    // device status word
+#ifdef B200FP8_DEBUG_KNOBS
+  int debug;
+#endif
 };
 
 template <int kCtaGroup>
@@ -93,6 +96,9 @@ struct SkinnyParams {
   float* partials;     // [num_ctas * segs_per_cta][tokens_pad][128] fp32
   uint32_t* counters;  // [tiles * 4], zero on entry, zero again on exit
   uint32_t* status;
+#ifdef B200FP8_DEBUG_KNOBS
+  unsigned long long* trace;
+#endif
 };
 
 cudaError_t launch_gemm_skinny(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const SkinnyParams& p,
