@@ -81,6 +81,17 @@ def test_gemm_oracle_matches_golden_outputs_bit_for_bit(golden_dir):
         assert torch.equal(y, _bf16(d["y_bf16"]))
 
 
+def test_cast_decode_equals_table_decode():
+    allb = torch.arange(256, dtype=torch.uint8).repeat(4, 1)
+    ones = torch.ones(4)
+    a = orc.gemm_rowwise(allb[:, :127], allb[:, :127], ones, ones, keep_fp32=True, decode="table")
+    b = orc.gemm_rowwise(allb[:, :127], allb[:, :127], ones, ones, keep_fp32=True, decode="cast")
+    assert torch.equal(a, b)
+    t = orc.decode_e4m3(allb[0])
+    c = allb[0].view(torch.float8_e4m3fn).to(torch.float32)
+    assert torch.equal(torch.nan_to_num(t, nan=-1.0), torch.nan_to_num(c, nan=-1.0))
+
+
 def test_c_gemm_oracle_within_tolerance_of_golden(golden_dir):
     # the C oracle adds in ascending k, torch's matmul in blocks: equal up to fp32 summation order
     d = _load(golden_dir, "config1_seed0_128x256x512.npz")
