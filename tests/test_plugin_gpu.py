@@ -1,0 +1,44 @@
+"""The operator boundary on a B200: our backend next to the baseline column, accuracy = 1."""
+import os
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+METRICS = "latency,tflops,gbps,speedup,accuracy"
+
+
+def test_standalone_operator_on_gpu(cuda_device):
+    from tritonbench_b200 import operator as standalone
+
+    standalone._attach_default_backends()
+    for shape in (["--m", "512", "--n", "1024", "--k", "1024"], ["--m", "16", "--n", "4096", "--k", "2048", "--bias"]):
+        args, extra = standalone.get_parser().parse_known_args(
+            ["--device", "cuda", "--metrics", METRICS, "--only", "torch_dequant_ref,b200_native,scaled_mm", "--iter", "20"] + shape
+        )
+        res = standalone.Operator(args, extra).run(args.warmup, args.iter)
+        _, cells = res.rows[0]
+        assert cells["b200_native"]["accuracy"] is True, cells
+        assert cells["b200_native"]["latency"] > 0 and cells["b200_native"]["tflops"] > 0
+        assert "b200-accuracy" in res.headers() and "b200-speedup" in res.headers()
+
+
+def test_plugin_through_the_reference_harness_on_gpu(cuda_device):
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "tritonbench")):
+        pytest.skip("no installed copy of the tritonbench package on this machine")
+    sys.path.insert(0, ref)
+    from tritonbench_b200 import tritonbench_plugin as plug
+
+    out = plug.run(
+        ["--op", plug.OP_NAME, "--device", "cuda", "--metrics", METRICS, "--only", "torch_dequant_ref,b200_native",
+         "--m", "1024", "--n", "2048", "--k", "1024"]
+    )
+    text = str(out)
+    assert "b200-tflops" in text and "b200-accuracy" in text, text
+    x_val, cells = out.result[0][0], out.result[0][1]
+    assert tuple(x_val) == (1024, 2048, 1024)
+    assert cells["b200_native"].accuracy is True
+    assert cells["b200_native"].latency is not None
