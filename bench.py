@@ -198,6 +198,28 @@ def run_reference(args, workload):
     print(json.dumps(line), flush=True)
 
 
+def time_e2e(ops, m, n, k, x_pair, wq, ws, e2e_steps, barrier, grouped, device, world, flops_step_rank):
+    """Wall-clock over e2e_steps synchronous host-buffer calls (each: H2D copies, kernel, D2H copy)."""
+    import torch.distributed as td
+
+    host = ops.HostGemm(m, n, k)
+    h_in = [t.cpu().contiguous().pin_memory() for t in (x_pair[0].view(torch.uint8), wq.view(torch.uint8), x_pair[1], ws)]
+    h_out = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):
+        host(*h_in, out=h_out)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        host(*h_in, out=h_out)
+    t_e2e = time.perf_counter() - t0
+    host.close()
+    if grouped:
+        t = torch.tensor([t_e2e], dtype=torch.float64, device=device)
+        td.all_reduce(t, op=td.ReduceOp.MAX)
+        t_e2e = float(t.item())
+    return t_e2e, world * flops_step_rank * e2e_steps / t_e2e / 1e12
+
+
 def run_own(args, workload):
     import torch.distributed as td
 
@@ -264,23 +286,10 @@ def run_own(args, workload):
     value = world * flops_step_rank / (ms_per_step * 1e-3) / 1e12
 
     # ---- end to end through the host-buffer C-ABI entry point ----
-    e2e_steps = min(steps, 10)
-    host = ops.HostGemm(m, n, k)
-    h_in = [t.cpu().contiguous().pin_memory() for t in (xs_list[0][0].view(torch.uint8), wq.view(torch.uint8), xs_list[0][1], ws)]
-    h_out = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
-    for _ in range(2):
-        host(*h_in, out=h_out)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        host(*h_in, out=h_out)
-    t_e2e = time.perf_counter() - t0
-    host.close()
-    if grouped:
-        t = torch.tensor([t_e2e], dtype=torch.float64, device=device)
-        td.all_reduce(t, op=td.ReduceOp.MAX)
-        t_e2e = float(t.item())
-    e2e_value = world * flops_step_rank * e2e_steps / t_e2e / 1e12
+    e2e_steps = 0 if args.kernel_only else min(steps, 10)
+    t_e2e, e2e_value = None, None
+    if e2e_steps:
+        t_e2e, e2e_value = time_e2e(ops, m, n, k, xs_list[0], wq, ws, e2e_steps, barrier, grouped, device, world, flops_step_rank)
     h2d = world * (m * k + n * k + 4 * (m + n))
     d2h = world * 2 * m * n
 
@@ -327,7 +336,7 @@ def run_own(args, workload):
         roofline["algorithmic_bytes_per_launch"] = alg_bytes
 
         cpu = None
-        if world == 1:
+        if world == 1 and not args.kernel_only:
             xq_h, xs_h = xs_list[0][0].cpu(), xs_list[0][1].cpu()
             rate, threads, sample, _ = cpu_oracle_rate(xq_h, wq.cpu(), xs_h, ws.cpu(), target_seconds=12.0)
             cpu = {"value": rate, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
@@ -358,7 +367,7 @@ def run_own(args, workload):
             },
             "roofline": roofline,
             "cpu_baseline": cpu,
-            "e2e": {
+            "e2e": None if not e2e_steps else {
                 "value": e2e_value,
                 "unit": UNIT,
                 "h2d_bytes_per_step": h2d,
@@ -382,11 +391,13 @@ def run_own(args, workload):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="square_8192")
     ap.add_argument("--gather", action="store_true", help="N>1: also time GEMM + in-place NCCL all-gather of Y")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU-baseline legs (for short profiler captures; not a bench run)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args, args.workload)
