@@ -82,6 +82,32 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
                          void* cuda_stream);
 
 /*
+ * The same GEMM for M <= 128 WITHOUT any caller-provided workspace and without a single allocation.
+ * (No counterpart in the reference: FBGEMM's wrappers allocate their output and temporaries per call.)
+ *
+ * For whom: a host that has handed all device memory to its own arena and lets no library call
+ * cudaMalloc (an inference server that sizes its KV cache to the last free byte, a runtime that
+ * forbids allocation once serving has started), and therefore cannot size and pass a workspace
+ * either.  The kernel is the stream-K decode kernel; its scratch (status word, arrival counters,
+ * fp32 partial sums) lives in a fixed 8 MiB array in device global memory that belongs to the
+ * loaded library: every GPU that loads the library holds those 8 MiB until the process exits.
+ *
+ *   - M > 128, or a shape whose partial sums need more than the 8 MiB, returns B200FP8_TOO_LARGE
+ *     (it fits, for example, M <= 16 with N up to 65536, and M = 32 with N = 28672, K = 8192);
+ *   - calls no cudaMalloc / cudaFree and no allocating library routine; it enqueues one small
+ *     cudaMemsetAsync (status word + the counters this call uses) and the kernel on `cuda_stream`;
+ *   - the FIRST call on each device looks up the array's device address (cudaGetSymbolAddress) and
+ *     raises the kernel's shared-memory limit: make that first call before any stream capture;
+ *   - all calls share the one array: two calls that overlap on the GPU (different streams, or
+ *     concurrent graphs) race on it.  Order them on one stream or with events.
+ * b200fp8_noalloc_status reads the status word of the array after the caller synchronised.
+ */
+int b200fp8_gemm_rowwise_noalloc(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
+                                 const void* bias_bf16, void* y_bf16, int64_t M, int64_t N, int64_t K, int64_t ldx,
+                                 int64_t ldw, int64_t ldy, void* cuda_stream);
+int b200fp8_noalloc_status(uint32_t* device_status);
+
+/*
  * Read the device status word of a workspace.  Call after the stream has been synchronised.
  * Returns B200FP8_OK or B200FP8_DEVICE_TIMEOUT; *device_status receives the raw word
  * (code << 24 | site).  Replaces: the reference's exit-on-error helper macros

@@ -294,6 +294,49 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
   return note_cuda(launch_gemm_tc<1>(tm_x, tm_w, tm_y, tp, pl.num_ctas, stream));
 }
 
+int b200fp8_gemm_rowwise_noalloc(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
+                                 const void* bias_bf16, void* y_bf16, int64_t M, int64_t N, int64_t K, int64_t ldx,
+                                 int64_t ldw, int64_t ldy, void* cuda_stream) {
+  if (xq == nullptr || wq == nullptr || x_scale == nullptr || w_scale == nullptr || y_bf16 == nullptr) {
+    return B200FP8_BAD_ARG;
+  }
+  int st = check_sizes(M, N, K);
+  if (st != B200FP8_OK) return st;
+  if (ldx < K || ldw < K || ldy < N) return B200FP8_BAD_ARG;
+  if (M > SkinnyGeometry::kMaxTokens) return B200FP8_TOO_LARGE;
+  DeviceInfo dev;
+  st = device_info(&dev);
+  if (st != B200FP8_OK) return st;
+  if (dev.cc_major != 10) return B200FP8_UNSUPPORTED_ARCH;
+  if (!tma_loadable(K, ldx, ldw, xq, wq)) return B200FP8_UNSUPPORTED_ALIGNMENT;
+  Plan pl;
+  st = make_plan(M, N, K, B200FP8_VARIANT_SKINNY, true, true, dev, &pl);
+  if (st != B200FP8_OK) return st;
+  if (pl.workspace_bytes > kStaticScratchBytes) return B200FP8_TOO_LARGE;  // partial sums would not fit
+
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  cudaError_t e = skinny_static_scratch(&scratch, &scratch_bytes);  // first call on a device: symbol look-up
+  if (e != cudaSuccess) return note_cuda(e);
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  // The array keeps whatever the last call left.  What must start at zero is the status word and
+  // the arrival counters of the tiles this call uses; the partial-sum slots are written before read.
+  const size_t clear_bytes =
+      B200FP8_WORKSPACE_HEADER_BYTES + static_cast<size_t>(pl.skinny.tiles) * 4 * sizeof(uint32_t);
+  e = cudaMemsetAsync(scratch, 0, clear_bytes, stream);
+  if (e != cudaSuccess) return note_cuda(e);
+  return b200fp8_gemm_rowwise(xq, wq, x_scale, w_scale, bias_bf16, y_bf16, M, N, K, ldx, ldw, ldy, scratch,
+                              scratch_bytes, B200FP8_VARIANT_SKINNY, cuda_stream);
+}
+
+int b200fp8_noalloc_status(uint32_t* device_status) {
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  const cudaError_t e = skinny_static_scratch(&scratch, &scratch_bytes);
+  if (e != cudaSuccess) return note_cuda(e);
+  return b200fp8_query_status(scratch, device_status);
+}
+
 int b200fp8_query_status(const void* workspace, uint32_t* device_status) {
   if (workspace == nullptr) return B200FP8_BAD_ARG;
   uint32_t word = 0;

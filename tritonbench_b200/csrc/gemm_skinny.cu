@@ -343,6 +343,27 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
 }  // namespace
 
+// Scratch of the no-allocation entry point.  In host code this name is only a handle for the
+// runtime: its device address comes from cudaGetSymbolAddress, once per device, below.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+cudaError_t skinny_static_scratch(void** device_ptr, size_t* bytes) {
+  static void* address_on_device[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (address_on_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess) return err;
+    address_on_device[dev] = ptr;
+  }
+  *device_ptr = address_on_device[dev];
+  *bytes = kStaticScratchBytes;
+  return cudaSuccess;
+}
+
 cudaError_t launch_gemm_skinny(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const SkinnyParams& p,
                                const SkinnyPlan& plan, cudaStream_t stream) {
   static size_t configured_bytes[64] = {};

@@ -104,6 +104,12 @@ struct SkinnyParams {
 cudaError_t launch_gemm_skinny(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const SkinnyParams& p,
                                const SkinnyPlan& plan, cudaStream_t stream);
 
+// Library-owned scratch for the entry point that allocates nothing: a fixed-size array in device
+// global memory that is part of the loaded module.  Returns its device address for the CURRENT
+// device (looked up once per device) and its size.
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB per GPU that loads the library
+cudaError_t skinny_static_scratch(void** device_ptr, size_t* bytes);
+
 // ------------------------------ CUDA-core kernel (gemm_simt.cu) -----------------------------
 struct SimtParams {
   const uint8_t* xq;

@@ -47,6 +47,8 @@ EXPORTED_SYMBOLS = (
     "b200fp8_host_ctx_create",
     "b200fp8_host_ctx_destroy",
     "b200fp8_gemm_rowwise_host",
+    "b200fp8_gemm_rowwise_noalloc",
+    "b200fp8_noalloc_status",
 )
 
 _lib: Optional[ctypes.CDLL] = None
@@ -96,6 +98,10 @@ def load() -> ctypes.CDLL:
     lib.b200fp8_host_ctx_destroy.argtypes = [c_void_p]
     lib.b200fp8_gemm_rowwise_host.restype = ctypes.c_int
     lib.b200fp8_gemm_rowwise_host.argtypes = [c_void_p] * 7
+    lib.b200fp8_gemm_rowwise_noalloc.restype = ctypes.c_int
+    lib.b200fp8_gemm_rowwise_noalloc.argtypes = [c_void_p] * 6 + [c_int64] * 6 + [c_void_p]
+    lib.b200fp8_noalloc_status.restype = ctypes.c_int
+    lib.b200fp8_noalloc_status.argtypes = [ctypes.POINTER(c_uint32)]
     if lib.b200fp8_abi_version() != 1:
         raise RuntimeError("libb200fp8.so has an ABI version this binding does not know")
     _lib = lib
