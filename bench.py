@@ -135,6 +135,11 @@ def cpu_oracle_rate(xq, wq, xs, ws, target_seconds: float, steps: int = 1, warmu
     target_seconds.  Returns (TFLOP/s, threads, sample description, seconds per step)."""
     from oracle import fp8_rowwise_oracle as orc
 
+    # all the host threads this process may use (torchrun exports OMP_NUM_THREADS=1 to its ranks)
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+    except (AttributeError, RuntimeError):
+        pass
     m, k = xq.shape
     n = wq.shape[0]
 
