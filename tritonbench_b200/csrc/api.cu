@@ -249,6 +249,9 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
     kp.bias = bias;
     kp.y = y;
     kp.M = static_cast<int>(M);
+#ifdef B200FP8_DEBUG_KNOBS
+    if (getenv("B200FP8_EPI_M")) kp.M = atoi(getenv("B200FP8_EPI_M"));  // experiment: epilogue sees fewer tokens
+#endif
     kp.N = static_cast<int>(N);
     kp.K = static_cast<int>(K);
     kp.ldy = ldy;
@@ -370,9 +373,9 @@ int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char*
     case B200FP8_VARIANT_SKINNY:
       snprintf(buf, n,
                "skinny swap-AB stream-K tile=128(W rows)x%d(tokens)x128 stages=%d ctas=%d units_per_cta=%d "
-               "segs_per_cta=%d smem=%zu workspace=%zu",
+               "whole_tiles_per_cta=%d k_split_tiles=%d smem=%zu workspace=%zu",
                pl.skinny.tokens_pad, pl.skinny.stages, pl.skinny.num_ctas, pl.skinny.units_per_cta,
-               pl.skinny.segs_per_cta, pl.skinny.smem_bytes, pl.workspace_bytes);
+               pl.skinny.dp_waves, pl.skinny.sk_tiles, pl.skinny.smem_bytes, pl.workspace_bytes);
       break;
     default:
       snprintf(buf, n, "simt tile=64x64x32 workspace=%zu", pl.workspace_bytes);

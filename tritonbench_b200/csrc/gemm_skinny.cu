@@ -4,15 +4,22 @@
 //   * swap-AB: a tile is 128 rows of W (the MMA M side, one TMEM lane each) against all tokens
 //     (MMA N = M rounded up to 16), so the tensor core consumes W at the rate TMA delivers it and
 //     CUDA cores never touch the operands;
-//   * stream-K: the (tile, k-block) space is cut into equal runs of consecutive units, one run per
-//     CTA, so every SM streams the same number of W bytes whatever N/128 is relative to the SM count;
+//   * stream-K: the (tile, k-block) space is cut into equal runs of consecutive
+//     units, one run per CTA, so every SM streams the same number of W bytes whatever N/128 is
+//     relative to the SM count;
 //   * a tile whose K range is split over several CTAs is finished by whichever CTA arrives last:
 //     each writes its fp32 partial sums to a slot in the workspace, bumps a per-(tile, lane quarter)
 //     counter, and the last one adds the slots in ascending CTA order (a fixed order, so the result
 //     does not depend on who is last), applies the scales and writes bf16.  No CTA waits for another.
 //
-// Warp roles are those of the large-M kernel: warp 0 TMA producer, warp 1 TMEM owner + MMA issuer,
-// warps 2-5 epilogue.  All mbarrier waits are bounded.
+// Warp roles: warp 0 TMA producer, warp 1 TMEM owner + MMA issuer, warps 2-5 drain the accumulators
+// (to Y for a whole tile, to a partial-sum slot for a split one), warps 6-9 do the cross-CTA
+// additions ("fix-ups") that the draining warps hand them through a small mailbox in shared memory,
+// so that a fix-up - a chain of dependent global-memory round trips - never keeps an accumulator
+// from being drained.  Split segments are processed first, so fix-ups happen while W still streams.
+// All waits are bounded.
+#include <stdlib.h>
+
 #include "kernels.h"
 #include "ptx.cuh"
 
@@ -28,12 +35,20 @@ SkinnyPlan make_skinny_plan(int M, int N, int K, int sm_count) {
   if (pl.stages > G::kMaxStages) pl.stages = G::kMaxStages;
   pl.tiles = (N + G::kRowsW - 1) / G::kRowsW;
   pl.kblocks = (K + G::kBlockK - 1) / G::kBlockK;
-  const long long total = static_cast<long long>(pl.tiles) * pl.kblocks;
-  long long per = (total + sm_count - 1) / sm_count;
+
+#ifdef B200FP8_DEBUG_KNOBS
+  if (getenv("B200FP8_SKINNY_STAGES")) pl.stages = atoi(getenv("B200FP8_SKINNY_STAGES"));
+#endif
+  // Whole waves of tiles are dealt out one tile per CTA (nothing to add across CTAs); only the
+  // remainder, fewer tiles than CTAs, is cut along K into equal runs.  All of it when tiles < CTAs.
+  pl.dp_waves = pl.tiles / sm_count;
+  pl.sk_tiles = pl.tiles - pl.dp_waves * sm_count;
+  const long long sk_units = static_cast<long long>(pl.sk_tiles) * pl.kblocks;
+  long long per = (sk_units + sm_count - 1) / sm_count;
   const long long floor_units = pl.kblocks < 4 ? pl.kblocks : 4;  // do not cut K finer than 512 bytes
   if (per < floor_units) per = floor_units;
   pl.units_per_cta = static_cast<int>(per);
-  pl.num_ctas = static_cast<int>((total + per - 1) / per);
+  pl.num_ctas = pl.dp_waves > 0 ? sm_count : static_cast<int>((sk_units + per - 1) / per);
   pl.segs_per_cta = (pl.units_per_cta + pl.kblocks - 1) / pl.kblocks + 1;
   pl.smem_bytes = static_cast<size_t>(pl.stages) * stage_bytes + G::kBarBytes + 1024;
   pl.partial_bytes =
@@ -49,11 +64,16 @@ enum WaitSite : uint32_t {
   kSiteMmaTmemEmpty = 0x202,
   kSiteMmaFull = 0x203,
   kSiteEpiTmemFull = 0x204,
+  kSiteMailEmpty = 0x205,
+  kSiteMailFull = 0x206,
 };
+
+constexpr int kMailDepth = 4;      // fix-up requests in flight per lane quarter
+constexpr int kMailDone = -1;      // "no more requests" marker
 
 struct Segment {
   int tile;
-  int slot;  // index of the segment inside this CTA's run (selects the partial-sum slot)
+  int slot;  // partial-sum slot (global index)
   int kb0;
   int kb1;
 };
@@ -61,8 +81,7 @@ struct Segment {
 // One CTA's run of consecutive units [u_begin, u_stop) cut at tile boundaries.  Segments that
 // cover only part of a tile's K range are processed FIRST (the one at the end of the run, then
 // the one at its start), the whole tiles after them: the cross-CTA fix-up of a split tile then
-// happens early, hidden behind the streaming of the remaining tiles, instead of at the very end
-// of the kernel where nothing overlaps it.
+// happens early, hidden behind the streaming of the remaining tiles.
 struct Run {
   long long u_begin;
   long long u_stop;
@@ -85,8 +104,8 @@ __device__ __forceinline__ Run make_run(long long u_begin, long long u_stop, int
   return r;
 }
 
-// i-th segment in processing order
-__device__ __forceinline__ Segment run_segment(const Run& r, int i) {
+// i-th segment of the run in processing order; `slot_base` is this CTA's first partial-sum slot
+__device__ __forceinline__ Segment run_segment(const Run& r, int i, int slot_base) {
   int j;  // position in the run
   int pos = 0;
   if (r.tail_first && i == 0) {
@@ -101,7 +120,7 @@ __device__ __forceinline__ Segment run_segment(const Run& r, int i) {
     }
   }
   Segment s;
-  s.slot = j;
+  s.slot = slot_base + j;
   s.tile = r.first_tile + j;
   const long long tile_u0 = static_cast<long long>(s.tile) * r.kblocks;
   s.kb0 = r.u_begin > tile_u0 ? static_cast<int>(r.u_begin - tile_u0) : 0;
@@ -111,8 +130,7 @@ __device__ __forceinline__ Segment run_segment(const Run& r, int i) {
 
 __global__ void __launch_bounds__(SkinnyGeometry::kThreads, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                   const SkinnyParams p, const int tokens_pad, const int stages, const int kblocks,
-                   const int units_per_cta, const int segs_per_cta, const long long total_units) {
+                   const SkinnyParams p, const SkinnyShape sh) {
   using G = SkinnyGeometry;
 
 #ifdef B200FP8_DEBUG_KNOBS
@@ -126,25 +144,46 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   uint8_t* base_ptr = smem_raw + (base - raw_addr);
   if (threadIdx.x == 0) SK_TRACE(0);
 
-  const int bytes_b = tokens_pad * G::kBlockK;
+  const int stages = sh.stages;
+  const int kblocks = sh.kblocks;
+  const int bytes_b = sh.tokens_pad * G::kBlockK;
   const uint32_t smem_a = base;
   const uint32_t smem_b = smem_a + stages * G::kBytesA;
   const uint32_t bars = smem_b + stages * bytes_b;
-  const uint32_t bar_full = bars;                       // [stages]
-  const uint32_t bar_empty = bars + 8 * stages;         // [stages]
-  const uint32_t bar_tmem_full = bars + 16 * stages;    // [2]
-  const uint32_t bar_tmem_empty = bar_tmem_full + 16;   // [2]
-  const uint32_t tmem_slot = bar_tmem_empty + 16;
+  const uint32_t bar_full = bars;                                   // [stages]
+  const uint32_t bar_empty = bars + 8 * stages;                     // [stages]
+  const uint32_t bar_tmem_full = bars + 16 * stages;                // [2]
+  const uint32_t bar_tmem_empty = bar_tmem_full + 16;               // [2]
+  const uint32_t bar_mail_full = bar_tmem_empty + 16;               // [4 quarters][kMailDepth]
+  const uint32_t bar_mail_empty = bar_mail_full + 8 * 4 * kMailDepth;  // [4 quarters][kMailDepth]
+  const uint32_t tmem_slot = bar_mail_empty + 8 * 4 * kMailDepth;
   uint8_t* tail_ptr = base_ptr + (tmem_slot - base);
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(tail_ptr);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tail_ptr + 4);
+  volatile int* mail_tile = reinterpret_cast<volatile int*>(tail_ptr + 8);  // [4 quarters][kMailDepth]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const long long u_begin = static_cast<long long>(blockIdx.x) * units_per_cta;
-  const long long u_stop = u_begin + units_per_cta < total_units ? u_begin + units_per_cta : total_units;
+  const int slot_base = static_cast<int>(blockIdx.x) * sh.segs_per_cta;
+  // this CTA's work: a run of the K-split region first, then its whole tiles
+  long long u_begin = static_cast<long long>(blockIdx.x) * sh.units_per_cta;
+  if (u_begin > sh.sk_units) u_begin = sh.sk_units;
+  const long long u_stop = u_begin + sh.units_per_cta < sh.sk_units ? u_begin + sh.units_per_cta : sh.sk_units;
   const Run run = make_run(u_begin, u_stop, kblocks);
+  const int first_whole = sh.sk_tiles + static_cast<int>(blockIdx.x);
+  const int whole_count = first_whole < sh.tiles ? (sh.tiles - first_whole + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x) : 0;
+  const int seg_count = run.count + whole_count;
+  auto segment_at = [&](int i) {
+    if (i < run.count) return run_segment(run, i, slot_base);
+    Segment s;
+    s.tile = first_whole + (i - run.count) * static_cast<int>(gridDim.x);
+    s.slot = 0;
+    s.kb0 = 0;
+    s.kb1 = kblocks;
+    return s;
+  };
+  const size_t slot_floats = static_cast<size_t>(sh.tokens_pad) * G::kRowsW;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -155,15 +194,20 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       mbar_init(bar_tmem_full + 8 * b, 1);
       mbar_init(bar_tmem_empty + 8 * b, 4);
     }
+    for (int s = 0; s < 4 * kMailDepth; ++s) {
+      mbar_init(bar_mail_full + 8 * s, 1);
+      mbar_init(bar_mail_empty + 8 * s, 1);
+    }
     *abort_flag = 0u;
     fence_mbar_init();
-  }
-  if (warp == 0 && lane == 0) {
     prefetch_tensormap(&tm_w);
     prefetch_tensormap(&tm_x);
   }
+  // two accumulators of tokens_pad columns; the allocation is a power of two of at least 32
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < 2u * static_cast<uint32_t>(sh.tokens_pad)) tmem_cols <<= 1;
   if (warp == 1) {
-    tmem_alloc<1>(tmem_slot, 256);
+    tmem_alloc<1>(tmem_slot, tmem_cols);
     tmem_relinquish<1>();
   }
   tc_fence_before_sync();
@@ -178,8 +222,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       const uint32_t tx_bytes = static_cast<uint32_t>(G::kBytesA + bytes_b);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int i = 0; i < run.count && ok; ++i) {
-        const Segment sg = run_segment(run, i);
+      for (int i = 0; i < seg_count && ok; ++i) {
+        const Segment sg = segment_at(i);
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           ok = mbar_wait<false>(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty);
           if (!ok) break;
@@ -201,17 +245,17 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   } else if (warp == 1) {
     // -------------------------------- MMA issuer --------------------------------
     if (lane == 0) {
-      const uint32_t idesc = instr_desc_e4m3(G::kRowsW, static_cast<uint32_t>(tokens_pad));
+      const uint32_t idesc = instr_desc_e4m3(G::kRowsW, static_cast<uint32_t>(sh.tokens_pad));
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int i = 0; i < run.count && ok; ++i) {
-        const Segment sg = run_segment(run, i);
+      for (int i = 0; i < seg_count && ok; ++i) {
+        const Segment sg = segment_at(i);
         const uint32_t buf = static_cast<uint32_t>(i) & 1u;
         const uint32_t use = (static_cast<uint32_t>(i) >> 1) & 1u;
         ok = mbar_wait<false>(bar_tmem_empty + 8 * buf, use ^ 1u, abort_flag, p.status, kSiteMmaTmemEmpty);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * G::kMaxTokens;
+        const uint32_t d_tmem = tmem_base + buf * static_cast<uint32_t>(sh.tokens_pad);
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           ok = mbar_wait<false>(bar_full + 8 * stage, phase, abort_flag, p.status, kSiteMmaFull);
           if (!ok) break;
@@ -234,14 +278,31 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       }
       SK_TRACE(3);
     }
-  } else {
-    // ---------------------------------- epilogue ---------------------------------
+  } else if (warp < 6) {
+    // ------------------------- drain: TMEM -> Y or partial-sum slot -------------------------
     const int quarter = warp & 3;
     const int lane_row = quarter * 32 + lane;  // row of the 128-row W tile = TMEM lane
-    const size_t slot_floats = static_cast<size_t>(tokens_pad) * G::kRowsW;
+    uint32_t mail_no = 0;
     bool ok = true;
-    for (int i = 0; i < run.count && ok; ++i) {
-      const Segment sg = run_segment(run, i);
+    // hand one tile (or the end marker) to this quarter's fix-up warp
+    auto post = [&](int tile) {
+      const uint32_t ring = mail_no % kMailDepth;
+      const uint32_t use = (mail_no / kMailDepth) & 1u;
+      ++mail_no;
+      const uint32_t idx = quarter * kMailDepth + ring;
+      bool free_slot = true;
+      if (lane == 0) {
+        free_slot = mbar_wait<false>(bar_mail_empty + 8 * idx, use ^ 1u, abort_flag, p.status, kSiteMailEmpty);
+        if (free_slot) {
+          mail_tile[idx] = tile;
+          mbar_arrive(bar_mail_full + 8 * idx);  // release: the entry is visible to the waiter
+        }
+      }
+      return __all_sync(0xffffffffu, free_slot) != 0;
+    };
+
+    for (int i = 0; i < seg_count && ok; ++i) {
+      const Segment sg = segment_at(i);
       const uint32_t buf = static_cast<uint32_t>(i) & 1u;
       const uint32_t use = (static_cast<uint32_t>(i) >> 1) & 1u;
       const int n = sg.tile * G::kRowsW + lane_row;  // output column
@@ -249,15 +310,16 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       const bool n_ok = n < p.N;
       const float ws = n_ok ? __ldg(p.w_scale + n) : 0.0f;
       const float bias = (n_ok && p.bias != nullptr) ? __bfloat162float(p.bias[n]) : 0.0f;
-      float* slot = p.partials + (static_cast<size_t>(blockIdx.x) * segs_per_cta + sg.slot) * slot_floats;
+      float* slot = p.partials + static_cast<size_t>(sg.slot) * slot_floats;
 
       ok = mbar_wait<false>(bar_tmem_full + 8 * buf, use, abort_flag, p.status, kSiteEpiTmemFull);
       ok = __all_sync(0xffffffffu, ok) != 0;
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * G::kMaxTokens;
+      const uint32_t t_addr =
+          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * static_cast<uint32_t>(sh.tokens_pad);
 
-      for (int c = 0; c < tokens_pad; c += 16) {
+      for (int c = 0; c < sh.tokens_pad; c += 16) {
         uint32_t acc[16];
         tmem_ld_32x16(t_addr + c, acc);
         tmem_ld_wait();
@@ -282,52 +344,85 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tmem_empty + 8 * buf);
+      if (full_k) continue;
 
-      if (!full_k) {
-        // publish this warp's part of the slot, then see whether every other part is already there
-        const long long tile_u0 = static_cast<long long>(sg.tile) * kblocks;
-        const int cta_first = static_cast<int>(tile_u0 / units_per_cta);
-        const int cta_last = static_cast<int>((tile_u0 + kblocks - 1) / units_per_cta);
-        const uint32_t parts = static_cast<uint32_t>(cta_last - cta_first + 1);
-        __threadfence();
-        __syncwarp();
-        uint32_t seen = 0;
-        if (lane == 0) seen = atomicAdd(p.counters + sg.tile * 4 + quarter, 1u);
-        seen = __shfl_sync(0xffffffffu, seen, 0);
-        if (seen == parts - 1u) {
-          __threadfence();
-          // Eight tokens at a time, so that eight independent loads per part are in flight; the
-          // parts of one element are still added in ascending CTA order.
-          for (int m0 = 0; m0 < p.M; m0 += 8) {
-            float sum[8];
+      // Publish this warp's part of the slot; if every other part of the tile is already there,
+      // this CTA finishes the tile: its fix-up warp does, this warp goes back to draining.
+      const long long tile_u0 = static_cast<long long>(sg.tile) * kblocks;
+      const int first_part = static_cast<int>(tile_u0 / sh.units_per_cta);
+      const int last_part = static_cast<int>((tile_u0 + kblocks - 1) / sh.units_per_cta);
+      const uint32_t parts = static_cast<uint32_t>(last_part - first_part + 1);
+      __threadfence();
+      __syncwarp();
+      uint32_t seen = 0;
+      if (lane == 0) seen = atomicAdd(p.counters + sg.tile * 4 + quarter, 1u);
+      seen = __shfl_sync(0xffffffffu, seen, 0);
+      if (seen == parts - 1u) ok = post(sg.tile);
+    }
+    post(kMailDone);
+    if (quarter == 0 && lane == 0) SK_TRACE(4);
+  } else {
+    // ------------------- fix-up: add the parts of a split tile, scale, write Y -------------------
+    const int quarter = warp & 3;
+    const int lane_row = quarter * 32 + lane;
+    for (uint32_t mail_no = 0;; ++mail_no) {
+      const uint32_t ring = mail_no % kMailDepth;
+      const uint32_t use = (mail_no / kMailDepth) & 1u;
+      const uint32_t idx = quarter * kMailDepth + ring;
+      bool ok = mbar_wait<false>(bar_mail_full + 8 * idx, use, abort_flag, p.status, kSiteMailFull);
+      ok = __all_sync(0xffffffffu, ok) != 0;
+      if (!ok) break;
+      const int tile = mail_tile[idx];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_mail_empty + 8 * idx);
+      if (tile == kMailDone) break;
+
+      const int n = tile * G::kRowsW + lane_row;
+      const bool n_ok = n < p.N;
+      const float ws = n_ok ? __ldg(p.w_scale + n) : 0.0f;
+      const float bias = (n_ok && p.bias != nullptr) ? __bfloat162float(p.bias[n]) : 0.0f;
+      const long long tile_u0 = static_cast<long long>(tile) * kblocks;
+      const int first_part = static_cast<int>(tile_u0 / sh.units_per_cta);
+      const int last_part = static_cast<int>((tile_u0 + kblocks - 1) / sh.units_per_cta);
+      __threadfence();  // the counter said every part is published; order our reads after that
+      // 16 tokens x up to 4 parts = up to 64 independent loads in flight per thread; the parts of an
+      // element are added in ascending CTA order whatever CTA does the adding.
+      for (int m0 = 0; m0 < p.M; m0 += 16) {
+        float sum[16];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sum[j] = 0.0f;
-            for (int cta = cta_first; cta <= cta_last; ++cta) {
-              const long long their_first = static_cast<long long>(cta) * units_per_cta / kblocks;
-              const float* src = p.partials +
-                                 (static_cast<size_t>(cta) * segs_per_cta + (sg.tile - their_first)) * slot_floats +
-                                 static_cast<size_t>(m0) * G::kRowsW + lane_row;
-              float part[8];
+        for (int j = 0; j < 16; ++j) sum[j] = 0.0f;
+        for (int part0 = first_part; part0 <= last_part; part0 += 4) {
+          float v[4][16];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) part[j] = __ldcg(src + j * G::kRowsW);  // rows >= M: unused padding
+          for (int q = 0; q < 4; ++q) {
+            const int part = part0 + q <= last_part ? part0 + q : last_part;
+            const long long their_first = static_cast<long long>(part) * sh.units_per_cta / kblocks;
+            const size_t their_slot = static_cast<size_t>(part) * sh.segs_per_cta + (tile - their_first);
+            const float* src =
+                p.partials + their_slot * slot_floats + static_cast<size_t>(m0) * G::kRowsW + lane_row;
 #pragma unroll
-              for (int j = 0; j < 8; ++j) sum[j] += part[j];
-            }
+            for (int j = 0; j < 16; ++j) v[q][j] = __ldcg(src + j * G::kRowsW);  // rows >= M: unused padding
+          }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int m = m0 + j;
-              if (m < p.M && n_ok) {
-                const float v = sum[j] * (__ldg(p.x_scale + m) * ws) + bias;
-                p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16_rn(v);
-              }
+          for (int q = 0; q < 4; ++q) {
+            if (part0 + q <= last_part) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) sum[j] += v[q][j];
             }
           }
-          __syncwarp();
-          if (lane == 0) p.counters[sg.tile * 4 + quarter] = 0u;  // leave the workspace zero
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + j;
+          if (m < p.M && n_ok) {
+            const float v = sum[j] * (__ldg(p.x_scale + m) * ws) + bias;
+            p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16_rn(v);
+          }
         }
       }
+      __syncwarp();
+      if (lane == 0) p.counters[tile * 4 + quarter] = 0u;  // leave the workspace zero
     }
-    if (quarter == 0 && lane == 0) SK_TRACE(4);
   }
 
   // ------------------------------------ common exit ------------------------------------
@@ -336,7 +431,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   if (warp == 1) {
-    tmem_dealloc<1>(tmem_base, 256);
+    tmem_dealloc<1>(tmem_base, tmem_cols);
   }
   if (threadIdx.x == 32) SK_TRACE(5);
 }
@@ -376,9 +471,16 @@ cudaError_t launch_gemm_skinny(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
     if (err != cudaSuccess) return err;
     configured_bytes[dev] = SkinnyGeometry::kSmemBudget;
   }
-  const long long total = static_cast<long long>(plan.tiles) * plan.kblocks;
-  gemm_skinny_kernel<<<plan.num_ctas, SkinnyGeometry::kThreads, plan.smem_bytes, stream>>>(
-      tm_w, tm_x, p, plan.tokens_pad, plan.stages, plan.kblocks, plan.units_per_cta, plan.segs_per_cta, total);
+  SkinnyShape sh = {};
+  sh.tokens_pad = plan.tokens_pad;
+  sh.stages = plan.stages;
+  sh.kblocks = plan.kblocks;
+  sh.units_per_cta = plan.units_per_cta;
+  sh.segs_per_cta = plan.segs_per_cta;
+  sh.sk_units = static_cast<long long>(plan.sk_tiles) * plan.kblocks;
+  sh.sk_tiles = plan.sk_tiles;
+  sh.tiles = plan.tiles;
+  gemm_skinny_kernel<<<plan.num_ctas, SkinnyGeometry::kThreads, plan.smem_bytes, stream>>>(tm_w, tm_x, p, sh);
   return cudaGetLastError();
 }
 

@@ -59,9 +59,9 @@ struct SkinnyGeometry {
   static constexpr int kRowsW = 128;   // W rows per tile (MMA M, TMEM lanes)
   static constexpr int kBlockK = 128;  // bytes of K per stage
   static constexpr int kMaxTokens = 128;
-  static constexpr int kThreads = 192;
+  static constexpr int kThreads = 320;  // producer, MMA issuer, 4 drain warps, 4 fix-up warps
   static constexpr int kBytesA = kRowsW * kBlockK;  // 16 KiB of W per stage
-  static constexpr int kBarBytes = 512;
+  static constexpr int kBarBytes = 1024;
   static constexpr int kMaxStages = 12;
   // The arrival counters occupy a region of fixed size right after the workspace header, whatever
   // N is, so that a workspace left zero by one problem size is still zero where the next size
@@ -79,12 +79,22 @@ struct SkinnyPlan {
   int kblocks;       // ceil(K / 128)
   int units_per_cta; // consecutive (tile, k-block) units each CTA owns
   int segs_per_cta;  // upper bound on tile segments per CTA (partial-sum slots)
+  int dp_waves;      // whole tiles per CTA (tiles / CTAs)
+  int sk_tiles;      // remaining tiles, cut along K into equal runs
   size_t smem_bytes;
   size_t partial_bytes;  // fp32 partial sums
   size_t counter_bytes;  // fixed-size region of per (tile, lane quarter) arrival counters
 };
 
 SkinnyPlan make_skinny_plan(int M, int N, int K, int sm_count);
+
+// what the kernel needs of the plan
+struct SkinnyShape {
+  int tokens_pad, stages, kblocks;
+  int units_per_cta, segs_per_cta;
+  long long sk_units;  // units of the K-split region = sk_tiles * kblocks
+  int sk_tiles, tiles;
+};
 
 struct SkinnyParams {
   const float* x_scale;
