@@ -258,9 +258,12 @@ def run_own(args, workload):
     outs = [torch.empty((m, n), dtype=torch.bfloat16, device=device) for _ in range(n_buf)]
     workspace = ops.get_workspace(device, ops.workspace_bytes(m, n, k))
 
+    # decode shapes: successive steps may overlap (each kernel reads only W before its predecessor is done)
+    overlap = m <= 128 and not args.no_overlap
+
     def step(i):
         xq, xs = xs_list[i % n_buf]
-        ops.fp8_gemm_rowwise(xq, wq, xs, ws, out=outs[i % n_buf], workspace=workspace)
+        ops.fp8_gemm_rowwise(xq, wq, xs, ws, out=outs[i % n_buf], workspace=workspace, overlap=overlap)
 
     def barrier():
         torch.cuda.synchronize(device)
@@ -369,6 +372,8 @@ def run_own(args, workload):
                 "inputs": f"X ~ {dist_name}(std {x_std}), W ~ {dist_name}(std {w_std}), rowwise e4m3, fp32 scales; W seed 0, X seed 1+rank",
                 "l2": f"{n_buf} X and Y buffers rotated; per-step working set {alg_bytes / 1e6:.0f} MB (L2 is 126 MB)",
                 "plan": lib.describe_plan(m, n, k),
+                "launch": "programmatic dependent launch: a step may start (prefetching W only) before the previous step has finished"
+                if overlap else "stream-ordered launches",
             },
             "roofline": roofline,
             "cpu_baseline": cpu,
@@ -401,6 +406,7 @@ def main():
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="square_8192")
     ap.add_argument("--gather", action="store_true", help="N>1: also time GEMM + in-place NCCL all-gather of Y")
+    ap.add_argument("--no-overlap", action="store_true", help="decode workloads: plain stream-ordered launches")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for short profiler captures; not a bench run)")
     args = ap.parse_args()

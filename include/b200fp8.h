@@ -48,6 +48,10 @@ typedef enum b200fp8_status {
 #define B200FP8_VARIANT_SIMT 4u      /* CUDA-core kernel, any alignment; slow, used as an on-GPU cross-check */
 #define B200FP8_VARIANT_MASK 0xFu
 #define B200FP8_FLAG_NO_TMA_STORE 0x10u /* tcgen05 variants: write Y with plain stores instead of TMA        */
+/* Decode kernel (M <= 128) only: launch with programmatic stream serialization, so the kernel may start
+ * while the kernel before it in the stream still runs.  It reads W (only W) before that kernel has
+ * completed, everything else after.  The caller promises that no work still in flight writes W. */
+#define B200FP8_FLAG_PDL 0x20u
 
 /* Size of the bytes at the start of every workspace that hold the device status word. */
 #define B200FP8_WORKSPACE_HEADER_BYTES 256u

@@ -287,23 +287,55 @@ def test_call_is_capturable_in_a_cuda_graph(cuda_device):
     """The reference times this operator by CUDA-graph replay; the call must allocate nothing and
     never synchronise.  Captured and replayed results equal the eager ones bit for bit."""
     ops = _ops()
-    for variant, shape in (("tc_2cta", (512, 1024, 1024)), ("tc_1cta", (300, 520, 400)), ("skinny", (16, 4096, 2048))):
+    for variant, shape, overlap in (("tc_2cta", (512, 1024, 1024), False), ("tc_1cta", (300, 520, 400), False),
+                                    ("skinny", (16, 4096, 2048), False), ("skinny", (16, 28672, 8192), True)):
         xq, wq, xs, ws = _gpu(*_inputs(*shape, seed=1))
         fn = ops.make_gemm_fn(xq, wq, xs, ws, variant=variant, reuse_out=True)
         eager = fn().clone()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            fn_side = ops.make_gemm_fn(xq, wq, xs, ws, variant=variant, reuse_out=True)
+            fn_side = ops.make_gemm_fn(xq, wq, xs, ws, variant=variant, reuse_out=True, overlap=overlap)
             fn_side()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
-                out = fn_side()
+                for _ in range(3 if overlap else 1):
+                    out = fn_side()
         out.zero_()
         for _ in range(3):
             graph.replay()
         torch.cuda.synchronize()
         assert torch.equal(out, eager), variant
+    ops.check_device_status()
+
+
+def test_overlapped_launch_of_decode_kernels_back_to_back(cuda_device):
+    """B200FP8_FLAG_PDL: each kernel may start while the one before it still runs and reads only W that
+    early.  A chain of decode GEMMs of different shapes, sharing one workspace and launched without any
+    host synchronisation in between, must give the same bits as the ordinary launches."""
+    ops = _ops()
+    shapes = [(16, 28672, 8192), (1, 4096, 2304), (16, 28672, 8192), (64, 4096, 2048), (8, 2304, 2304), (128, 2304, 6656)]
+    cases = []
+    for i, (m, n, k) in enumerate(shapes):
+        xq, wq, xs, ws = _gpu(*_inputs(m, n, k, seed=20 + i, w_std=0.02))
+        cases.append((xq, wq, xs, ws, ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="skinny")))
+    ws_bytes = max(ops.workspace_bytes(m, n, k) for (m, n, k) in shapes)
+    workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    for rep in range(3):
+        outs = [ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="skinny", workspace=workspace, overlap=True)
+                for (xq, wq, xs, ws, _) in cases]
+        torch.cuda.synchronize()
+        for out, case in zip(outs, cases):
+            assert torch.equal(out, case[4]), f"rep {rep}"
+    # a writer of X directly in front of the GEMM: X is read only after the writer has completed
+    xq, wq, xs, ws, want = cases[0]
+    x_bytes = xq.view(torch.uint8).clone()
+    for rep in range(3):
+        scratch = torch.zeros_like(x_bytes)
+        scratch.copy_(x_bytes)  # the copy kernel is the immediate predecessor on the stream
+        got = ops.fp8_gemm_rowwise(scratch.view(torch.float8_e4m3fn), wq, xs, ws, variant="skinny", overlap=True)
+        assert torch.equal(got, want)
     ops.check_device_status()
 
 

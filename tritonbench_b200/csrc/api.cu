@@ -139,6 +139,7 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
     pl.num_ctas = static_cast<int>(2 * clusters);
   } else if (v == B200FP8_VARIANT_SKINNY) {
     pl.skinny = make_skinny_plan(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), dev.sm_count);
+    pl.skinny.overlap_previous_kernel = (flags & B200FP8_FLAG_PDL) != 0;
     pl.workspace_bytes += pl.skinny.counter_bytes;
     pl.workspace_bytes = (pl.workspace_bytes + 255) & ~static_cast<size_t>(255);
     pl.workspace_bytes += pl.skinny.partial_bytes;

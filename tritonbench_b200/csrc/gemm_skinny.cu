@@ -18,6 +18,13 @@
 // so that a fix-up - a chain of dependent global-memory round trips - never keeps an accumulator
 // from being drained.  Split segments are processed first, so fix-ups happen while W still streams.
 // All waits are bounded.
+//
+// Launched with the programmatic-serialization attribute (B200FP8_FLAG_PDL) the kernel may start
+// while the kernel before it in the stream is still running.  It then fills its whole pipeline
+// with W - weights, which the caller promises nothing in flight is writing - and touches everything
+// else (X, scales, bias, Y, workspace) only after griddepcontrol.wait, i.e. after the previous kernel
+// has completed.  Back-to-back decode GEMMs thus overlap one kernel's tail, where SMs finish at
+// different times, with the next kernel's prologue and first 192 KiB of weights per SM.
 #include <stdlib.h>
 
 #include "kernels.h"
@@ -214,6 +221,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  if (threadIdx.x == 0) griddep_launch_dependents();  // the next kernel does its own waiting
   if (threadIdx.x == 0) SK_TRACE(1);
 
   if (warp == 0) {
@@ -222,21 +230,44 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       const uint32_t tx_bytes = static_cast<uint32_t>(G::kBytesA + bytes_b);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      // First pass over the ring: W only (every stage is free, nothing to wait for), remembering
+      // which k-block each stage holds.  Then wait for the kernels before this one, add the X
+      // boxes of those stages, and carry on with both operands per stage.
+      int issued = 0;
+      bool x_allowed = false;
+      int first_pass_kb[G::kMaxStages];
+      auto allow_x = [&]() {
+        griddep_wait();
+        const int n = issued < stages ? issued : stages;
+        for (int s = 0; s < n; ++s) {
+          tma_load_2d(smem_b + s * bytes_b, &tm_x, bar_full + 8 * s, first_pass_kb[s] * G::kBlockK, 0);
+        }
+        x_allowed = true;
+      };
       for (int i = 0; i < seg_count && ok; ++i) {
         const Segment sg = segment_at(i);
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
-          ok = mbar_wait<false>(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty);
-          if (!ok) break;
+          if (!x_allowed && issued == stages) allow_x();
           const uint32_t full = bar_full + 8 * stage;
-          mbar_arrive_expect_tx(full, tx_bytes);
-          tma_load_2d(smem_a + stage * G::kBytesA, &tm_w, full, kb * G::kBlockK, sg.tile * G::kRowsW);
-          tma_load_2d(smem_b + stage * bytes_b, &tm_x, full, kb * G::kBlockK, 0);
+          if (x_allowed) {
+            ok = mbar_wait<false>(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty);
+            if (!ok) break;
+            mbar_arrive_expect_tx(full, tx_bytes);
+            tma_load_2d(smem_a + stage * G::kBytesA, &tm_w, full, kb * G::kBlockK, sg.tile * G::kRowsW);
+            tma_load_2d(smem_b + stage * bytes_b, &tm_x, full, kb * G::kBlockK, 0);
+          } else {
+            mbar_arrive_expect_tx(full, tx_bytes);
+            tma_load_2d(smem_a + stage * G::kBytesA, &tm_w, full, kb * G::kBlockK, sg.tile * G::kRowsW);
+            first_pass_kb[stage] = kb;
+          }
+          ++issued;
           if (++stage == static_cast<uint32_t>(stages)) {
             stage = 0;
             phase ^= 1u;
           }
         }
       }
+      if (!x_allowed) allow_x();
       if (!ok) {
         const unsigned long long t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -282,6 +313,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     // ------------------------- drain: TMEM -> Y or partial-sum slot -------------------------
     const int quarter = warp & 3;
     const int lane_row = quarter * 32 + lane;  // row of the 128-row W tile = TMEM lane
+    griddep_wait();  // scales, bias, Y and the workspace belong to the previous kernel until it is done
     uint32_t mail_no = 0;
     bool ok = true;
     // hand one tile (or the end marker) to this quarter's fix-up warp
@@ -365,6 +397,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     // ------------------- fix-up: add the parts of a split tile, scale, write Y -------------------
     const int quarter = warp & 3;
     const int lane_row = quarter * 32 + lane;
+    griddep_wait();
     for (uint32_t mail_no = 0;; ++mail_no) {
       const uint32_t ring = mail_no % kMailDepth;
       const uint32_t use = (mail_no / kMailDepth) & 1u;
@@ -480,8 +513,17 @@ cudaError_t launch_gemm_skinny(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
   sh.sk_units = static_cast<long long>(plan.sk_tiles) * plan.kblocks;
   sh.sk_tiles = plan.sk_tiles;
   sh.tiles = plan.tiles;
-  gemm_skinny_kernel<<<plan.num_ctas, SkinnyGeometry::kThreads, plan.smem_bytes, stream>>>(tm_w, tm_x, p, sh);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(plan.num_ctas), 1, 1);
+  cfg.blockDim = dim3(SkinnyGeometry::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = plan.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = plan.overlap_previous_kernel ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, gemm_skinny_kernel, tm_w, tm_x, p, sh);
 }
 
 }  // namespace b200fp8

@@ -81,6 +81,7 @@ struct SkinnyPlan {
   int segs_per_cta;  // upper bound on tile segments per CTA (partial-sum slots)
   int dp_waves;      // whole tiles per CTA (tiles / CTAs)
   int sk_tiles;      // remaining tiles, cut along K into equal runs
+  bool overlap_previous_kernel;  // launch with programmatic stream serialization
   size_t smem_bytes;
   size_t partial_bytes;  // fp32 partial sums
   size_t counter_bytes;  // fixed-size region of per (tile, lane quarter) arrival counters

@@ -46,6 +46,15 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---------------------------- programmatic dependent launch ----------------------------
+// Both are no-ops in a kernel that was launched without the programmatic-serialization attribute.
+// wait: returns once every kernel this launch depends on has completed and its writes are visible.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// launch_dependents: the next kernel in the stream may start being scheduled (it does its own wait).
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ------------------------------------ cluster helpers ----------------------------------
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n"

@@ -25,6 +25,7 @@ VARIANT_TC_2CTA = 2
 VARIANT_SKINNY = 3
 VARIANT_SIMT = 4
 FLAG_NO_TMA_STORE = 0x10
+FLAG_PDL = 0x20
 VARIANTS = {
     "auto": VARIANT_AUTO,
     "tc_1cta": VARIANT_TC_1CTA,
