@@ -97,7 +97,7 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
  * loaded library: every GPU that loads the library holds those 8 MiB until the process exits.
  *
  *   - M > 128, or a shape whose partial sums need more than the 8 MiB, returns B200FP8_TOO_LARGE
- *     (it fits, for example, M <= 16 with N up to 65536, and M = 32 with N = 28672, K = 8192);
+ *     (the scratch a decode problem needs grows with M only: every problem with M <= 48 fits);
  *   - calls no cudaMalloc / cudaFree and no allocating library routine; it enqueues one small
  *     cudaMemsetAsync (status word + the counters this call uses) and the kernel on `cuda_stream`;
  *   - the FIRST call on each device looks up the array's device address (cudaGetSymbolAddress) and

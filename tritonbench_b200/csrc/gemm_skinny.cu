@@ -29,6 +29,7 @@
 
 #include "kernels.h"
 #include "ptx.cuh"
+#include "streamk.cuh"
 
 namespace b200fp8 {
 
@@ -78,63 +79,6 @@ enum WaitSite : uint32_t {
 constexpr int kMailDepth = 4;      // fix-up requests in flight per lane quarter
 constexpr int kMailDone = -1;      // "no more requests" marker
 
-struct Segment {
-  int tile;
-  int slot;  // partial-sum slot (global index)
-  int kb0;
-  int kb1;
-};
-
-// One CTA's run of consecutive units [u_begin, u_stop) cut at tile boundaries.  Segments that
-// cover only part of a tile's K range are processed FIRST (the one at the end of the run, then
-// the one at its start), the whole tiles after them: the cross-CTA fix-up of a split tile then
-// happens early, hidden behind the streaming of the remaining tiles.
-struct Run {
-  long long u_begin;
-  long long u_stop;
-  int kblocks;
-  int first_tile;
-  int count;
-  bool tail_first;  // last segment is partial and goes first
-  bool head_next;   // first segment is partial (and is not that same segment)
-};
-
-__device__ __forceinline__ Run make_run(long long u_begin, long long u_stop, int kblocks) {
-  Run r;
-  r.u_begin = u_begin;
-  r.u_stop = u_stop;
-  r.kblocks = kblocks;
-  r.first_tile = static_cast<int>(u_begin / kblocks);
-  r.count = u_stop > u_begin ? static_cast<int>((u_stop - 1) / kblocks) - r.first_tile + 1 : 0;
-  r.tail_first = r.count > 0 && (u_stop % kblocks) != 0;
-  r.head_next = r.count > 0 && (u_begin % kblocks) != 0 && !(r.tail_first && r.count == 1);
-  return r;
-}
-
-// i-th segment of the run in processing order; `slot_base` is this CTA's first partial-sum slot
-__device__ __forceinline__ Segment run_segment(const Run& r, int i, int slot_base) {
-  int j;  // position in the run
-  int pos = 0;
-  if (r.tail_first && i == 0) {
-    j = r.count - 1;
-  } else {
-    pos += r.tail_first ? 1 : 0;
-    if (r.head_next && i == pos) {
-      j = 0;
-    } else {
-      pos += r.head_next ? 1 : 0;
-      j = (r.head_next ? 1 : 0) + (i - pos);
-    }
-  }
-  Segment s;
-  s.slot = slot_base + j;
-  s.tile = r.first_tile + j;
-  const long long tile_u0 = static_cast<long long>(s.tile) * r.kblocks;
-  s.kb0 = r.u_begin > tile_u0 ? static_cast<int>(r.u_begin - tile_u0) : 0;
-  s.kb1 = r.u_stop < tile_u0 + r.kblocks ? static_cast<int>(r.u_stop - tile_u0) : r.kblocks;
-  return s;
-}
-
 __global__ void __launch_bounds__(SkinnyGeometry::kThreads, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const SkinnyParams p, const SkinnyShape sh) {
@@ -172,25 +116,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int slot_base = static_cast<int>(blockIdx.x) * sh.segs_per_cta;
-  // this CTA's work: a run of the K-split region first, then its whole tiles
-  long long u_begin = static_cast<long long>(blockIdx.x) * sh.units_per_cta;
-  if (u_begin > sh.sk_units) u_begin = sh.sk_units;
-  const long long u_stop = u_begin + sh.units_per_cta < sh.sk_units ? u_begin + sh.units_per_cta : sh.sk_units;
-  const Run run = make_run(u_begin, u_stop, kblocks);
-  const int first_whole = sh.sk_tiles + static_cast<int>(blockIdx.x);
-  const int whole_count = first_whole < sh.tiles ? (sh.tiles - first_whole + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x) : 0;
-  const int seg_count = run.count + whole_count;
-  auto segment_at = [&](int i) {
-    if (i < run.count) return run_segment(run, i, slot_base);
-    Segment s;
-    s.tile = first_whole + (i - run.count) * static_cast<int>(gridDim.x);
-    s.slot = 0;
-    s.kb0 = 0;
-    s.kb1 = kblocks;
-    return s;
-  };
   const size_t slot_floats = static_cast<size_t>(sh.tokens_pad) * G::kRowsW;
+  // this CTA's work: a run of the K-split region first, then its whole tiles
+  const CtaWork work = make_cta_work(static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), sh.tiles, sh.sk_tiles,
+                                     kblocks, sh.units_per_cta, sh.segs_per_cta);
+  const int seg_count = work.count;
+  auto segment_at = [&](int i) { return work_segment(work, i); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -380,9 +311,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
       // Publish this warp's part of the slot; if every other part of the tile is already there,
       // this CTA finishes the tile: its fix-up warp does, this warp goes back to draining.
-      const long long tile_u0 = static_cast<long long>(sg.tile) * kblocks;
-      const int first_part = static_cast<int>(tile_u0 / sh.units_per_cta);
-      const int last_part = static_cast<int>((tile_u0 + kblocks - 1) / sh.units_per_cta);
+      int first_part, last_part;
+      tile_parts(sg.tile, kblocks, sh.units_per_cta, &first_part, &last_part);
       const uint32_t parts = static_cast<uint32_t>(last_part - first_part + 1);
       __threadfence();
       __syncwarp();
@@ -414,9 +344,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       const bool n_ok = n < p.N;
       const float ws = n_ok ? __ldg(p.w_scale + n) : 0.0f;
       const float bias = (n_ok && p.bias != nullptr) ? __bfloat162float(p.bias[n]) : 0.0f;
-      const long long tile_u0 = static_cast<long long>(tile) * kblocks;
-      const int first_part = static_cast<int>(tile_u0 / sh.units_per_cta);
-      const int last_part = static_cast<int>((tile_u0 + kblocks - 1) / sh.units_per_cta);
+      int first_part, last_part;
+      tile_parts(tile, kblocks, sh.units_per_cta, &first_part, &last_part);
       __threadfence();  // the counter said every part is published; order our reads after that
       // 16 tokens x up to 4 parts = up to 64 independent loads in flight per thread; the parts of an
       // element are added in ascending CTA order whatever CTA does the adding.
@@ -429,8 +358,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int part = part0 + q <= last_part ? part0 + q : last_part;
-            const long long their_first = static_cast<long long>(part) * sh.units_per_cta / kblocks;
-            const size_t their_slot = static_cast<size_t>(part) * sh.segs_per_cta + (tile - their_first);
+            const size_t their_slot = part_slot(part, tile, kblocks, sh.units_per_cta, sh.segs_per_cta);
             const float* src =
                 p.partials + their_slot * slot_floats + static_cast<size_t>(m0) * G::kRowsW + lane_row;
 #pragma unroll
