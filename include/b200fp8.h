@@ -52,6 +52,9 @@ typedef enum b200fp8_status {
  * while the kernel before it in the stream still runs.  It reads W (only W) before that kernel has
  * completed, everything else after.  The caller promises that no work still in flight writes W. */
 #define B200FP8_FLAG_PDL 0x20u
+/* Y holds IEEE fp16 instead of bf16 (the output type of TritonBench's `fp8_gemm` operator with per-tensor
+ * scales, tritonbench/operators/fp8_gemm/fp8_gemm.py:88-101); same 16-bit storage, same leading dimension. */
+#define B200FP8_FLAG_OUT_FP16 0x40u
 
 /* Size of the bytes at the start of every workspace that hold the device status word. */
 #define B200FP8_WORKSPACE_HEADER_BYTES 256u
@@ -110,6 +113,24 @@ int b200fp8_gemm_rowwise_noalloc(const void* xq, const void* wq, const float* x_
                                  const void* bias_bf16, void* y_bf16, int64_t M, int64_t N, int64_t K, int64_t ldx,
                                  int64_t ldw, int64_t ldy, void* cuda_stream);
 int b200fp8_noalloc_status(uint32_t* device_status);
+
+/*
+ * Rowwise e4m3 quantiser: x [rows, cols] (row pitch ldx ELEMENTS) -> q [rows, cols] e4m3 bytes (row pitch ldq
+ * bytes) and scale [rows] fp32 such that x ~ float(q) * scale.  One pass over HBM, asynchronous on the stream.
+ *   x_dtype  B200FP8_DTYPE_BF16 / _FP16 / _FP32
+ *   recipe   B200FP8_QUANT_OPERATOR: bit-exact with the operator's `fp8_row_quantize`
+ *            (tritonbench/operators/fp8_gemm_rowwise/operator.py:136-145: arithmetic in x's dtype,
+ *            multiplier 448 / clamp(rowmax, 1e-12), fp16 multiplier clamped to 65504, returns 1 / multiplier);
+ *            B200FP8_QUANT_FP32 (fp32 x only): scale = max(rowabsmax, 1e-12) / 448, q = e4m3(clamp(x / scale)).
+ * Replaces: the five eager torch kernels per operand of operator.py:136-145 called from operator.py:280-297.
+ */
+#define B200FP8_DTYPE_BF16 0
+#define B200FP8_DTYPE_FP16 1
+#define B200FP8_DTYPE_FP32 2
+#define B200FP8_QUANT_OPERATOR 0
+#define B200FP8_QUANT_FP32 1
+int b200fp8_row_quantize(const void* x, int x_dtype, int recipe, int64_t rows, int64_t cols, int64_t ldx, void* q,
+                         int64_t ldq, float* scale, void* cuda_stream);
 
 /*
  * Read the device status word of a workspace.  Call after the stream has been synchronised.

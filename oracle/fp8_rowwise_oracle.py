@@ -20,6 +20,8 @@ What this restates:
                               to the operands in fp32 before the product, and the stock shims' bias
                               add (operator.py:207-213) done in fp32 before the single bf16 rounding
   * `flops`, `gbytes`         operator.py:248-271
+  * `gemm_rowwise(out_dtype=float16)` with all-ones scales is the sibling operator `fp8_gemm`'s
+    `torch._scaled_mm(a, b, 1.0, 1.0, out_dtype=float16)` (tritonbench/operators/fp8_gemm/fp8_gemm.py:88-101)
 """
 import math
 from typing import Optional, Tuple
@@ -89,6 +91,7 @@ def gemm_rowwise(
     bias: Optional[torch.Tensor] = None,
     keep_fp32: bool = False,
     decode: str = "table",
+    out_dtype: torch.dtype = torch.bfloat16,
 ) -> torch.Tensor:
     """Y = bf16((float(xq) * x_scale[:, None]) @ (float(wq) * w_scale[:, None]).T (+ bias)) on CPU in fp32.
 
@@ -105,7 +108,7 @@ def gemm_rowwise(
     y = x @ w.T
     if bias is not None:
         y = y + bias.cpu().to(torch.float32)[None, :]
-    return y if keep_fp32 else y.to(torch.bfloat16)
+    return y if keep_fp32 else y.to(out_dtype)
 
 
 def bf16_ulp(v: torch.Tensor) -> torch.Tensor:
@@ -114,17 +117,24 @@ def bf16_ulp(v: torch.Tensor) -> torch.Tensor:
     return torch.exp2(torch.floor(torch.log2(a)) - 7.0)
 
 
-def tolerance(ref_fp32: torch.Tensor) -> torch.Tensor:
-    """Per-element bound: 1 bf16 ulp of |ref| + 1e-2 * RMS(ref)."""
+def fp16_ulp(v: torch.Tensor) -> torch.Tensor:
+    """Spacing of fp16 numbers at |v| (10 mantissa bits; subnormal spacing 2^-24 below 2^-14)."""
+    a = v.abs().to(torch.float32).clamp(min=2.0 ** -14)
+    return torch.exp2(torch.floor(torch.log2(a)) - 10.0)
+
+
+def tolerance(ref_fp32: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Per-element bound: 1 ulp of the output type at |ref| + 1e-2 * RMS(ref)."""
     rms = ref_fp32.to(torch.float64).pow(2).mean().sqrt().to(torch.float32)
-    return bf16_ulp(ref_fp32) + 1e-2 * rms
+    ulp = fp16_ulp(ref_fp32) if out_dtype == torch.float16 else bf16_ulp(ref_fp32)
+    return ulp + 1e-2 * rms
 
 
 def compare(out_bf16: torch.Tensor, ref_bf16: torch.Tensor) -> dict:
     """max |out - ref| against the tolerance, everything as float32 on CPU."""
     out = out_bf16.detach().cpu().to(torch.float32)
     ref = ref_bf16.detach().cpu().to(torch.float32)
-    tol = tolerance(ref)
+    tol = tolerance(ref, ref_bf16.dtype)
     diff = (out - ref).abs()
     ratio = diff / tol
     return {

@@ -339,6 +339,39 @@ def test_overlapped_launch_of_decode_kernels_back_to_back(cuda_device):
     ops.check_device_status()
 
 
+@pytest.mark.parametrize("variant,shape", [("tc_1cta", (300, 520, 400)), ("tc_2cta", (513, 1001, 256)), ("tc_2cta", (512, 1024, 1024)),
+                                           ("skinny", (17, 520, 400)), ("skinny", (16, 4096, 2048)), ("simt", (50, 70, 90))])
+def test_fp16_output(cuda_device, variant, shape):
+    m, n, k = shape
+    xq, wq, xs, ws = _inputs(m, n, k, seed=13)
+    ref = orc.gemm_rowwise(xq, wq, xs, ws, out_dtype=torch.float16)
+    y = _run(variant, xq, wq, xs, ws, out_dtype=torch.float16)
+    assert y.dtype == torch.float16
+    _assert_close(y, ref, f"{variant} fp16 out")
+    y2 = _run(variant, xq, wq, xs, ws, out_dtype=torch.float16, tma_store=False)
+    _assert_close(y2, ref, f"{variant} fp16 out, plain stores")
+
+
+def test_fp8_gemm_call_with_per_tensor_and_unit_scales(cuda_device):
+    """The sibling operator's call: a [M,K], b [K,N] column-major, per-tensor scales, fp16 out by default."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(21)
+    m, n, k = 384, 768, 1024
+    a = torch.randn((m, k), generator=g).to(torch.float8_e4m3fn)
+    b = torch.randn((k, n), generator=g).to(torch.float8_e4m3fn).T.contiguous().T  # the operator's own layout
+    ones_m, ones_n = torch.ones(m), torch.ones(n)
+    y = ops.fp8_gemm(a.cuda(), b.cuda())
+    ops.check_device_status()
+    assert y.dtype == torch.float16
+    _assert_close(y, orc.gemm_rowwise(a, b.T, ones_m, ones_n, out_dtype=torch.float16), "fp8_gemm unit scales")
+    y = ops.fp8_gemm(a.cuda(), b.cuda(), 0.5, torch.tensor(0.25), out_dtype=torch.bfloat16)
+    _assert_close(y, orc.gemm_rowwise(a, b.T, ones_m * 0.5, ones_n * 0.25), "fp8_gemm per-tensor scales")
+    y = ops.fp8_gemm(a.cuda(), b.cuda(), torch.full((m, 1), 2.0).cuda(), torch.full((1, n), 0.5).cuda(), out_dtype=torch.bfloat16)
+    _assert_close(y, orc.gemm_rowwise(a, b.T, ones_m * 2.0, ones_n * 0.5), "fp8_gemm rowwise scales")
+    with pytest.raises(ValueError):
+        ops.fp8_gemm(a.cuda(), b.cuda().contiguous())
+
+
 def test_host_buffer_entry_point(cuda_device):
     ops = _ops()
     for variant, shape in (("auto", (384, 768, 512)), ("auto", (16, 2304, 2048))):

@@ -42,3 +42,21 @@ def test_plugin_through_the_reference_harness_on_gpu(cuda_device):
     assert tuple(x_val) == (1024, 2048, 1024)
     assert cells["b200_native"].accuracy is True
     assert cells["b200_native"].latency is not None
+
+
+def test_fp8_gemm_operator_backend_through_the_reference_harness(cuda_device):
+    """The sibling operator `fp8_gemm`: our column next to its own torch._scaled_mm baseline, both output types."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "tritonbench")):
+        pytest.skip("no installed copy of the tritonbench package on this machine")
+    sys.path.insert(0, ref)
+    from tritonbench_b200 import tritonbench_plugin as plug
+
+    for extra in ([], ["--scaling_rowwise"]):
+        out = plug.run(
+            ["--op", "fp8_gemm", "--device", "cuda", "--metrics", "latency,tflops,speedup,accuracy", "--only",
+             "torch_fp8_gemm,b200_native", "--m", "1024", "--n", "2048", "--k", "1024"] + extra
+        )
+        assert "b200-tflops" in str(out)
+        cells = out.result[0][1]
+        assert cells["b200_native"].accuracy is True, extra

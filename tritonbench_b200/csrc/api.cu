@@ -230,7 +230,8 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
 
   if (pl.variant == B200FP8_VARIANT_SIMT) {
     SimtParams sp = {static_cast<const uint8_t*>(xq), static_cast<const uint8_t*>(wq), x_scale, w_scale, bias, y,
-                     static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), ldx, ldw, ldy};
+                     static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), ldx, ldw, ldy,
+                     (flags & B200FP8_FLAG_OUT_FP16) ? 1 : 0};
     return note_cuda(launch_gemm_simt(sp, stream));
   }
 
@@ -256,6 +257,7 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
     kp.N = static_cast<int>(N);
     kp.K = static_cast<int>(K);
     kp.ldy = ldy;
+    kp.out_fp16 = (flags & B200FP8_FLAG_OUT_FP16) ? 1 : 0;
     kp.counters = reinterpret_cast<uint32_t*>(ws + off);
     off = (off + pl.skinny.counter_bytes + 255) & ~static_cast<size_t>(255);
     kp.partials = reinterpret_cast<float*>(ws + off);
@@ -289,6 +291,7 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
   tp.K = static_cast<int>(K);
   tp.ldy = ldy;
   tp.use_tma_store = pl.tma_store ? 1 : 0;
+  tp.out_fp16 = (flags & B200FP8_FLAG_OUT_FP16) ? 1 : 0;
   tp.group_m = pl.group_m;
   tp.status = status_word;
 #ifdef B200FP8_DEBUG_KNOBS
@@ -339,6 +342,29 @@ int b200fp8_noalloc_status(uint32_t* device_status) {
   const cudaError_t e = skinny_static_scratch(&scratch, &scratch_bytes);
   if (e != cudaSuccess) return note_cuda(e);
   return b200fp8_query_status(scratch, device_status);
+}
+
+int b200fp8_row_quantize(const void* x, int x_dtype, int recipe, int64_t rows, int64_t cols, int64_t ldx, void* q,
+                         int64_t ldq, float* scale, void* cuda_stream) {
+  if (x == nullptr || q == nullptr || scale == nullptr) return B200FP8_BAD_ARG;
+  if (rows <= 0 || cols <= 0 || ldx < cols || ldq < cols) return B200FP8_BAD_ARG;
+  if (rows > 0x7FFFFFFFll || cols > 0x7FFFFF00ll) return B200FP8_TOO_LARGE;
+  if (x_dtype < kQuantBf16 || x_dtype > kQuantFp32) return B200FP8_BAD_ARG;
+  if (recipe != kRecipeOperator && recipe != kRecipeFp32) return B200FP8_BAD_ARG;
+  if (recipe == kRecipeFp32 && x_dtype != kQuantFp32) return B200FP8_BAD_ARG;
+  const int64_t elem = x_dtype == kQuantFp32 ? 4 : 2;
+  QuantParams p = {};
+  p.x = x;
+  p.q = static_cast<uint8_t*>(q);
+  p.scale = scale;
+  p.rows = rows;
+  p.cols = static_cast<int>(cols);
+  p.ldx = ldx;
+  p.ldq = ldq;
+  p.dtype = x_dtype;
+  p.recipe = recipe;
+  p.vector_ok = aligned16(x) && (ldx * elem) % 16 == 0 && (reinterpret_cast<uintptr_t>(q) & 7u) == 0 && ldq % 8 == 0;
+  return note_cuda(launch_row_quantize(p, static_cast<cudaStream_t>(cuda_stream)));
 }
 
 int b200fp8_query_status(const void* workspace, uint32_t* device_status) {

@@ -3,6 +3,7 @@
 // do not, and it is the on-GPU cross-check for sizes where a host check would take minutes.
 // It is two orders of magnitude slower than the tensor-core kernels and is never chosen for a
 // shape those kernels accept.
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
 #include "kernels.h"
@@ -60,7 +61,11 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
       if (n >= p.N) continue;
       float v = acc[i][j] * (sx * p.w_scale[n]);
       if (p.bias != nullptr) v += __bfloat162float(p.bias[n]);
-      p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16_rn(v);
+      if (p.out_fp16) {
+        reinterpret_cast<__half*>(p.y)[static_cast<long long>(m) * p.ldy + n] = __float2half_rn(v);
+      } else {
+        p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16_rn(v);
+      }
     }
   }
 }

@@ -292,7 +292,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             const int m = c + j;
             if (m < p.M && n_ok) {
               const float v = __uint_as_float(acc[j]) * (__ldg(p.x_scale + m) * ws) + bias;
-              p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16_rn(v);
+              reinterpret_cast<uint16_t*>(p.y)[static_cast<long long>(m) * p.ldy + n] = to_out16(v, p.out_fp16);
             }
           }
         } else {
@@ -377,7 +377,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           const int m = m0 + j;
           if (m < p.M && n_ok) {
             const float v = sum[j] * (__ldg(p.x_scale + m) * ws) + bias;
-            p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16_rn(v);
+            reinterpret_cast<uint16_t*>(p.y)[static_cast<long long>(m) * p.ldy + n] = to_out16(v, p.out_fp16);
           }
         }
       }

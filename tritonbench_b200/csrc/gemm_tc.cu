@@ -289,15 +289,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const uint32_t chunk = static_cast<uint32_t>((half * 4 + j) ^ (lane & 7));
-              st_shared_v4(row_addr + chunk * 16, pack_bf16x2(v[8 * j + 0], v[8 * j + 1]),
-                           pack_bf16x2(v[8 * j + 2], v[8 * j + 3]), pack_bf16x2(v[8 * j + 4], v[8 * j + 5]),
-                           pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+              if (p.out_fp16) {
+                st_shared_v4(row_addr + chunk * 16, pack_f16x2(v[8 * j + 0], v[8 * j + 1]),
+                             pack_f16x2(v[8 * j + 2], v[8 * j + 3]), pack_f16x2(v[8 * j + 4], v[8 * j + 5]),
+                             pack_f16x2(v[8 * j + 6], v[8 * j + 7]));
+              } else {
+                st_shared_v4(row_addr + chunk * 16, pack_bf16x2(v[8 * j + 0], v[8 * j + 1]),
+                             pack_bf16x2(v[8 * j + 2], v[8 * j + 3]), pack_bf16x2(v[8 * j + 4], v[8 * j + 5]),
+                             pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+              }
             }
           } else if (row < p.M) {
-            __nv_bfloat16* dst = p.y + static_cast<long long>(row) * p.ldy + c_first;
+            uint16_t* dst = reinterpret_cast<uint16_t*>(p.y) + static_cast<long long>(row) * p.ldy + c_first;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              if (c_first + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+              if (c_first + j < p.N) dst[j] = to_out16(v[j], p.out_fp16);
             }
           }
         }

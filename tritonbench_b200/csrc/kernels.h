@@ -43,6 +43,7 @@ struct TcParams {
   int M, N, K;
   long long ldy;       // elements
   int use_tma_store;   // 0: plain predicated stores
+  int out_fp16;        // 0: Y holds bf16, 1: Y holds IEEE fp16
   int group_m;         // tile-rasterisation group height (tiles)
   uint32_t* status;    // device status word
 #ifdef B200FP8_DEBUG_KNOBS
@@ -104,6 +105,7 @@ struct SkinnyParams {
   __nv_bfloat16* y;
   int M, N, K;
   long long ldy;
+  int out_fp16;
   float* partials;     // [num_ctas * segs_per_cta][tokens_pad][128] fp32
   uint32_t* counters;  // [tiles * 4], zero on entry, zero again on exit
   uint32_t* status;
@@ -131,8 +133,29 @@ struct SimtParams {
   __nv_bfloat16* y;
   int M, N, K;
   long long ldx, ldw, ldy;
+  int out_fp16;
 };
 
 cudaError_t launch_gemm_simt(const SimtParams& p, cudaStream_t stream);
+
+// ------------------------------ rowwise quantiser (quantize.cu) -----------------------------
+constexpr int kQuantBf16 = 0, kQuantFp16 = 1, kQuantFp32 = 2;  // dtype of x
+constexpr int kRecipeOperator = 0;  // the operator's fp8_row_quantize: arithmetic in x's dtype, multiplier 448/max
+constexpr int kRecipeFp32 = 1;      // benchmark recipe: scale = max(absmax, 1e-12) / 448 in fp32, q = x / scale
+
+struct QuantParams {
+  const void* x;
+  uint8_t* q;
+  float* scale;
+  long long rows;
+  int cols;
+  long long ldx;  // elements
+  long long ldq;  // bytes
+  int dtype;
+  int recipe;
+  int vector_ok;  // rows of x start on 16-byte boundaries and rows of q on 8-byte boundaries
+};
+
+cudaError_t launch_row_quantize(const QuantParams& p, cudaStream_t stream);
 
 }  // namespace b200fp8

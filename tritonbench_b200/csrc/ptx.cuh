@@ -326,6 +326,18 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
+// same with IEEE fp16 halves
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// one fp32 -> the 16 bits of a bf16 (out_fp16 == 0) or fp16 (out_fp16 != 0) value, round to nearest even
+__device__ __forceinline__ uint16_t to_out16(float v, int out_fp16) {
+  return static_cast<uint16_t>((out_fp16 ? pack_f16x2(v, 0.0f) : pack_bf16x2(v, 0.0f)) & 0xFFFFu);
+}
+
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }

@@ -1,0 +1,231 @@
+// Rowwise e4m3 quantiser: one pass over HBM.  A CTA owns a row, keeps it in registers between
+// the absmax reduction and the quantisation, and writes e4m3 bytes plus one fp32 scale.
+//
+// Two recipes, both bit-exact with the torch expressions they replace:
+//   kRecipeOperator   the operator's own `fp8_row_quantize`: every step in the dtype T of x, each
+//                     result rounded to T as torch's eager kernels do:
+//                        c = max(rowabsmax, T(1e-12));  mult = T(T(1 / c) * 448)   [torch evaluates scalar / tensor
+//                        as reciprocal(tensor) * scalar];  (fp16: mult = min(mult, 65504))
+//                        q = e4m3( clamp( T(x * mult), +-448 ) );  scale = float( T(1 / mult) )
+//   kRecipeFp32       the benchmark recipe on fp32 math:
+//                        scale = max(rowabsmax, 1e-12) / 448;  q = e4m3( clamp( x / scale, +-448 ) )
+// Divisions and products are IEEE round-to-nearest (no fast-math), conversions to e4m3 round to
+// nearest even and cannot overflow after the clamp.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include <type_traits>
+
+#include "kernels.h"
+
+namespace b200fp8 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kVec = 8;       // elements per vector load (16 bytes of a 16-bit type; two loads for fp32)
+constexpr int kMaxVecs = 8;   // vectors a thread keeps in registers: rows up to 256*8*8 = 16384 elements
+
+template <typename T> struct Conv;
+template <> struct Conv<__nv_bfloat16> {
+  static __device__ __forceinline__ float up(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ float rnd(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+template <> struct Conv<__half> {
+  static __device__ __forceinline__ float up(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ float rnd(float v) { return __half2float(__float2half_rn(v)); }
+};
+template <> struct Conv<float> {
+  static __device__ __forceinline__ float up(float v) { return v; }
+  static __device__ __forceinline__ float rnd(float v) { return v; }
+};
+
+__device__ __forceinline__ uint8_t to_e4m3(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+__device__ __forceinline__ float block_max(float v, float* smem) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = smem[0];
+#pragma unroll
+  for (int w = 1; w < kThreads / 32; ++w) r = fmaxf(r, smem[w]);
+  return r;
+}
+
+// eight consecutive elements as loaded (kept packed between the two passes to save registers)
+template <typename T>
+struct Raw {
+  uint4 lo;
+  uint4 hi;  // used by 4-byte T only
+};
+
+template <typename T>
+__device__ __forceinline__ Raw<T> load_raw(const T* p) {
+  Raw<T> r;
+  r.lo = *reinterpret_cast<const uint4*>(p);
+  if constexpr (sizeof(T) == 4) r.hi = *reinterpret_cast<const uint4*>(p + 4);
+  return r;
+}
+
+// absmax of the eight elements, and their eight e4m3 codes.  16-bit types stay packed: two
+// elements per instruction for |x|, max, the product (mul.rn of the packed type IS the correctly
+// rounded product torch computes) and the e4m3 conversion (cvt.rn.satfinite.e4m3x2.f32; saturation
+// to +-448 is the clamp).
+template <typename T, int kRecipe>
+struct Ops;
+
+template <int kRecipe>
+struct Ops<__nv_bfloat16, kRecipe> {
+  static __device__ __forceinline__ float absmax(const Raw<__nv_bfloat16>& r) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r.lo);
+    __nv_bfloat162 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+    return fmaxf(__low2float(m), __high2float(m));
+  }
+  static __device__ __forceinline__ uint2 codes(const Raw<__nv_bfloat16>& r, float mult) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r.lo);
+    const __nv_bfloat162 m2 = __float2bfloat162_rn(mult);  // mult is a bf16 value already
+    uint32_t w[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float2 a = __bfloat1622float2(__hmul2(h[2 * i], m2));
+      const float2 b = __bfloat1622float2(__hmul2(h[2 * i + 1], m2));
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(a, __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(b, __NV_SATFINITE, __NV_E4M3);
+      w[i] = lo | (hi << 16);
+    }
+    return make_uint2(w[0], w[1]);
+  }
+};
+
+template <int kRecipe>
+struct Ops<__half, kRecipe> {
+  static __device__ __forceinline__ float absmax(const Raw<__half>& r) {
+    const __half2* h = reinterpret_cast<const __half2*>(&r.lo);
+    __half2 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+    return fmaxf(__low2float(m), __high2float(m));
+  }
+  static __device__ __forceinline__ uint2 codes(const Raw<__half>& r, float mult) {
+    const __half2* h = reinterpret_cast<const __half2*>(&r.lo);
+    const __half2 m2 = __float2half2_rn(mult);
+    uint32_t w[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float2 a = __half22float2(__hmul2(h[2 * i], m2));
+      const float2 b = __half22float2(__hmul2(h[2 * i + 1], m2));
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(a, __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(b, __NV_SATFINITE, __NV_E4M3);
+      w[i] = lo | (hi << 16);
+    }
+    return make_uint2(w[0], w[1]);
+  }
+};
+
+template <int kRecipe>
+struct Ops<float, kRecipe> {
+  static __device__ __forceinline__ float absmax(const Raw<float>& r) {
+    const float* a = reinterpret_cast<const float*>(&r.lo);
+    const float* b = reinterpret_cast<const float*>(&r.hi);
+    float m = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m = fmaxf(m, fmaxf(fabsf(a[j]), fabsf(b[j])));
+    return m;
+  }
+  static __device__ __forceinline__ float one(float v, float mult) {
+    return kRecipe == kRecipeOperator ? __fmul_rn(v, mult) : __fdiv_rn(v, mult);
+  }
+  static __device__ __forceinline__ uint2 codes(const Raw<float>& r, float mult) {
+    const float* a = reinterpret_cast<const float*>(&r.lo);
+    const float* b = reinterpret_cast<const float*>(&r.hi);
+    const uint32_t c0 = __nv_cvt_float2_to_fp8x2(make_float2(one(a[0], mult), one(a[1], mult)), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t c1 = __nv_cvt_float2_to_fp8x2(make_float2(one(a[2], mult), one(a[3], mult)), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t c2 = __nv_cvt_float2_to_fp8x2(make_float2(one(b[0], mult), one(b[1], mult)), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t c3 = __nv_cvt_float2_to_fp8x2(make_float2(one(b[2], mult), one(b[3], mult)), __NV_SATFINITE, __NV_E4M3);
+    return make_uint2(c0 | (c1 << 16), c2 | (c3 << 16));
+  }
+};
+
+template <typename T, int kRecipe>
+__global__ void __launch_bounds__(kThreads) row_quantize_kernel(const QuantParams p) {
+  __shared__ float red[kThreads / 32];
+  const long long row = blockIdx.x;
+  const T* x = static_cast<const T*>(p.x) + row * p.ldx;
+  uint8_t* q = p.q + row * p.ldq;
+  const int cols = p.cols;
+  const int vec_cols = p.vector_ok ? (cols / kVec) * kVec : 0;  // handled with 16-byte accesses
+  const int nvec = vec_cols / kVec;
+
+  // pass 1: absmax; the first kMaxVecs vectors of every thread stay (packed) in registers
+  using O = Ops<T, kRecipe>;
+  Raw<T> keep[kMaxVecs];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kMaxVecs; ++i) {
+    const int v = threadIdx.x + i * kThreads;
+    if (v < nvec) keep[i] = load_raw<T>(x + v * kVec);
+  }
+#pragma unroll
+  for (int i = 0; i < kMaxVecs; ++i) {
+    const int v = threadIdx.x + i * kThreads;
+    if (v < nvec) amax = fmaxf(amax, O::absmax(keep[i]));
+  }
+  for (int v = threadIdx.x + kMaxVecs * kThreads; v < nvec; v += kThreads) {  // rows longer than 16384
+    amax = fmaxf(amax, O::absmax(load_raw<T>(x + v * kVec)));
+  }
+  for (int c = vec_cols + threadIdx.x; c < cols; c += kThreads) amax = fmaxf(amax, fabsf(Conv<T>::up(x[c])));
+  amax = block_max(amax, red);
+
+  // the row's multiplier (or divisor) and the scale handed to the GEMM
+  float mult, scale;
+  if constexpr (kRecipe == kRecipeOperator) {
+    const float c = fmaxf(amax, Conv<T>::rnd(1e-12f));
+    mult = Conv<T>::rnd(__fmul_rn(Conv<T>::rnd(__fdiv_rn(1.0f, c)), 448.0f));
+    if constexpr (std::is_same<T, __half>::value) mult = fminf(mult, 65504.0f);
+    scale = Conv<T>::rnd(__fdiv_rn(1.0f, mult));
+  } else {
+    scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+    mult = scale;  // used as the divisor
+  }
+  if (threadIdx.x == 0) p.scale[row] = scale;
+
+  // pass 2: quantise from registers (re-reading only what did not fit)
+#pragma unroll
+  for (int i = 0; i < kMaxVecs; ++i) {
+    const int v = threadIdx.x + i * kThreads;
+    if (v < nvec) *reinterpret_cast<uint2*>(q + v * kVec) = O::codes(keep[i], mult);
+  }
+  for (int v = threadIdx.x + kMaxVecs * kThreads; v < nvec; v += kThreads) {
+    *reinterpret_cast<uint2*>(q + v * kVec) = O::codes(load_raw<T>(x + v * kVec), mult);
+  }
+  for (int c = vec_cols + threadIdx.x; c < cols; c += kThreads) {
+    const float v = Conv<T>::up(x[c]);
+    const float y = kRecipe == kRecipeOperator ? Conv<T>::rnd(__fmul_rn(v, mult)) : __fdiv_rn(v, mult);
+    q[c] = to_e4m3(y);
+  }
+}
+
+template <typename T>
+cudaError_t launch_t(const QuantParams& p, cudaStream_t stream) {
+  const dim3 grid(static_cast<unsigned>(p.rows), 1, 1);
+  if (p.recipe == kRecipeOperator) {
+    row_quantize_kernel<T, kRecipeOperator><<<grid, kThreads, 0, stream>>>(p);
+  } else {
+    row_quantize_kernel<T, kRecipeFp32><<<grid, kThreads, 0, stream>>>(p);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_row_quantize(const QuantParams& p, cudaStream_t stream) {
+  switch (p.dtype) {
+    case kQuantBf16: return launch_t<__nv_bfloat16>(p, stream);
+    case kQuantFp16: return launch_t<__half>(p, stream);
+    case kQuantFp32: return launch_t<float>(p, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace b200fp8

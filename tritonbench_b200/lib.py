@@ -26,6 +26,9 @@ VARIANT_SKINNY = 3
 VARIANT_SIMT = 4
 FLAG_NO_TMA_STORE = 0x10
 FLAG_PDL = 0x20
+FLAG_OUT_FP16 = 0x40
+DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2
+QUANT_OPERATOR, QUANT_FP32 = 0, 1
 VARIANTS = {
     "auto": VARIANT_AUTO,
     "tc_1cta": VARIANT_TC_1CTA,
@@ -50,6 +53,7 @@ EXPORTED_SYMBOLS = (
     "b200fp8_gemm_rowwise_host",
     "b200fp8_gemm_rowwise_noalloc",
     "b200fp8_noalloc_status",
+    "b200fp8_row_quantize",
 )
 
 _lib: Optional[ctypes.CDLL] = None
@@ -103,6 +107,8 @@ def load() -> ctypes.CDLL:
     lib.b200fp8_gemm_rowwise_noalloc.argtypes = [c_void_p] * 6 + [c_int64] * 6 + [c_void_p]
     lib.b200fp8_noalloc_status.restype = ctypes.c_int
     lib.b200fp8_noalloc_status.argtypes = [ctypes.POINTER(c_uint32)]
+    lib.b200fp8_row_quantize.restype = ctypes.c_int
+    lib.b200fp8_row_quantize.argtypes = [c_void_p, ctypes.c_int, ctypes.c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p]
     if lib.b200fp8_abi_version() != 1:
         raise RuntimeError("libb200fp8.so has an ABI version this binding does not know")
     _lib = lib

@@ -57,8 +57,10 @@ def fp8_gemm_rowwise(
     tma_store: bool = True,
     workspace: Optional[torch.Tensor] = None,
     overlap: bool = False,
+    out_dtype: torch.dtype = torch.bfloat16,
 ) -> torch.Tensor:
     """Y = bf16((xq @ wq.T) * x_scale[:, None] * w_scale[None, :] (+ bias)), fp32 accumulation.
+    out_dtype=torch.float16 rounds the result to IEEE fp16 instead of bf16.
 
     overlap=True (decode shapes): the kernel may start before the previous kernel on the stream has
     finished and reads wq - nothing else - that early; pass it only when nothing in flight writes wq.
@@ -87,12 +89,14 @@ def fp8_gemm_rowwise(
         if bias.dtype != torch.bfloat16 or bias.numel() != n:
             raise ValueError("bias must be bfloat16 with N elements")
         bias = bias.contiguous()
+    if out_dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError("out_dtype must be bfloat16 or float16")
     if out is None:
-        out = torch.empty((m, n), dtype=torch.bfloat16, device=xq.device)
-    elif out.dtype != torch.bfloat16 or tuple(out.shape) != (m, n) or out.stride(1) != 1:
-        raise ValueError("out must be bfloat16 [M, N] with N contiguous")
+        out = torch.empty((m, n), dtype=out_dtype, device=xq.device)
+    elif out.dtype != out_dtype or tuple(out.shape) != (m, n) or out.stride(1) != 1:
+        raise ValueError(f"out must be {out_dtype} [M, N] with N contiguous")
 
-    flags = _flags(variant, tma_store, overlap)
+    flags = _flags(variant, tma_store, overlap) | (_lib.FLAG_OUT_FP16 if out_dtype == torch.float16 else 0)
     lib = _lib.load()
     if workspace is None:
         workspace = get_workspace(xq.device, workspace_bytes(m, n, k, flags))
@@ -107,8 +111,51 @@ def fp8_gemm_rowwise(
     return out
 
 
+def fp8_row_quantize(x: torch.Tensor, recipe: str = "operator") -> Tuple[torch.Tensor, torch.Tensor]:
+    """CUDA rowwise quantiser: (xq float8_e4m3fn [R, C], scale float32 [R]).
+
+    recipe="operator" is the reference's `fp8_row_quantize` (operator.py:136-145) bit for bit, for
+    bf16 / fp16 / fp32 x; recipe="fp32" is scale = max(rowabsmax, 1e-12) / 448 on fp32 x."""
+    _require_cuda(x, "x")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be [rows, cols] with cols contiguous")
+    dtypes = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16, torch.float32: _lib.DTYPE_FP32}
+    if x.dtype not in dtypes:
+        raise ValueError(f"unsupported dtype {x.dtype}")
+    recipes = {"operator": _lib.QUANT_OPERATOR, "fp32": _lib.QUANT_FP32}
+    if recipe not in recipes:
+        raise ValueError(f"unknown recipe {recipe!r}")
+    rows, cols = x.shape
+    q = torch.empty((rows, cols), dtype=torch.uint8, device=x.device)
+    scale = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    status = _lib.load().b200fp8_row_quantize(
+        x.data_ptr(), dtypes[x.dtype], recipes[recipe], rows, cols, x.stride(0), q.data_ptr(), q.stride(0),
+        scale.data_ptr(), torch.cuda.current_stream(x.device).cuda_stream,
+    )
+    _lib.check(status, f"b200fp8_row_quantize({rows}x{cols}, {x.dtype}, {recipe})")
+    return q.view(torch.float8_e4m3fn), scale
+
+
+def fp8_gemm(a: torch.Tensor, b: torch.Tensor, scale_a=None, scale_b=None, out_dtype: torch.dtype = torch.float16,
+             **kw) -> torch.Tensor:
+    """The call of TritonBench's `fp8_gemm` operator, `torch._scaled_mm(a, b, scale_a, scale_b, out_dtype=...)`
+    (tritonbench/operators/fp8_gemm/fp8_gemm.py:88-101): a [M, K] e4m3 row-major, b [K, N] e4m3 column-major
+    (b.T contiguous), scales per tensor (scalars or None = 1.0) or per row / column ([M, 1] and [1, N])."""
+    if b.dim() != 2 or b.stride(0) != 1:
+        raise ValueError("b must be [K, N] with K contiguous (a transposed view of a row-major [N, K] tensor)")
+    m, n = a.shape[0], b.shape[1]
+
+    def vec(s, count):
+        if s is None:
+            return torch.ones(count, dtype=torch.float32, device=a.device)
+        s = torch.as_tensor(s, dtype=torch.float32, device=a.device)
+        return s.reshape(-1).expand(count).contiguous() if s.numel() == 1 else s.reshape(count).contiguous()
+
+    return fp8_gemm_rowwise(a, b.t(), vec(scale_a, m), vec(scale_b, n), out_dtype=out_dtype, **kw)
+
+
 def make_gemm_fn(xq, wq, x_scale, w_scale, bias=None, variant: str = "auto", reuse_out: bool = False,
-                 overlap: bool = False) -> Callable:
+                 overlap: bool = False, out_dtype: torch.dtype = torch.bfloat16) -> Callable:
     """Zero-argument closure in the shape the TritonBench harness wants from a backend
     (triton_op.py:765-785).  The workspace is allocated here, outside any timed or captured
     region; each call of the closure only enqueues the kernel."""
@@ -116,10 +163,11 @@ def make_gemm_fn(xq, wq, x_scale, w_scale, bias=None, variant: str = "auto", reu
     n = wq.shape[0]
     flags = _flags(variant, True)
     ws = get_workspace(xq.device, workspace_bytes(m, n, k, flags))
-    out = torch.empty((m, n), dtype=torch.bfloat16, device=xq.device) if reuse_out else None
+    out = torch.empty((m, n), dtype=out_dtype, device=xq.device) if reuse_out else None
 
     def fn():
-        return fp8_gemm_rowwise(xq, wq, x_scale, w_scale, bias, out=out, variant=variant, workspace=ws, overlap=overlap)
+        return fp8_gemm_rowwise(xq, wq, x_scale, w_scale, bias, out=out, variant=variant, workspace=ws, overlap=overlap,
+                                out_dtype=out_dtype)
 
     return fn
 

@@ -1,6 +1,8 @@
 """Input side of the operator: rowwise e4m3 quantisation and the seeded synthetic inputs of the
-benchmark configurations.  Runs on whatever device the tensors are on (input generation is untimed
-set-up in the reference as well: tritonbench/operators/fp8_gemm_rowwise/operator.py:280-297).
+benchmark configurations (input generation is untimed set-up in the reference as well:
+tritonbench/operators/fp8_gemm_rowwise/operator.py:280-297).  CUDA tensors go through the library's
+fused quantiser kernel (b200fp8_row_quantize); CPU tensors - fixtures, tests, the CPU benchmark legs -
+through the torch expressions below, which produce the same bits.
 """
 from typing import Optional, Tuple
 
@@ -14,6 +16,10 @@ def fp8_row_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Same contract as the reference's `fp8_row_quantize` (operator.py:136-145): multiplier
     448 / clamp(rowmax, 1e-12) in x's dtype, clamp, cast to float8_e4m3fn, return (xq, 1/multiplier
     as float32)."""
+    if x.is_cuda:
+        from . import ops
+
+        return ops.fp8_row_quantize(x, recipe="operator")  # one fused kernel, same bits
     row_max = x.abs().amax(dim=1)
     mult = E4M3_MAX / row_max.clamp(min=EPS)
     if x.dtype is torch.float16:
@@ -25,6 +31,10 @@ def fp8_row_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
 def fp8_row_quantize_fp32(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Benchmark recipe: scale = max(rowabsmax, 1e-12) / 448 in fp32; xq = e4m3(clamp(x / scale))."""
     x = x.to(torch.float32)
+    if x.is_cuda:
+        from . import ops
+
+        return ops.fp8_row_quantize(x, recipe="fp32")
     scale = x.abs().amax(dim=1).clamp(min=EPS) / E4M3_MAX
     xq = (x / scale[:, None]).clamp(min=-E4M3_MAX, max=E4M3_MAX).to(torch.float8_e4m3fn)
     return xq, scale

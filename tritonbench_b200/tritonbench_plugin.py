@@ -99,6 +99,37 @@ def scaled_mm(self, xq, wq, x_scale, w_scale, bias) -> Callable:
     return fn
 
 
+def b200_fp8_gemm(self, a, b) -> Callable:
+    """Backend for the sibling operator `fp8_gemm` (tritonbench/operators/fp8_gemm/fp8_gemm.py:47-101): the same
+    kernels with unit scales; bf16 output with `--scaling_rowwise`, fp16 output with per-tensor scales, exactly
+    as the operator's own `torch_fp8_gemm` baseline chooses."""
+    if not a.is_cuda:
+        raise NotImplementedError("b200 backend runs on CUDA devices only; there is no CPU path")
+    from . import ops
+
+    rowwise = bool(getattr(self.extra_args, "scaling_rowwise", False))
+    out_dtype = torch.bfloat16 if rowwise else torch.float16
+    m, n = a.shape[0], b.shape[1]
+    ones_m = torch.ones(m, dtype=torch.float32, device=a.device)
+    ones_n = torch.ones(n, dtype=torch.float32, device=a.device)
+    overlap = m <= 128 and os.environ.get("B200FP8_OVERLAP", "1") != "0"
+    return ops.make_gemm_fn(a, b.t(), ones_m, ones_n, None, overlap=overlap, out_dtype=out_dtype)
+
+
+def register_fp8_gemm():
+    """Add the backend to the `fp8_gemm` operator.  Returns the operator class."""
+    from tritonbench.utils.triton_op import REGISTERED_BENCHMARKS, register_benchmark
+
+    module = importlib.import_module("tritonbench.operators.fp8_gemm.fp8_gemm")
+    cls = module.Operator
+    if BACKEND not in REGISTERED_BENCHMARKS.get("fp8_gemm", {}):
+        register_benchmark(operator_name="fp8_gemm", func_name=BACKEND, label="b200", enabled=torch.cuda.is_available())(
+            b200_fp8_gemm
+        )
+        setattr(cls, BACKEND, b200_fp8_gemm)
+    return cls
+
+
 def _wrap_init(cls) -> None:
     stock_init = cls.__init__
     if getattr(stock_init, "__b200_wrapped__", False):
@@ -157,8 +188,10 @@ def run(argv: List[str]):
     from tritonbench.utils.parser import get_parser
 
     args, extra = get_parser().parse_known_args(argv)
-    if args.op != OP_NAME:
-        raise SystemExit(f"this plugin serves --op {OP_NAME} only")
+    if args.op == "fp8_gemm":
+        register_fp8_gemm()
+    elif args.op != OP_NAME:
+        raise SystemExit(f"this plugin serves --op {OP_NAME} and --op fp8_gemm only")
     opbench = load_opbench_by_name(args.op)(tb_args=args, extra_args=extra)
     try:
         opbench.run(args.warmup, args.iter)
