@@ -115,6 +115,21 @@ int b200fp8_gemm_rowwise_noalloc(const void* xq, const void* wq, const float* x_
 int b200fp8_noalloc_status(uint32_t* device_status);
 
 /*
+ * Grouped form (mixture-of-experts): the rows of xq [M_total, K] are partitioned, in order, into num_groups
+ * groups of group_rows[g] rows (an int32 array in DEVICE memory, read by the kernel: no host round trip when
+ * the sizes come from a router kernel); group g is multiplied with rows [g*N, (g+1)*N) of the stacked
+ * wq [num_groups*N, K]; x_scale [M_total], w_scale [num_groups*N]; y [M_total, N].  Rows beyond the sum of the
+ * group sizes are left untouched.  Needs only the workspace header (256 bytes).
+ * Replaces: `grouped_gemm_fp8_rowwise(group_A, group_B, m_sizes, a_scale, b_scale)` and
+ * `torch.ops.fbgemm.f8f8bf16_rowwise_grouped_stacked` in
+ * tritonbench/operators/fp8_gemm_rowwise_grouped/operator.py:412-470.
+ */
+int b200fp8_gemm_rowwise_grouped(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
+                                 const int32_t* group_rows, int64_t num_groups, void* y_bf16, int64_t M_total,
+                                 int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, void* workspace,
+                                 size_t workspace_bytes, uint32_t flags, void* cuda_stream);
+
+/*
  * Rowwise e4m3 quantiser: x [rows, cols] (row pitch ldx ELEMENTS) -> q [rows, cols] e4m3 bytes (row pitch ldq
  * bytes) and scale [rows] fp32 such that x ~ float(q) * scale.  One pass over HBM, asynchronous on the stream.
  *   x_dtype  B200FP8_DTYPE_BF16 / _FP16 / _FP32

@@ -111,6 +111,24 @@ def gemm_rowwise(
     return y if keep_fp32 else y.to(out_dtype)
 
 
+def gemm_rowwise_grouped(xq, wq, m_sizes, x_scale, w_scale) -> torch.Tensor:
+    """Grouped form (tritonbench/operators/fp8_gemm_rowwise_grouped/operator.py:412-470, 547-580): rows of
+    xq [M_total, K] split in order into groups of m_sizes[g] rows; group g uses rows [g*N, (g+1)*N) of the stacked
+    wq [G*N, K].  Plain loop over the groups with `gemm_rowwise`; rows past the groups stay zero."""
+    sizes = [int(v) for v in m_sizes.cpu().tolist()]
+    groups = len(sizes)
+    n = wq.shape[0] // groups
+    y = torch.zeros((xq.shape[0], n), dtype=torch.bfloat16)
+    r0 = 0
+    for g, rows in enumerate(sizes):
+        if rows > 0:
+            y[r0 : r0 + rows] = gemm_rowwise(
+                xq[r0 : r0 + rows], wq[g * n : (g + 1) * n], x_scale[r0 : r0 + rows], w_scale[g * n : (g + 1) * n]
+            )
+        r0 += rows
+    return y
+
+
 def bf16_ulp(v: torch.Tensor) -> torch.Tensor:
     """Spacing of bf16 numbers at |v|: 2^(floor(log2|v|) - 7); the smallest normal's ulp below that."""
     a = v.abs().to(torch.float32).clamp(min=2.0 ** -126)

@@ -372,6 +372,54 @@ def test_fp8_gemm_call_with_per_tensor_and_unit_scales(cuda_device):
         ops.fp8_gemm(a.cuda(), b.cuda().contiguous())
 
 
+GROUPED_CASES = [
+    # (m_sizes, N, K)
+    ([512, 512], 1024, 1024),
+    ([256, 256, 256, 256], 1024, 1024),
+    ([100, 0, 333, 1, 130], 520, 400),     # ragged, an empty group, a one-row group, tails everywhere
+    ([129, 127, 31, 33], 264, 144),
+    ([2048, 2048, 2048, 2048], 4096, 4096),  # the operator's (8192, 4096, 4096) shape with 4 groups
+]
+
+
+@pytest.mark.parametrize("case", GROUPED_CASES)
+def test_grouped_gemm(cuda_device, case):
+    ops = _ops()
+    sizes, n, k = case
+    groups, m_total = len(sizes), sum(sizes)
+    from tritonbench_b200 import quantize
+
+    xq, xs = quantize.make_quantized(m_total, k, seed=31)
+    wq, ws = quantize.make_quantized(groups * n, k, seed=32, std=0.05)
+    m_sizes = torch.tensor(sizes, dtype=torch.int32)
+    ref = orc.gemm_rowwise_grouped(xq, wq, m_sizes, xs, ws)
+    y = ops.fp8_gemm_rowwise_grouped(*_gpu(xq, wq, m_sizes, xs, ws))
+    ops.check_device_status()
+    _assert_close(y, ref, f"grouped {case}")
+    # no group may write into its neighbour's rows: equal to the per-group plain GEMMs bit for bit
+    r0 = 0
+    for g, rows in enumerate(sizes):
+        if rows:
+            one = ops.fp8_gemm_rowwise(*_gpu(xq[r0:r0 + rows], wq[g * n:(g + 1) * n], xs[r0:r0 + rows], ws[g * n:(g + 1) * n]),
+                                       variant="tc_1cta")
+            assert torch.equal(y[r0:r0 + rows], one), f"group {g}"
+        r0 += rows
+
+
+def test_grouped_gemm_leaves_rows_beyond_the_groups_untouched(cuda_device):
+    ops = _ops()
+    from tritonbench_b200 import quantize
+
+    xq, xs = quantize.make_quantized(300, 256, seed=1)
+    wq, ws = quantize.make_quantized(2 * 264, 256, seed=2)
+    m_sizes = torch.tensor([100, 120], dtype=torch.int32)
+    out = torch.full((300, 264), 7.0, dtype=torch.bfloat16, device="cuda")
+    y = ops.fp8_gemm_rowwise_grouped(*_gpu(xq, wq, m_sizes, xs, ws), out=out)
+    ref = orc.gemm_rowwise_grouped(xq, wq, m_sizes, xs, ws)
+    _assert_close(y[:220], ref[:220], "grouped prefix")
+    assert bool((y[220:] == 7.0).all())
+
+
 def test_host_buffer_entry_point(cuda_device):
     ops = _ops()
     for variant, shape in (("auto", (384, 768, 512)), ("auto", (16, 2304, 2048))):

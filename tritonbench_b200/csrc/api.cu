@@ -344,6 +344,65 @@ int b200fp8_noalloc_status(uint32_t* device_status) {
   return b200fp8_query_status(scratch, device_status);
 }
 
+int b200fp8_gemm_rowwise_grouped(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
+                                 const int32_t* group_rows, int64_t num_groups, void* y_bf16, int64_t M_total,
+                                 int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, void* workspace,
+                                 size_t workspace_bytes, uint32_t flags, void* cuda_stream) {
+  if (xq == nullptr || wq == nullptr || x_scale == nullptr || w_scale == nullptr || y_bf16 == nullptr ||
+      workspace == nullptr || group_rows == nullptr) {
+    return B200FP8_BAD_ARG;
+  }
+  int st = check_sizes(M_total, N, K);
+  if (st != B200FP8_OK) return st;
+  if (num_groups <= 0 || num_groups > 4096) return B200FP8_BAD_ARG;
+  if (num_groups * N > 0x7FFFFF00ll) return B200FP8_TOO_LARGE;
+  if (ldx < K || ldw < K || ldy < N) return B200FP8_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0 || workspace_bytes < B200FP8_WORKSPACE_HEADER_BYTES) {
+    return B200FP8_BAD_ARG;
+  }
+  const uint32_t variant = flags & B200FP8_VARIANT_MASK;
+  if (variant != B200FP8_VARIANT_AUTO && variant != B200FP8_VARIANT_TC_1CTA) return B200FP8_BAD_ARG;
+  DeviceInfo dev;
+  st = device_info(&dev);
+  if (st != B200FP8_OK) return st;
+  if (dev.cc_major != 10) return B200FP8_UNSUPPORTED_ARCH;
+  if (!tma_loadable(K, ldx, ldw, xq, wq)) return B200FP8_UNSUPPORTED_ALIGNMENT;
+
+  CUtensorMap tm_x, tm_w, tm_y;
+  memset(&tm_y, 0, sizeof(tm_y));
+  st = encode_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, M_total, K, ldx, TcGeometry::kBlockK, TcGeometry::kBlockM);
+  if (st != B200FP8_OK) return st;
+  st = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, num_groups * N, K, ldw, TcGeometry::kBlockK,
+                 TcGeometry::kBlockN);
+  if (st != B200FP8_OK) return st;
+  const bool tma_store = (ldy % 8 == 0) && aligned16(y_bf16) && (flags & B200FP8_FLAG_NO_TMA_STORE) == 0;
+  if (tma_store) {
+    st = encode_2d(&tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y_bf16, M_total, N, ldy * 2, TcGeometry::kStoreCols,
+                   TcGeometry::kStoreRows);
+    if (st != B200FP8_OK) return st;
+  }
+  TcParams tp = {};
+  tp.x_scale = x_scale;
+  tp.w_scale = w_scale;
+  tp.bias = nullptr;
+  tp.y = static_cast<__nv_bfloat16*>(y_bf16);
+  tp.M = static_cast<int>(M_total);
+  tp.N = static_cast<int>(N);
+  tp.K = static_cast<int>(K);
+  tp.ldy = ldy;
+  tp.use_tma_store = tma_store ? 1 : 0;
+  tp.out_fp16 = (flags & B200FP8_FLAG_OUT_FP16) ? 1 : 0;
+  tp.group_m = 8;
+  tp.num_groups = static_cast<int>(num_groups);
+  tp.group_rows = group_rows;
+  tp.status = static_cast<uint32_t*>(workspace);
+  // the group sizes live on the device, so the tile count is not known here: one CTA per SM, each
+  // walks the tile list it derives from the sizes
+  const int64_t max_tiles = ((M_total + 127) / 128 + num_groups) * ((N + 255) / 256);
+  const int ctas = static_cast<int>(max_tiles < dev.sm_count ? max_tiles : dev.sm_count);
+  return note_cuda(launch_gemm_tc<1>(tm_x, tm_w, tm_y, tp, ctas, static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int b200fp8_row_quantize(const void* x, int x_dtype, int recipe, int64_t rows, int64_t cols, int64_t ldx, void* q,
                          int64_t ldq, float* scale, void* cuda_stream) {
   if (x == nullptr || q == nullptr || scale == nullptr) return B200FP8_BAD_ARG;

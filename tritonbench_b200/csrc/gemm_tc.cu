@@ -13,6 +13,12 @@
 //   warps 2-5  epilogue: tcgen05.ld one TMEM lane quarter each, multiply by x_scale[m]*w_scale[n],
 //              add bias, round to bf16, stage 32x64 boxes in swizzled shared memory, TMA-store.
 //
+// Grouped mode (single-CTA variant; a mixture-of-experts layer): the rows of X are partitioned into
+// groups by a device array of group sizes, group g multiplies rows g*N..(g+1)*N of the stacked W.
+// The tile list is then built on the device from the group sizes (no host round trip); a tile never
+// writes rows of the next group: boxes that straddle a group's end are stored with plain predicated
+// stores instead of TMA.
+//
 // The accumulator is double buffered in TMEM, so the epilogue of tile i overlaps the main loop
 // of tile i+1.  Every mbarrier wait is bounded (ptx.cuh: mbar_wait); on a time-out the kernel
 // records a status word and all roles fall through to the common exit, which frees TMEM.
@@ -49,6 +55,60 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n,
   return c;
 }
 
+// Everything a role needs to know about one tile.
+struct TileInfo {
+  int row0;       // first row of X / Y of the CTA's 128-row block
+  int row_limit;  // rows >= row_limit are not this tile's to write (end of M, or end of the group)
+  int col0;       // first column of Y
+  int w_row0;     // first row of W of the CTA's share
+  int scale_col0; // index of w_scale / bias of column col0 (differs from col0 in grouped mode)
+};
+
+struct TileSpace {
+  int M, N, tiles_n, group_m;
+  int num_groups;         // 0: plain GEMM
+  const int* group_rows;  // [num_groups] rows of X per group (device memory)
+  int plain_tiles_m;
+};
+
+__device__ __forceinline__ int count_tiles(const TileSpace& ts, int tile_m) {
+  if (ts.num_groups == 0) return ts.plain_tiles_m * ts.tiles_n;
+  int total = 0;
+  for (int g = 0; g < ts.num_groups; ++g) total += ((__ldg(ts.group_rows + g) + tile_m - 1) / tile_m) * ts.tiles_n;
+  return total;
+}
+
+template <int kCtaGroup>
+__device__ __forceinline__ TileInfo tile_info(const TileSpace& ts, int t, uint32_t cta_rank) {
+  using Cfg = TcConfig<kCtaGroup>;
+  TileInfo ti;
+  if (ts.num_groups == 0) {
+    const TileCoord tc = tile_coord(t, ts.plain_tiles_m, ts.tiles_n, ts.group_m);
+    ti.row0 = tc.m_tile * Cfg::kTileM + static_cast<int>(cta_rank) * Cfg::kBlockM;
+    ti.row_limit = ts.M;
+    ti.col0 = tc.n_tile * Cfg::kBlockN;
+    ti.w_row0 = ti.col0 + static_cast<int>(cta_rank) * Cfg::kRowsW;
+    ti.scale_col0 = ti.col0;
+    return ti;
+  }
+  int first_tile = 0, first_row = 0;
+  int g = 0, rows = 0, tiles_m = 0;
+  for (; g < ts.num_groups; ++g) {
+    rows = __ldg(ts.group_rows + g);
+    tiles_m = (rows + Cfg::kTileM - 1) / Cfg::kTileM;
+    if (t < first_tile + tiles_m * ts.tiles_n) break;
+    first_tile += tiles_m * ts.tiles_n;
+    first_row += rows;
+  }
+  const TileCoord tc = tile_coord(t - first_tile, tiles_m, ts.tiles_n, ts.group_m);
+  ti.row0 = first_row + tc.m_tile * Cfg::kTileM + static_cast<int>(cta_rank) * Cfg::kBlockM;
+  ti.row_limit = min(first_row + rows, ts.M);
+  ti.col0 = tc.n_tile * Cfg::kBlockN;
+  ti.w_row0 = g * ts.N + ti.col0 + static_cast<int>(cta_rank) * Cfg::kRowsW;
+  ti.scale_col0 = g * ts.N + ti.col0;
+  return ti;
+}
+
 template <int kCtaGroup>
 __global__ void __launch_bounds__(TcGeometry::kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
@@ -81,9 +141,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
   const int cluster_id = blockIdx.x / kCtaGroup;
   const int num_clusters = gridDim.x / kCtaGroup;
 
-  const int tiles_m = (p.M + Cfg::kTileM - 1) / Cfg::kTileM;
-  const int tiles_n = (p.N + Cfg::kBlockN - 1) / Cfg::kBlockN;
-  const int num_tiles = tiles_m * tiles_n;
+  TileSpace ts;
+  ts.M = p.M;
+  ts.N = p.N;
+  ts.tiles_n = (p.N + Cfg::kBlockN - 1) / Cfg::kBlockN;
+  ts.group_m = p.group_m;
+  ts.num_groups = kPair ? 0 : p.num_groups;
+  ts.group_rows = p.group_rows;
+  ts.plain_tiles_m = (p.M + Cfg::kTileM - 1) / Cfg::kTileM;
+  const int num_tiles = count_tiles(ts, Cfg::kTileM);
   const int num_kb = (p.K + Cfg::kBlockK - 1) / Cfg::kBlockK;
 
   if (threadIdx.x == 0) {
@@ -122,9 +188,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-        const TileCoord tc = tile_coord(t, tiles_m, tiles_n, p.group_m);
-        const int row_x = tc.m_tile * Cfg::kTileM + static_cast<int>(cta_rank) * Cfg::kBlockM;
-        const int row_w = tc.n_tile * Cfg::kBlockN + static_cast<int>(cta_rank) * Cfg::kRowsW;
+        const TileInfo ti = tile_info<kCtaGroup>(ts, t, cta_rank);
+        const int row_x = ti.row0;
+        const int row_w = ti.w_row0;
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait<kPair>(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty);
           if (!ok) break;
@@ -207,13 +273,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     uint32_t store_count = 0;
     bool ok = true;
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local_tile) {
-      const TileCoord tc = tile_coord(t, tiles_m, tiles_n, p.group_m);
+      const TileInfo ti = tile_info<kCtaGroup>(ts, t, cta_rank);
       const uint32_t buf = local_tile & 1u;
       const uint32_t use = (local_tile >> 1) & 1u;
-      const int row0 = tc.m_tile * Cfg::kTileM + static_cast<int>(cta_rank) * Cfg::kBlockM + quarter * 32;
+      const int row0 = ti.row0 + quarter * 32;
       const int row = row0 + lane;
-      const int col0 = tc.n_tile * Cfg::kBlockN;
-      const float xs = row < p.M ? __ldg(p.x_scale + row) : 0.0f;
+      const int col0 = ti.col0;
+      const int row_limit = ti.row_limit;
+      const float* w_scale = p.w_scale + (ti.scale_col0 - col0);  // w_scale[column] for this tile's group
+      const __nv_bfloat16* bias = p.bias != nullptr ? p.bias + (ti.scale_col0 - col0) : nullptr;
+      // a box whose 32 rows straddle the end of a group must not be stored whole
+      const bool box_rows_whole = ts.num_groups == 0 || row0 + Cfg::kStoreRows <= row_limit;
+      const bool tma_box = p.use_tma_store && box_rows_whole;
+      const float xs = row < row_limit ? __ldg(p.x_scale + row) : 0.0f;
 
       ok = mbar_wait<kPair>(bar_tmem_full + 8 * buf, use, abort_flag, p.status, kSiteEpiTmemFull);
       ok = __all_sync(0xffffffffu, ok) != 0;  // the whole warp leaves together
@@ -236,7 +308,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
       for (int box = 0; box < Cfg::kBlockN / Cfg::kStoreCols; ++box) {
         const int box_col = col0 + box * Cfg::kStoreCols;
         const uint32_t sbuf = stage_buf + (store_count & 1u) * (Cfg::kStoreRows * Cfg::kStoreCols * 2);
-        if (p.use_tma_store) {
+        if (tma_box) {
           // the buffer about to be rewritten was the source of the store before last
           if (lane == 0) tma_store_wait_read<1>();
           __syncwarp();
@@ -260,11 +332,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
           }
           const int c_first = box_col + half * 32;
           float v[32];
-          const bool vec_ok = (c_first + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(p.w_scale + c_first) & 15u) == 0);
+          const bool vec_ok = (c_first + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(w_scale + c_first) & 15u) == 0);
           if (vec_ok) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const float4 ws = __ldg(reinterpret_cast<const float4*>(p.w_scale + c_first) + j);
+              const float4 ws = __ldg(reinterpret_cast<const float4*>(w_scale + c_first) + j);
               v[4 * j + 0] = __uint_as_float(acc[4 * j + 0]) * (xs * ws.x);
               v[4 * j + 1] = __uint_as_float(acc[4 * j + 1]) * (xs * ws.y);
               v[4 * j + 2] = __uint_as_float(acc[4 * j + 2]) * (xs * ws.z);
@@ -273,17 +345,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const float ws = (c_first + j < p.N) ? __ldg(p.w_scale + c_first + j) : 0.0f;
+              const float ws = (c_first + j < p.N) ? __ldg(w_scale + c_first + j) : 0.0f;
               v[j] = __uint_as_float(acc[j]) * (xs * ws);
             }
           }
-          if (p.bias != nullptr) {
+          if (bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              if (c_first + j < p.N) v[j] += __bfloat162float(p.bias[c_first + j]);
+              if (c_first + j < p.N) v[j] += __bfloat162float(bias[c_first + j]);
             }
           }
-          if (p.use_tma_store) {
+          if (tma_box) {
             // row `lane` of the box is 128 bytes; 16-byte chunk j sits at chunk (j ^ (lane & 7))
             const uint32_t row_addr = sbuf + lane * 128;
 #pragma unroll
@@ -299,7 +371,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                              pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
               }
             }
-          } else if (row < p.M) {
+          } else if (row < row_limit) {
             uint16_t* dst = reinterpret_cast<uint16_t*>(p.y) + static_cast<long long>(row) * p.ldy + c_first;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -307,10 +379,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
             }
           }
         }
-        if (p.use_tma_store) {
+        if (tma_box) {
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0 && row0 < p.M && box_col < p.N) {
+          if (lane == 0 && row0 < row_limit && box_col < p.N) {
             tma_store_2d(&tm_y, sbuf, box_col, row0);
           }
           if (lane == 0) tma_store_commit();

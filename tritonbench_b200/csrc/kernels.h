@@ -45,6 +45,8 @@ struct TcParams {
   int use_tma_store;   // 0: plain predicated stores
   int out_fp16;        // 0: Y holds bf16, 1: Y holds IEEE fp16
   int group_m;         // tile-rasterisation group height (tiles)
+  int num_groups;      // 0: plain GEMM.  >0: rows of X are partitioned into groups (single-CTA variant)
+  const int* group_rows;  // [num_groups] rows per group, device memory; group g uses W rows [g*N, (g+1)*N)
   uint32_t* status;    // device status word
 #ifdef B200FP8_DEBUG_KNOBS
   int debug;

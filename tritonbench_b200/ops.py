@@ -136,6 +136,37 @@ def fp8_row_quantize(x: torch.Tensor, recipe: str = "operator") -> Tuple[torch.T
     return q.view(torch.float8_e4m3fn), scale
 
 
+def fp8_gemm_rowwise_grouped(
+    xq: torch.Tensor, wq: torch.Tensor, m_sizes: torch.Tensor, x_scale: torch.Tensor, w_scale: torch.Tensor,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Grouped GEMM in the argument order of the reference's
+    `grouped_gemm_fp8_rowwise(group_A, group_B, m_sizes, a_scale, b_scale)`
+    (tritonbench/operators/fp8_gemm_rowwise_grouped/operator.py:412-432): xq [M_total, K], wq [G*N, K] stacked,
+    m_sizes int32 [G] on the device (never copied to the host), scales per row; returns bf16 [M_total, N]."""
+    for t, name in ((xq, "xq"), (wq, "wq"), (m_sizes, "m_sizes"), (x_scale, "x_scale"), (w_scale, "w_scale")):
+        _require_cuda(t, name)
+    if m_sizes.dtype != torch.int32 or m_sizes.dim() != 1 or not m_sizes.is_contiguous():
+        raise ValueError("m_sizes must be a contiguous int32 vector")
+    groups = m_sizes.numel()
+    m_total, k = xq.shape
+    if wq.shape[0] % groups != 0 or wq.shape[1] != k:
+        raise ValueError("wq must be [G*N, K]")
+    n = wq.shape[0] // groups
+    if x_scale.numel() != m_total or w_scale.numel() != wq.shape[0]:
+        raise ValueError("x_scale must have M_total elements and w_scale G*N elements")
+    if out is None:
+        out = torch.empty((m_total, n), dtype=torch.bfloat16, device=xq.device)
+    workspace = get_workspace(xq.device, _lib.WORKSPACE_HEADER_BYTES)
+    status = _lib.load().b200fp8_gemm_rowwise_grouped(
+        xq.data_ptr(), wq.data_ptr(), x_scale.contiguous().data_ptr(), w_scale.contiguous().data_ptr(), m_sizes.data_ptr(),
+        groups, out.data_ptr(), m_total, n, k, xq.stride(0), wq.stride(0), out.stride(0),
+        workspace.data_ptr(), workspace.numel(), 0, torch.cuda.current_stream(xq.device).cuda_stream,
+    )
+    _lib.check(status, f"b200fp8_gemm_rowwise_grouped(M={m_total}, G={groups}, N={n}, K={k})")
+    return out
+
+
 def fp8_gemm(a: torch.Tensor, b: torch.Tensor, scale_a=None, scale_b=None, out_dtype: torch.dtype = torch.float16,
              **kw) -> torch.Tensor:
     """The call of TritonBench's `fp8_gemm` operator, `torch._scaled_mm(a, b, scale_a, scale_b, out_dtype=...)`

@@ -130,6 +130,52 @@ def register_fp8_gemm():
     return cls
 
 
+def b200_grouped(self, group_A, group_B, m_sizes, a_scale, b_scale) -> Callable:
+    """Backend for `fp8_gemm_rowwise_grouped` (tritonbench/operators/fp8_gemm_rowwise_grouped/operator.py:412-470)."""
+    if not group_A.is_cuda:
+        raise NotImplementedError("b200 backend runs on CUDA devices only; there is no CPU path")
+    from . import ops
+
+    groups = m_sizes.numel()
+    out = torch.empty((group_A.shape[0], group_B.shape[0] // groups), dtype=torch.bfloat16, device=group_A.device)
+    sizes = m_sizes.to(torch.int32).contiguous()
+    ops.get_workspace(group_A.device, 256)  # allocated here, outside the timed / captured region
+    return lambda: ops.fp8_gemm_rowwise_grouped(group_A, group_B, sizes, a_scale, b_scale, out=out)
+
+
+def torch_dequant_grouped_ref(self, group_A, group_B, m_sizes, a_scale, b_scale) -> Callable:
+    """fp32 dequantise-then-matmul per group: the baseline column where FBGEMM's grouped kernels are absent."""
+    sizes = [int(v) for v in m_sizes.cpu().tolist()]
+    n = group_B.shape[0] // len(sizes)
+
+    def fn():
+        outs, r0 = [], 0
+        for g, rows in enumerate(sizes):
+            x = group_A[r0 : r0 + rows].to(torch.float32) * a_scale[r0 : r0 + rows, None]
+            w = group_B[g * n : (g + 1) * n].to(torch.float32) * b_scale[g * n : (g + 1) * n, None]
+            outs.append((x @ w.T).to(torch.bfloat16))
+            r0 += rows
+        return torch.cat(outs)
+
+    return fn
+
+
+def register_grouped():
+    """Add the backends to the `fp8_gemm_rowwise_grouped` operator.  Returns the operator class."""
+    _install_fbgemm_standin()
+    from tritonbench.utils.triton_op import REGISTERED_BENCHMARKS, register_benchmark
+
+    op = "fp8_gemm_rowwise_grouped"
+    module = importlib.import_module(f"tritonbench.operators.{op}.operator")
+    cls = module.Operator
+    if BACKEND not in REGISTERED_BENCHMARKS.get(op, {}):
+        register_benchmark(operator_name=op, func_name=BACKEND, label="b200", enabled=torch.cuda.is_available())(b200_grouped)
+        setattr(cls, BACKEND, b200_grouped)
+        register_benchmark(operator_name=op, func_name="torch_dequant_ref", baseline=True)(torch_dequant_grouped_ref)
+        setattr(cls, "torch_dequant_ref", torch_dequant_grouped_ref)
+    return cls
+
+
 def _wrap_init(cls) -> None:
     stock_init = cls.__init__
     if getattr(stock_init, "__b200_wrapped__", False):
@@ -190,8 +236,12 @@ def run(argv: List[str]):
     args, extra = get_parser().parse_known_args(argv)
     if args.op == "fp8_gemm":
         register_fp8_gemm()
+    elif args.op == "fp8_gemm_rowwise_grouped":
+        register_grouped()
+        if args.atol is None and args.rtol is None:
+            args.atol, args.rtol = 1e-3, 1.6e-2
     elif args.op != OP_NAME:
-        raise SystemExit(f"this plugin serves --op {OP_NAME} and --op fp8_gemm only")
+        raise SystemExit(f"this plugin serves --op {OP_NAME}, fp8_gemm and fp8_gemm_rowwise_grouped only")
     opbench = load_opbench_by_name(args.op)(tb_args=args, extra_args=extra)
     try:
         opbench.run(args.warmup, args.iter)
