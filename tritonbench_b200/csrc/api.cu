@@ -2,7 +2,6 @@
 // variant, TMA descriptor encoding, workspace layout, and the host-buffer context.
 #include <cudaTypedefs.h>
 #include <stdio.h>
-#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -16,9 +15,6 @@ namespace {
 using namespace b200fp8;
 
 thread_local int g_last_cuda_error = 0;
-#ifdef B200FP8_DEBUG_KNOBS
-unsigned long long* g_debug_trace = nullptr;
-#endif
 
 struct DeviceInfo {
   bool known = false;
@@ -158,9 +154,6 @@ int check_sizes(int64_t M, int64_t N, int64_t K) {
 
 extern "C" {
 
-#ifdef B200FP8_DEBUG_KNOBS
-void b200fp8_debug_set_trace(void* p) { g_debug_trace = static_cast<unsigned long long*>(p); }
-#endif
 
 int b200fp8_abi_version(void) { return B200FP8_ABI_VERSION; }
 
@@ -251,9 +244,6 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
     kp.bias = bias;
     kp.y = y;
     kp.M = static_cast<int>(M);
-#ifdef B200FP8_DEBUG_KNOBS
-    if (getenv("B200FP8_EPI_M")) kp.M = atoi(getenv("B200FP8_EPI_M"));  // experiment: epilogue sees fewer tokens
-#endif
     kp.N = static_cast<int>(N);
     kp.K = static_cast<int>(K);
     kp.ldy = ldy;
@@ -262,9 +252,6 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
     off = (off + pl.skinny.counter_bytes + 255) & ~static_cast<size_t>(255);
     kp.partials = reinterpret_cast<float*>(ws + off);
     kp.status = status_word;
-#ifdef B200FP8_DEBUG_KNOBS
-    kp.trace = g_debug_trace;
-#endif
     return note_cuda(launch_gemm_skinny(tm_w, tm_x, kp, pl.skinny, stream));
   }
 
@@ -294,9 +281,6 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
   tp.out_fp16 = (flags & B200FP8_FLAG_OUT_FP16) ? 1 : 0;
   tp.group_m = pl.group_m;
   tp.status = status_word;
-#ifdef B200FP8_DEBUG_KNOBS
-  tp.debug = getenv("B200FP8_DEBUG") ? atoi(getenv("B200FP8_DEBUG")) : 0;
-#endif
   if (cta_group == 2) return note_cuda(launch_gemm_tc<2>(tm_x, tm_w, tm_y, tp, pl.num_ctas, stream));
   return note_cuda(launch_gemm_tc<1>(tm_x, tm_w, tm_y, tp, pl.num_ctas, stream));
 }

@@ -25,8 +25,6 @@
 // else (X, scales, bias, Y, workspace) only after griddepcontrol.wait, i.e. after the previous kernel
 // has completed.  Back-to-back decode GEMMs thus overlap one kernel's tail, where SMs finish at
 // different times, with the next kernel's prologue and first 192 KiB of weights per SM.
-#include <stdlib.h>
-
 #include "kernels.h"
 #include "ptx.cuh"
 #include "streamk.cuh"
@@ -44,9 +42,6 @@ SkinnyPlan make_skinny_plan(int M, int N, int K, int sm_count) {
   pl.tiles = (N + G::kRowsW - 1) / G::kRowsW;
   pl.kblocks = (K + G::kBlockK - 1) / G::kBlockK;
 
-#ifdef B200FP8_DEBUG_KNOBS
-  if (getenv("B200FP8_SKINNY_STAGES")) pl.stages = atoi(getenv("B200FP8_SKINNY_STAGES"));
-#endif
   // Whole waves of tiles are dealt out one tile per CTA (nothing to add across CTAs); only the
   // remainder, fewer tiles than CTAs, is cut along K into equal runs.  All of it when tiles < CTAs.
   pl.dp_waves = pl.tiles / sm_count;
@@ -84,16 +79,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                    const SkinnyParams p, const SkinnyShape sh) {
   using G = SkinnyGeometry;
 
-#ifdef B200FP8_DEBUG_KNOBS
-#define SK_TRACE(i) do { if (p.trace) p.trace[blockIdx.x * 8 + (i)] = globaltimer_ns(); } while (0)
-#else
-#define SK_TRACE(i) do {} while (0)
-#endif
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw_addr);
-  if (threadIdx.x == 0) SK_TRACE(0);
 
   const int stages = sh.stages;
   const int kblocks = sh.kblocks;
@@ -153,7 +142,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
   if (threadIdx.x == 0) griddep_launch_dependents();  // the next kernel does its own waiting
-  if (threadIdx.x == 0) SK_TRACE(1);
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
@@ -221,7 +209,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           ok = mbar_wait<false>(bar_full + 8 * stage, phase, abort_flag, p.status, kSiteMmaFull);
           if (!ok) break;
-          if (i == 0 && kb == sg.kb0) SK_TRACE(2);
           tc_fence_after_sync();
           const uint64_t a_desc = smem_desc_k_sw128(smem_a + stage * G::kBytesA);
           const uint64_t b_desc = smem_desc_k_sw128(smem_b + stage * bytes_b);
@@ -238,7 +225,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         if (!ok) break;
         tc_commit(bar_tmem_full + 8 * buf);
       }
-      SK_TRACE(3);
     }
   } else if (warp < 6) {
     // ------------------------- drain: TMEM -> Y or partial-sum slot -------------------------
@@ -322,7 +308,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       if (seen == parts - 1u) ok = post(sg.tile);
     }
     post(kMailDone);
-    if (quarter == 0 && lane == 0) SK_TRACE(4);
   } else {
     // ------------------- fix-up: add the parts of a split tile, scale, write Y -------------------
     const int quarter = warp & 3;
@@ -394,7 +379,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   if (warp == 1) {
     tmem_dealloc<1>(tmem_base, tmem_cols);
   }
-  if (threadIdx.x == 32) SK_TRACE(5);
 }
 
 }  // namespace

@@ -292,17 +292,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * Cfg::kBlockN;
-#ifdef B200FP8_DEBUG_KNOBS
-      if (p.debug & 1) {  // experiment: hand the accumulator back without reading it
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          if constexpr (kPair) mbar_arrive_cluster(tmem_empty_remote + 8 * buf);
-          else mbar_arrive(bar_tmem_empty + 8 * buf);
-        }
-        continue;
-      }
-#endif
 
 #pragma unroll 1
       for (int box = 0; box < Cfg::kBlockN / Cfg::kStoreCols; ++box) {

@@ -48,9 +48,6 @@ struct TcParams {
   int num_groups;      // 0: plain GEMM.  >0: rows of X are partitioned into groups (single-CTA variant)
   const int* group_rows;  // [num_groups] rows per group, device memory; group g uses W rows [g*N, (g+1)*N)
   uint32_t* status;    // device status word
-#ifdef B200FP8_DEBUG_KNOBS
-  int debug;
-#endif
 };
 
 template <int kCtaGroup>
@@ -111,9 +108,6 @@ struct SkinnyParams {
   float* partials;     // [num_ctas * segs_per_cta][tokens_pad][128] fp32
   uint32_t* counters;  // [tiles * 4], zero on entry, zero again on exit
   uint32_t* status;
-#ifdef B200FP8_DEBUG_KNOBS
-  unsigned long long* trace;
-#endif
 };
 
 cudaError_t launch_gemm_skinny(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const SkinnyParams& p,
