@@ -46,6 +46,7 @@ typedef enum b200fp8_status {
 #define B200FP8_VARIANT_TC_2CTA 2u   /* tcgen05 256x256x128 tiles, cta_group::2 CTA pair per tile         */
 #define B200FP8_VARIANT_SKINNY 3u    /* M <= 128: swap-AB tcgen05 stream-K, W streamed once from HBM      */
 #define B200FP8_VARIANT_SIMT 4u      /* CUDA-core kernel, any alignment; slow, used as an on-GPU cross-check */
+#define B200FP8_VARIANT_TC_SPLITK 5u /* few tiles, long K: 2 or 4 CTAs of a cluster split K, reduce over DSMEM    */
 #define B200FP8_VARIANT_MASK 0xFu
 #define B200FP8_FLAG_NO_TMA_STORE 0x10u /* tcgen05 variants: write Y with plain stores instead of TMA        */
 /* Decode kernel (M <= 128) only: launch with programmatic stream serialization, so the kernel may start

@@ -75,6 +75,26 @@ def test_tile_tails_large_m_kernels(cuda_device, variant, shape):
     _assert_close(_run(variant, xq, wq, xs, ws, tma_store=False), ref, f"{variant} {shape} plain stores")
 
 
+SPLITK_SHAPES = [(777, 1024, 8192), (256, 512, 4096), (129, 257, 144), (300, 520, 400), (128, 256, 128), (1, 8, 16),
+                 (512, 1024, 16384), (1000, 1001, 1040)]
+
+
+@pytest.mark.parametrize("shape", SPLITK_SHAPES)
+def test_cluster_split_k_kernel(cuda_device, shape):
+    """K split across the CTAs of a cluster, partial sums exchanged over distributed shared memory."""
+    m, n, k = shape
+    xq, wq, xs, ws = _inputs(m, n, k, seed=3 * m + k)
+    bias = (torch.randn(n, generator=torch.Generator().manual_seed(1)) * 10).to(torch.bfloat16)
+    ref = orc.gemm_rowwise(xq, wq, xs, ws)
+    y = _run("tc_splitk", xq, wq, xs, ws)
+    _assert_close(y, ref, f"tc_splitk {shape}")
+    assert torch.equal(_run("tc_splitk", xq, wq, xs, ws), y)  # fixed summation order: run-to-run identical
+    _assert_close(_run("tc_splitk", xq, wq, xs, ws, tma_store=False), ref, f"tc_splitk {shape} plain stores")
+    _assert_close(_run("tc_splitk", xq, wq, xs, ws, bias=bias), orc.gemm_rowwise(xq, wq, xs, ws, bias), "tc_splitk bias")
+    _assert_close(_run("tc_splitk", xq, wq, xs, ws, out_dtype=torch.float16),
+                  orc.gemm_rowwise(xq, wq, xs, ws, out_dtype=torch.float16), "tc_splitk fp16")
+
+
 SKINNY_SHAPES = [
     (1, 8, 16), (1, 256, 512), (3, 1000, 1040), (8, 2304, 2304), (16, 1024, 1024), (17, 520, 400), (33, 4096, 2304),
     (64, 4096, 2048), (100, 1000, 4096), (128, 2304, 6656), (127, 129, 144),

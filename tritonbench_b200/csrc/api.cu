@@ -88,6 +88,8 @@ struct Plan {
   bool tma_store;
   int num_ctas;      // tcgen05 variants
   int group_m;
+  int split;         // cluster split-K variant: CTAs per tile
+  int tiles;         // cluster split-K variant: 128x256 tiles
   SkinnyPlan skinny;  // skinny variant
   size_t workspace_bytes;
 };
@@ -98,11 +100,30 @@ bool tma_loadable(int64_t K, int64_t ldx, int64_t ldw, const void* xq, const voi
   return ldx % 16 == 0 && ldw % 16 == 0 && aligned16(xq) && aligned16(wq);
 }
 
+// Cost model for the few-tile case, in units of one k-block of main loop: waves x (k-blocks per CTA + fixed
+// cost of a CTA) + the exchange.  Returns the number of CTAs that should share a tile's K range (1, 2 or 4).
+int best_split(int64_t M, int64_t N, int64_t K, int sm_count) {
+  const int64_t tiles = ((M + 127) / 128) * ((N + 255) / 256);
+  const int64_t kb = (K + TcGeometry::kBlockK - 1) / TcGeometry::kBlockK;
+  const int64_t fixed = 12, exchange = 6;
+  int best = 1;
+  int64_t best_cost = ((tiles + sm_count - 1) / sm_count) * (kb + fixed);
+  for (int s = 2; s <= 4; s *= 2) {
+    if (kb / s < 4) break;
+    const int64_t cost = ((tiles * s + sm_count - 1) / sm_count) * ((kb + s - 1) / s + fixed) + exchange;
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
+}
+
 int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma_ok, bool y_tma_ok,
               const DeviceInfo& dev, Plan* out) {
   Plan pl = {};
   uint32_t v = flags & B200FP8_VARIANT_MASK;
-  if (v > B200FP8_VARIANT_SIMT) return B200FP8_BAD_ARG;
+  if (v > B200FP8_VARIANT_TC_SPLITK) return B200FP8_BAD_ARG;
   if (v == B200FP8_VARIANT_AUTO) {
     if (!operands_tma_ok) {
       v = B200FP8_VARIANT_SIMT;
@@ -113,6 +134,7 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
       // the pair tiles could not occupy the SMs anyway
       const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
       v = pair_tiles >= dev.sm_count / 2 ? B200FP8_VARIANT_TC_2CTA : B200FP8_VARIANT_TC_1CTA;
+      if (v == B200FP8_VARIANT_TC_1CTA && best_split(M, N, K, dev.sm_count) > 1) v = B200FP8_VARIANT_TC_SPLITK;
     }
   } else if (v != B200FP8_VARIANT_SIMT && !operands_tma_ok) {
     return B200FP8_UNSUPPORTED_ALIGNMENT;
@@ -133,6 +155,10 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
     const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
     const int64_t clusters = tiles < dev.max_pair_clusters ? tiles : dev.max_pair_clusters;
     pl.num_ctas = static_cast<int>(2 * clusters);
+  } else if (v == B200FP8_VARIANT_TC_SPLITK) {
+    pl.tiles = static_cast<int>(((M + 127) / 128) * ((N + 255) / 256));
+    pl.split = best_split(M, N, K, dev.sm_count);
+    if (pl.split < 2) pl.split = 2;  // forced variant on a shape the model would not split
   } else if (v == B200FP8_VARIANT_SKINNY) {
     pl.skinny = make_skinny_plan(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), dev.sm_count);
     pl.skinny.overlap_previous_kernel = (flags & B200FP8_FLAG_PDL) != 0;
@@ -281,6 +307,9 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
   tp.out_fp16 = (flags & B200FP8_FLAG_OUT_FP16) ? 1 : 0;
   tp.group_m = pl.group_m;
   tp.status = status_word;
+  if (pl.variant == B200FP8_VARIANT_TC_SPLITK) {
+    return note_cuda(launch_gemm_splitk(tm_x, tm_w, tm_y, tp, pl.tiles, pl.split, stream));
+  }
   if (cta_group == 2) return note_cuda(launch_gemm_tc<2>(tm_x, tm_w, tm_y, tp, pl.num_ctas, stream));
   return note_cuda(launch_gemm_tc<1>(tm_x, tm_w, tm_y, tp, pl.num_ctas, stream));
 }
@@ -439,6 +468,10 @@ int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char*
     case B200FP8_VARIANT_TC_2CTA:
       snprintf(buf, n, "tc_2cta tile=256x256x128 stages=%d ctas=%d group_m=%d smem=%d workspace=%zu",
                TcConfig<2>::kStages, pl.num_ctas, pl.group_m, TcConfig<2>::kSmemBytes, pl.workspace_bytes);
+      break;
+    case B200FP8_VARIANT_TC_SPLITK:
+      snprintf(buf, n, "tc_splitk tile=128x256x128 cluster=%d (K split, DSMEM reduce-scatter) stages=4 ctas=%d workspace=%zu",
+               pl.split, pl.tiles * pl.split, pl.workspace_bytes);
       break;
     case B200FP8_VARIANT_SKINNY:
       snprintf(buf, n,

@@ -112,6 +112,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   const int seg_count = work.count;
   auto segment_at = [&](int i) { return work_segment(work, i); };
 
+  // Producer state that survives the set-up barrier: thread 0 starts streaming W as soon as it has
+  // initialised the barriers, without waiting for the TMEM allocation or the other warps.
+  const uint32_t tx_bytes = static_cast<uint32_t>(G::kBytesA + bytes_b);
+  int first_pass_kb[G::kMaxStages];  // k-block held by each stage after the first pass over the ring
+  int issued = 0, resume_i = 0, resume_kb = 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
@@ -129,6 +134,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     fence_mbar_init();
     prefetch_tensormap(&tm_w);
     prefetch_tensormap(&tm_x);
+    // First pass over the ring: W only (weights; every stage is free, nothing to wait for).  X joins
+    // after griddepcontrol.wait below, because the kernel before this one may still be producing it.
+    for (int i = 0; i < seg_count && issued < stages; ++i) {
+      const Segment sg = segment_at(i);
+      int kb = sg.kb0;
+      for (; kb < sg.kb1 && issued < stages; ++kb) {
+        const uint32_t full = bar_full + 8 * issued;
+        mbar_arrive_expect_tx(full, tx_bytes);
+        tma_load_2d(smem_a + issued * G::kBytesA, &tm_w, full, kb * G::kBlockK, sg.tile * G::kRowsW);
+        first_pass_kb[issued] = kb;
+        ++issued;
+      }
+      resume_i = i;
+      resume_kb = kb;
+    }
   }
   // two accumulators of tokens_pad columns; the allocation is a power of two of at least 32
   uint32_t tmem_cols = 32;
@@ -146,47 +166,29 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0) {
-      const uint32_t tx_bytes = static_cast<uint32_t>(G::kBytesA + bytes_b);
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = static_cast<uint32_t>(issued % stages);
+      uint32_t phase = static_cast<uint32_t>(issued / stages) & 1u;
       bool ok = true;
-      // First pass over the ring: W only (every stage is free, nothing to wait for), remembering
-      // which k-block each stage holds.  Then wait for the kernels before this one, add the X
-      // boxes of those stages, and carry on with both operands per stage.
-      int issued = 0;
-      bool x_allowed = false;
-      int first_pass_kb[G::kMaxStages];
-      auto allow_x = [&]() {
-        griddep_wait();
-        const int n = issued < stages ? issued : stages;
-        for (int s = 0; s < n; ++s) {
-          tma_load_2d(smem_b + s * bytes_b, &tm_x, bar_full + 8 * s, first_pass_kb[s] * G::kBlockK, 0);
-        }
-        x_allowed = true;
-      };
-      for (int i = 0; i < seg_count && ok; ++i) {
+      // the kernels before this one are done from here on: add the X boxes of the first-pass stages
+      griddep_wait();
+      for (int s = 0; s < issued; ++s) {
+        tma_load_2d(smem_b + s * bytes_b, &tm_x, bar_full + 8 * s, first_pass_kb[s] * G::kBlockK, 0);
+      }
+      for (int i = resume_i; i < seg_count && ok; ++i) {
         const Segment sg = segment_at(i);
-        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
-          if (!x_allowed && issued == stages) allow_x();
+        for (int kb = (i == resume_i ? resume_kb : sg.kb0); kb < sg.kb1; ++kb) {
+          ok = mbar_wait<false>(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty);
+          if (!ok) break;
           const uint32_t full = bar_full + 8 * stage;
-          if (x_allowed) {
-            ok = mbar_wait<false>(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty);
-            if (!ok) break;
-            mbar_arrive_expect_tx(full, tx_bytes);
-            tma_load_2d(smem_a + stage * G::kBytesA, &tm_w, full, kb * G::kBlockK, sg.tile * G::kRowsW);
-            tma_load_2d(smem_b + stage * bytes_b, &tm_x, full, kb * G::kBlockK, 0);
-          } else {
-            mbar_arrive_expect_tx(full, tx_bytes);
-            tma_load_2d(smem_a + stage * G::kBytesA, &tm_w, full, kb * G::kBlockK, sg.tile * G::kRowsW);
-            first_pass_kb[stage] = kb;
-          }
-          ++issued;
+          mbar_arrive_expect_tx(full, tx_bytes);
+          tma_load_2d(smem_a + stage * G::kBytesA, &tm_w, full, kb * G::kBlockK, sg.tile * G::kRowsW);
+          tma_load_2d(smem_b + stage * bytes_b, &tm_x, full, kb * G::kBlockK, 0);
           if (++stage == static_cast<uint32_t>(stages)) {
             stage = 0;
             phase ^= 1u;
           }
         }
       }
-      if (!x_allowed) allow_x();
       if (!ok) {
         const unsigned long long t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);

@@ -163,11 +163,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     }
     *abort_flag = 0u;
     fence_mbar_init();
-  }
-  if (warp == 0 && lane == 0) {
     prefetch_tensormap(&tm_x);
     prefetch_tensormap(&tm_w);
     if (p.use_tma_store) prefetch_tensormap(&tm_y);
+    if constexpr (!kPair) {
+      // Single CTA: the first pass over the ring needs no waiting, so it starts before the set-up barrier
+      // (a CTA pair cannot: the peer's loads credit the leader's barriers, which must exist first).
+      if (cluster_id < num_tiles) {
+        const TileInfo ti = tile_info<kCtaGroup>(ts, cluster_id, 0u);
+        for (int kb = 0; kb < num_kb && kb < kStages; ++kb) {
+          const uint32_t full = bar_full + 8 * kb;
+          mbar_arrive_expect_tx(full, Cfg::kStageTxBytes);
+          tma_load_2d(smem_a + kb * Cfg::kBytesA, &tm_x, full, kb * Cfg::kBlockK, ti.row0);
+          tma_load_2d(smem_b + kb * Cfg::kBytesB, &tm_w, full, kb * Cfg::kBlockK, ti.w_row0);
+        }
+      }
+    }
   }
   if (warp == 1) {
     tmem_alloc<kCtaGroup>(tmem_slot, 512);
@@ -185,13 +196,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
+      // k-blocks of the first tile already issued before the set-up barrier (single CTA only)
+      const int pre = kPair ? 0 : (num_kb < kStages ? num_kb : kStages);
+      uint32_t stage = static_cast<uint32_t>(pre % kStages), phase = static_cast<uint32_t>(pre / kStages) & 1u;
       bool ok = true;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
         const TileInfo ti = tile_info<kCtaGroup>(ts, t, cta_rank);
         const int row_x = ti.row0;
         const int row_w = ti.w_row0;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = (t == cluster_id ? pre : 0); kb < num_kb; ++kb) {
           ok = mbar_wait<kPair>(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty);
           if (!ok) break;
           const uint32_t dst_a = smem_a + stage * Cfg::kBytesA;

@@ -54,6 +54,10 @@ template <int kCtaGroup>
 cudaError_t launch_gemm_tc(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
                            const TcParams& p, int num_ctas, cudaStream_t stream);
 
+// split-K inside a cluster of `split` CTAs per 128x256 tile, reduced over distributed shared memory (gemm_splitk.cu)
+cudaError_t launch_gemm_splitk(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
+                               const TcParams& p, int tiles, int split, cudaStream_t stream);
+
 // ------------------------ skinny-M stream-K kernel (gemm_skinny.cu) ------------------------
 struct SkinnyGeometry {
   static constexpr int kRowsW = 128;   // W rows per tile (MMA M, TMEM lanes)

@@ -24,6 +24,7 @@ VARIANT_TC_1CTA = 1
 VARIANT_TC_2CTA = 2
 VARIANT_SKINNY = 3
 VARIANT_SIMT = 4
+VARIANT_TC_SPLITK = 5
 FLAG_NO_TMA_STORE = 0x10
 FLAG_PDL = 0x20
 FLAG_OUT_FP16 = 0x40
@@ -35,6 +36,7 @@ VARIANTS = {
     "tc_2cta": VARIANT_TC_2CTA,
     "skinny": VARIANT_SKINNY,
     "simt": VARIANT_SIMT,
+    "tc_splitk": VARIANT_TC_SPLITK,
 }
 WORKSPACE_HEADER_BYTES = 256
 
