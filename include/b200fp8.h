@@ -157,6 +157,15 @@ int b200fp8_row_quantize(const void* x, int x_dtype, int recipe, int64_t rows, i
 int b200fp8_query_status(const void* workspace, uint32_t* device_status);
 
 /*
+ * Self-test of the failure path: launches one CTA that waits on a barrier nothing will ever arrive on, with a
+ * limit of `limit_us` microseconds (at most one second).  The wait runs out, the kernel ends normally, and after a
+ * synchronise b200fp8_query_status(workspace) returns B200FP8_DEVICE_TIMEOUT.  Nothing faults, traps or hangs;
+ * re-initialise the workspace afterwards.  Replaces: nothing in the reference (its native code exits the process
+ * on error, tritonbench/operators/mixed_gemm/kernels/helper.h:40-64).
+ */
+int b200fp8_selftest_wait_timeout(void* workspace, uint32_t limit_us, void* cuda_stream);
+
+/*
  * Human-readable plan for a problem size: variant, tile, grid, pipeline depth, workspace.
  * Writes a NUL-terminated string of at most n-1 characters.
  * Replaces: the backend knobs the reference passes to FBGEMM (operator.py:187-199).
@@ -166,7 +175,8 @@ int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char*
 /*
  * Host-buffer form, the call a host program without its own device memory makes:
  * inputs and output live in host memory (pinned for full PCIe speed), device staging
- * buffers belong to the context.  One call = copy in, GEMM, copy out, synchronise.
+ * buffers belong to the context.  One call = copy in, GEMM, copy out, synchronise.  Problems of 2048 rows or
+ * more are pipelined in 1024-row panels over three streams, so both PCIe directions and the GPU work at once.
  * Replaces: `input_cast(.to(device))` + backend call + result read in
  * tritonbench/utils/triton_op.py:846-850,1221-1232.
  */

@@ -440,6 +440,34 @@ def test_grouped_gemm_leaves_rows_beyond_the_groups_untouched(cuda_device):
     assert bool((y[220:] == 7.0).all())
 
 
+def test_a_wait_that_runs_out_becomes_a_status_code_not_a_hang(cuda_device):
+    """Failure detection without a fault: a CTA waits 2 ms on a barrier that nothing sets; the wait gives up,
+    the kernel ends normally, the host reads DEVICE_TIMEOUT, and the GPU context is still good for the next GEMM."""
+    import ctypes
+    import time
+
+    from tritonbench_b200 import lib
+
+    ops = _ops()
+    cdll = lib.load()
+    ws = torch.zeros(256, dtype=torch.uint8, device="cuda")
+    t0 = time.perf_counter()
+    assert cdll.b200fp8_selftest_wait_timeout(ws.data_ptr(), 2000, torch.cuda.current_stream().cuda_stream) == lib.OK
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0
+    word = ctypes.c_uint32(0)
+    assert cdll.b200fp8_query_status(ws.data_ptr(), ctypes.byref(word)) == lib.DEVICE_TIMEOUT
+    assert word.value >> 24 == 1 and (word.value & 0xFFFFFF) == 0x7E57
+    with pytest.raises(lib.B200Fp8Error) as e:
+        lib.check(lib.DEVICE_TIMEOUT, "selftest")
+    assert e.value.status == lib.DEVICE_TIMEOUT
+    ws.zero_()
+    assert cdll.b200fp8_query_status(ws.data_ptr(), ctypes.byref(word)) == lib.OK
+    xq, wq, xs, wsc = _inputs(128, 256, 512)
+    _assert_close(_run("auto", xq, wq, xs, wsc), orc.gemm_rowwise(xq, wq, xs, wsc), "GEMM after the self-test")
+    assert cdll.b200fp8_selftest_wait_timeout(ws.data_ptr(), 0, None) == lib.BAD_ARG
+
+
 def test_host_buffer_entry_point(cuda_device):
     ops = _ops()
     for variant, shape in (("auto", (384, 768, 512)), ("auto", (16, 2304, 2048))):

@@ -439,6 +439,13 @@ int b200fp8_row_quantize(const void* x, int x_dtype, int recipe, int64_t rows, i
   return note_cuda(launch_row_quantize(p, static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int b200fp8_selftest_wait_timeout(void* workspace, uint32_t limit_us, void* cuda_stream) {
+  if (workspace == nullptr || limit_us == 0 || limit_us > 1000000u) return B200FP8_BAD_ARG;
+  return note_cuda(launch_wait_timeout_selftest(static_cast<uint32_t*>(workspace),
+                                                static_cast<unsigned long long>(limit_us) * 1000ull,
+                                                static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int b200fp8_query_status(const void* workspace, uint32_t* device_status) {
   if (workspace == nullptr) return B200FP8_BAD_ARG;
   uint32_t word = 0;
@@ -488,24 +495,39 @@ int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char*
 }
 
 // ------------------------------------ host-buffer context ------------------------------------
+// One call = copy in, GEMM, copy out.  The copies are what the call costs (PCIe), so large problems are
+// cut into row panels that flow through three streams: panel i+1 of X goes up while panel i is multiplied
+// and panel i-1 of Y comes down; both PCIe directions are busy at once.  W and the scales go first.
+namespace {
+constexpr int kMaxPanels = 64;
+constexpr int64_t kPanelRows = 1024;
+}  // namespace
+
 struct b200fp8_host_ctx {
   int64_t M, N, K;
   uint32_t flags;
-  cudaStream_t stream;
+  int panels;
+  int64_t panel_rows;
+  cudaStream_t s_in, s_compute, s_out;
+  cudaEvent_t ev_w, ev_start;
+  cudaEvent_t ev_x[kMaxPanels];
+  cudaEvent_t ev_y[kMaxPanels];
   uint8_t* d_x;
   uint8_t* d_w;
   float* d_xs;
   float* d_ws;
   __nv_bfloat16* d_bias;
   __nv_bfloat16* d_y;
-  void* d_workspace;
-  size_t workspace_bytes;
-  uint32_t* h_status;  // pinned
+  uint8_t* d_workspace;       // one workspace per panel (panels in flight must not share one)
+  size_t workspace_bytes;     // per panel
+  uint32_t* h_status;         // pinned, one word per panel
 };
 
 int b200fp8_host_ctx_destroy(b200fp8_host_ctx* c) {
   if (c == nullptr) return B200FP8_OK;
-  if (c->stream) cudaStreamSynchronize(c->stream);
+  if (c->s_in) cudaStreamSynchronize(c->s_in);
+  if (c->s_compute) cudaStreamSynchronize(c->s_compute);
+  if (c->s_out) cudaStreamSynchronize(c->s_out);
   cudaFree(c->d_x);
   cudaFree(c->d_w);
   cudaFree(c->d_xs);
@@ -514,7 +536,15 @@ int b200fp8_host_ctx_destroy(b200fp8_host_ctx* c) {
   cudaFree(c->d_y);
   cudaFree(c->d_workspace);
   if (c->h_status) cudaFreeHost(c->h_status);
-  if (c->stream) cudaStreamDestroy(c->stream);
+  if (c->ev_w) cudaEventDestroy(c->ev_w);
+  if (c->ev_start) cudaEventDestroy(c->ev_start);
+  for (int i = 0; i < kMaxPanels; ++i) {
+    if (c->ev_x[i]) cudaEventDestroy(c->ev_x[i]);
+    if (c->ev_y[i]) cudaEventDestroy(c->ev_y[i]);
+  }
+  if (c->s_in) cudaStreamDestroy(c->s_in);
+  if (c->s_compute) cudaStreamDestroy(c->s_compute);
+  if (c->s_out) cudaStreamDestroy(c->s_out);
   delete c;
   return B200FP8_OK;
 }
@@ -535,21 +565,38 @@ int b200fp8_host_ctx_create(int64_t M, int64_t N, int64_t K, uint32_t flags, b20
   c->N = N;
   c->K = K;
   c->flags = flags;
-  c->workspace_bytes = b200fp8_workspace_bytes(M, N, K, flags);
-  cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+  // panels of 1024 rows once there are at least two of them; at most kMaxPanels
+  c->panel_rows = M >= 2 * kPanelRows ? kPanelRows : M;
+  while ((M + c->panel_rows - 1) / c->panel_rows > kMaxPanels) c->panel_rows *= 2;
+  c->panels = static_cast<int>((M + c->panel_rows - 1) / c->panel_rows);
+  const int64_t last_rows = M - (c->panels - 1) * c->panel_rows;
+  const size_t ws_a = b200fp8_workspace_bytes(c->panel_rows, N, K, flags);
+  const size_t ws_b = b200fp8_workspace_bytes(last_rows, N, K, flags);
+  c->workspace_bytes = (((ws_a > ws_b ? ws_a : ws_b) + 255) / 256) * 256;
+  cudaError_t e = cudaSuccess;
+  if (ws_a == 0 || ws_b == 0) e = cudaErrorInvalidValue;
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_compute, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_w, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_start, cudaEventDisableTiming);
+  for (int i = 0; i < c->panels && e == cudaSuccess; ++i) {
+    e = cudaEventCreateWithFlags(&c->ev_x[i], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_y[i], cudaEventDisableTiming);
+  }
   if (e == cudaSuccess) e = cudaMalloc(&c->d_x, static_cast<size_t>(M) * K);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_w, static_cast<size_t>(N) * K);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_xs, static_cast<size_t>(M) * sizeof(float));
   if (e == cudaSuccess) e = cudaMalloc(&c->d_ws, static_cast<size_t>(N) * sizeof(float));
   if (e == cudaSuccess) e = cudaMalloc(&c->d_bias, static_cast<size_t>(N) * sizeof(__nv_bfloat16));
   if (e == cudaSuccess) e = cudaMalloc(&c->d_y, static_cast<size_t>(M) * N * sizeof(__nv_bfloat16));
-  if (e == cudaSuccess) e = cudaMalloc(&c->d_workspace, c->workspace_bytes);
-  if (e == cudaSuccess) e = cudaMallocHost(&c->h_status, sizeof(uint32_t));
-  if (e == cudaSuccess) e = cudaMemsetAsync(c->d_workspace, 0, c->workspace_bytes, c->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
-  if (e != cudaSuccess || c->workspace_bytes == 0) {
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_workspace, c->workspace_bytes * c->panels);
+  if (e == cudaSuccess) e = cudaMallocHost(&c->h_status, sizeof(uint32_t) * kMaxPanels);
+  if (e == cudaSuccess) e = cudaMemsetAsync(c->d_workspace, 0, c->workspace_bytes * c->panels, c->s_compute);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(c->s_compute);
+  if (e != cudaSuccess) {
     b200fp8_host_ctx_destroy(c);
-    return e != cudaSuccess ? note_cuda(e) : B200FP8_BAD_ARG;
+    return note_cuda(e);
   }
   *out = c;
   return B200FP8_OK;
@@ -562,23 +609,51 @@ int b200fp8_gemm_rowwise_host(b200fp8_host_ctx* c, const void* xq, const void* w
     return B200FP8_BAD_ARG;
   }
   const size_t M = static_cast<size_t>(c->M), N = static_cast<size_t>(c->N), K = static_cast<size_t>(c->K);
-  cudaError_t e = cudaMemcpyAsync(c->d_x, xq, M * K, cudaMemcpyHostToDevice, c->stream);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(c->d_w, wq, N * K, cudaMemcpyHostToDevice, c->stream);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(c->d_xs, x_scale, M * sizeof(float), cudaMemcpyHostToDevice, c->stream);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(c->d_ws, w_scale, N * sizeof(float), cudaMemcpyHostToDevice, c->stream);
+  // weights, scales and bias first
+  cudaError_t e = cudaMemcpyAsync(c->d_w, wq, N * K, cudaMemcpyHostToDevice, c->s_in);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(c->d_ws, w_scale, N * sizeof(float), cudaMemcpyHostToDevice, c->s_in);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(c->d_xs, x_scale, M * sizeof(float), cudaMemcpyHostToDevice, c->s_in);
   if (e == cudaSuccess && bias_bf16 != nullptr) {
-    e = cudaMemcpyAsync(c->d_bias, bias_bf16, N * sizeof(__nv_bfloat16), cudaMemcpyHostToDevice, c->stream);
+    e = cudaMemcpyAsync(c->d_bias, bias_bf16, N * sizeof(__nv_bfloat16), cudaMemcpyHostToDevice, c->s_in);
   }
+  if (e == cudaSuccess) e = cudaEventRecord(c->ev_w, c->s_in);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(c->s_compute, c->ev_w, 0);
   if (e != cudaSuccess) return note_cuda(e);
-  const int st = b200fp8_gemm_rowwise(c->d_x, c->d_w, c->d_xs, c->d_ws, bias_bf16 != nullptr ? c->d_bias : nullptr,
-                                      c->d_y, c->M, c->N, c->K, c->K, c->K, c->N, c->d_workspace,
-                                      c->workspace_bytes, c->flags, c->stream);
-  if (st != B200FP8_OK) return st;
-  e = cudaMemcpyAsync(y_bf16, c->d_y, M * N * sizeof(__nv_bfloat16), cudaMemcpyDeviceToHost, c->stream);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(c->h_status, c->d_workspace, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+
+  const uint8_t* x_host = static_cast<const uint8_t*>(xq);
+  __nv_bfloat16* y_host = static_cast<__nv_bfloat16*>(y_bf16);
+  for (int i = 0; i < c->panels; ++i) {
+    const size_t r0 = static_cast<size_t>(i) * c->panel_rows;
+    const size_t rows = (r0 + c->panel_rows <= M) ? static_cast<size_t>(c->panel_rows) : M - r0;
+    e = cudaMemcpyAsync(c->d_x + r0 * K, x_host + r0 * K, rows * K, cudaMemcpyHostToDevice, c->s_in);
+    if (e == cudaSuccess) e = cudaEventRecord(c->ev_x[i], c->s_in);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->s_compute, c->ev_x[i], 0);
+    if (e != cudaSuccess) return note_cuda(e);
+    uint8_t* ws = c->d_workspace + static_cast<size_t>(i) * c->workspace_bytes;
+    const int st = b200fp8_gemm_rowwise(c->d_x + r0 * K, c->d_w, c->d_xs + r0, c->d_ws,
+                                        bias_bf16 != nullptr ? c->d_bias : nullptr, c->d_y + r0 * N,
+                                        static_cast<int64_t>(rows), c->N, c->K, c->K, c->K, c->N, ws,
+                                        c->workspace_bytes, c->flags, c->s_compute);
+    if (st != B200FP8_OK) return st;
+    e = cudaEventRecord(c->ev_y[i], c->s_compute);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->s_out, c->ev_y[i], 0);
+    if (e == cudaSuccess) {
+      e = cudaMemcpyAsync(y_host + r0 * N, c->d_y + r0 * N, rows * N * sizeof(__nv_bfloat16), cudaMemcpyDeviceToHost,
+                          c->s_out);
+    }
+    if (e == cudaSuccess) {
+      e = cudaMemcpyAsync(c->h_status + i, ws, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->s_out);
+    }
+    if (e != cudaSuccess) return note_cuda(e);
+  }
+  e = cudaStreamSynchronize(c->s_out);
+  // the next call must not overwrite d_w / d_x while this call's kernels could still read them: they cannot,
+  // every kernel has completed before its panel's copy-out, and the last copy-out has completed here
   if (e != cudaSuccess) return note_cuda(e);
-  return (*c->h_status >> 24) == kDevTimeout ? B200FP8_DEVICE_TIMEOUT : B200FP8_OK;
+  for (int i = 0; i < c->panels; ++i) {
+    if ((c->h_status[i] >> 24) == kDevTimeout) return B200FP8_DEVICE_TIMEOUT;
+  }
+  return B200FP8_OK;
 }
 
 }  // extern "C"

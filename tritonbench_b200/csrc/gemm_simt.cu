@@ -7,6 +7,7 @@
 #include <cuda_fp8.h>
 
 #include "kernels.h"
+#include "ptx.cuh"
 
 namespace b200fp8 {
 namespace {
@@ -70,7 +71,31 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
   }
 }
 
+// Self-test of the bounded wait every tensor-core kernel is built on: one CTA waits on an mbarrier
+// that nothing will ever arrive on.  The wait must run out after `limit_ns`, record its site in the
+// status word and let the kernel end normally.
+constexpr uint32_t kSiteSelfTest = 0x7E57;
+
+__global__ void wait_timeout_selftest_kernel(uint32_t* status, unsigned long long limit_ns) {
+  __shared__ unsigned long long barrier_storage;
+  __shared__ uint32_t abort_flag;
+  const uint32_t bar = smem_u32(&barrier_storage);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    abort_flag = 0u;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  // every thread waits; the first to run out of time raises the flag, the others leave on seeing it
+  mbar_wait<false>(bar, 0u, &abort_flag, status, kSiteSelfTest, limit_ns);
+}
+
 }  // namespace
+
+cudaError_t launch_wait_timeout_selftest(uint32_t* status, unsigned long long limit_ns, cudaStream_t stream) {
+  wait_timeout_selftest_kernel<<<1, 64, 0, stream>>>(status, limit_ns);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_gemm_simt(const SimtParams& p, cudaStream_t stream) {
   const dim3 grid((p.N + kTile - 1) / kTile, (p.M + kTile - 1) / kTile, 1);

@@ -138,6 +138,9 @@ struct SimtParams {
 
 cudaError_t launch_gemm_simt(const SimtParams& p, cudaStream_t stream);
 
+// one CTA waits `limit_ns` on a barrier nothing arrives on, then records a time-out in *status
+cudaError_t launch_wait_timeout_selftest(uint32_t* status, unsigned long long limit_ns, cudaStream_t stream);
+
 // ------------------------------ rowwise quantiser (quantize.cu) -----------------------------
 constexpr int kQuantBf16 = 0, kQuantFp16 = 1, kQuantFp32 = 2;  // dtype of x
 constexpr int kRecipeOperator = 0;  // the operator's fp8_row_quantize: arithmetic in x's dtype, multiplier 448/max

@@ -124,7 +124,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // (it then raises the CTA's abort flag and records the site) or another role already did.
 template <bool kClusterScope>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* status, uint32_t site) {
+                                          uint32_t* status, uint32_t site,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait<kClusterScope>(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   uint32_t polls = 0;
@@ -132,7 +133,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait<kClusterScope>(bar, parity)) return true;
     if ((++polls & 0xFFu) == 0u) {
       if (*abort_flag != 0u) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1u;
         atomicCAS(status, kDevOk, (kDevTimeout << 24) | (site & 0xFFFFFFu));
         return false;

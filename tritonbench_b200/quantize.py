@@ -101,3 +101,37 @@ def make_inputs(
     xq, xs = make_quantized(m, k, x_seed, device, dist, x_std)
     wq, ws = make_quantized(n, k, w_seed, device, dist, w_std)
     return xq, wq, xs, ws
+
+
+def _main() -> None:
+    """python -m tritonbench_b200.quantize --rows R --cols C [--dtype bf16|fp16|fp32] [--iters N]
+    times the CUDA quantiser kernel (CUDA events, back-to-back calls) and prints GB/s."""
+    import argparse
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", type=int, default=28672)
+    ap.add_argument("--cols", type=int, default=8192)
+    ap.add_argument("--dtype", choices=["bf16", "fp16", "fp32"], default="bf16")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    from . import ops
+
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
+    x = torch.randn((args.rows, args.cols), device="cuda", dtype=dt)
+    for _ in range(args.warmup):
+        ops.fp8_row_quantize(x)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.iters):
+        ops.fp8_row_quantize(x)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / args.iters * 1e3
+    nbytes = args.rows * args.cols * (x.element_size() + 1) + 4 * args.rows
+    print(f"row_quantize {args.rows}x{args.cols} {args.dtype}: {us:.1f} us per call, {nbytes / us / 1e3:.0f} GB/s")
+
+
+if __name__ == "__main__":
+    _main()
