@@ -131,6 +131,19 @@ int b200fp8_gemm_rowwise_grouped(const void* xq, const void* wq, const float* x_
                                  size_t workspace_bytes, uint32_t flags, void* cuda_stream);
 
 /*
+ * Block-scaled form: one fp32 scale per 128x128 block of X and of W,
+ *   Y[m,n] = bf16( sum_kb (sum_{k in block kb} X[m,k] W[n,k]) * x_scale[m/128][kb] * w_scale[n/128][kb] ),
+ * x_scale [ceil(M/128)][ld_xs], w_scale [ceil(N/128)][ld_ws] fp32 (row pitches in elements, >= ceil(K/128)).
+ * Every k-block's product is accumulated in tensor memory on its own and promoted into fp32 registers with
+ * that block's scale.  Needs only the workspace header.
+ * Replaces: `matmul_fp8_block(xq, wq, x_scale, w_scale)` and `torch.ops.fbgemm.f8f8bf16_blockwise` in
+ * tritonbench/operators/fp8_gemm_blockwise/operator.py:139-149.
+ */
+int b200fp8_gemm_blockwise(const void* xq, const void* wq, const float* x_scale, const float* w_scale, void* y_bf16,
+                           int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, int64_t ld_xs,
+                           int64_t ld_ws, void* workspace, size_t workspace_bytes, uint32_t flags, void* cuda_stream);
+
+/*
  * Rowwise e4m3 quantiser: x [rows, cols] (row pitch ldx ELEMENTS) -> q [rows, cols] e4m3 bytes (row pitch ldq
  * bytes) and scale [rows] fp32 such that x ~ float(q) * scale.  One pass over HBM, asynchronous on the stream.
  *   x_dtype  B200FP8_DTYPE_BF16 / _FP16 / _FP32

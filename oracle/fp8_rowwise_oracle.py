@@ -129,6 +129,32 @@ def gemm_rowwise_grouped(xq, wq, m_sizes, x_scale, w_scale) -> torch.Tensor:
     return y
 
 
+def block_quantize_reference(x: torch.Tensor, block_m: int = 128, block_k: int = 128):
+    """tritonbench/operators/fp8_gemm_blockwise/operator.py:87-120: per 128x128 block, multiplier 448 / blockmax
+    (blockmax clamped to 1e-12 in x's dtype, the division in fp32, infinite multipliers replaced by 1), the scaled
+    values cast to e4m3 without a clamp; returns (xq, reciprocal multipliers [grid_m, grid_k] fp32)."""
+    m, k = x.shape
+    grid_m, grid_k = -(-m // block_m), -(-k // block_k)
+    padded = torch.zeros(grid_m * block_m, grid_k * block_k, dtype=x.dtype)
+    padded[:m, :k] = x
+    block_max = torch.clamp(padded.abs().reshape(grid_m, block_m, grid_k, block_k).amax(dim=(1, 3)), min=EPS)
+    scale = E4M3_MAX / block_max.to(torch.float32)
+    scale[scale == float("inf")] = 1.0
+    xq = (padded * scale.repeat_interleave(block_m, dim=0).repeat_interleave(block_k, dim=1))[:m, :k]
+    return xq.to(torch.float8_e4m3fn), 1 / scale
+
+
+def gemm_blockwise(xq, wq, x_scale, w_scale, keep_fp32: bool = False) -> torch.Tensor:
+    """Block-scaled GEMM (operator.py:139-149 call sites): operands dequantised with their 128x128 block scales
+    in fp32, fp32 matmul, bf16 result."""
+    m, k = xq.shape
+    n = wq.shape[0]
+    xs = x_scale.cpu().to(torch.float32).repeat_interleave(128, dim=0).repeat_interleave(128, dim=1)[:m, :k]
+    ws = w_scale.cpu().to(torch.float32).repeat_interleave(128, dim=0).repeat_interleave(128, dim=1)[:n, :k]
+    y = (decode_e4m3(xq.cpu()) * xs) @ (decode_e4m3(wq.cpu()) * ws).T
+    return y if keep_fp32 else y.to(torch.bfloat16)
+
+
 def bf16_ulp(v: torch.Tensor) -> torch.Tensor:
     """Spacing of bf16 numbers at |v|: 2^(floor(log2|v|) - 7); the smallest normal's ulp below that."""
     a = v.abs().to(torch.float32).clamp(min=2.0 ** -126)

@@ -10,6 +10,8 @@ What it pins
     at load time; FBGEMM is not vendored in the reference tree, so a one-function stand-in module
     that returns (torch.float8_e4m3fn, None, 448.0, 1e-12) is installed first.  Nothing else of
     FBGEMM is faked, and the stock backends stay disabled.
+  * block quantiser: the sibling operator's `fp8_block_quantize`
+    (tritonbench/operators/fp8_gemm_blockwise/operator.py:87-120), imported and run the same way.
   * GEMM: the reference has no runnable implementation and no test vectors for the GEMM itself
     (its kernels live in FBGEMM), so the stored Y is the fp32 dequantise-then-matmul result computed
     with plain torch CPU ops here, written out independently of oracle/ (no import of it).
@@ -113,6 +115,21 @@ def main():
 
     # (4) the shape list the reference feeds the operator (operator.py:107-128)
     np.savez_compressed(os.path.join(HERE, "ref_builtin_shapes.npz"), shapes=np.array(shapes, dtype=np.int64))
+
+    # (6) the block quantiser of the sibling operator fp8_gemm_blockwise (operator.py:87-120).  That module
+    #     imports fbgemm_gpu.experimental.gen_ai for its side effects only; an empty stand-in lets it load.
+    gen_ai = types.ModuleType("fbgemm_gpu.experimental.gen_ai")
+    sys.modules["fbgemm_gpu.experimental.gen_ai"] = gen_ai
+    sys.modules["fbgemm_gpu.experimental"].gen_ai = gen_ai
+    import importlib
+
+    blockwise = importlib.import_module("tritonbench.operators.fp8_gemm_blockwise.operator")
+    torch.manual_seed(1337)
+    xb = torch.randn((200, 300), dtype=torch.bfloat16)
+    xb[130:140, 128:256] = 0.0
+    xb[3, 5] = 1000.0
+    qb, sb = blockwise.fp8_block_quantize(xb)
+    np.savez_compressed(os.path.join(HERE, "ref_block_quantizer_200x300.npz"), x_bf16=bf16_bits(xb), q=u8(qb), scale=sb.numpy())
 
     # (5) all 256 e4m3 byte patterns as torch decodes them
     allb = torch.arange(256, dtype=torch.uint8)

@@ -468,6 +468,31 @@ def test_a_wait_that_runs_out_becomes_a_status_code_not_a_hang(cuda_device):
     assert cdll.b200fp8_selftest_wait_timeout(ws.data_ptr(), 0, None) == lib.BAD_ARG
 
 
+BLOCKWISE_SHAPES = [(128, 256, 128), (128, 256, 512), (200, 300, 400), (777, 1024, 2048), (1, 2304, 2048), (64, 4096, 2048),
+                    (2048, 8192, 2048), (513, 1001, 1040), (4096, 2304, 4096)]
+
+
+@pytest.mark.parametrize("shape", BLOCKWISE_SHAPES)
+def test_block_scaled_gemm(cuda_device, shape):
+    """128x128 block scales: per-k-block promotion in the kernel against dequantise-then-matmul in the oracle."""
+    ops = _ops()
+    from tritonbench_b200 import quantize
+
+    m, n, k = shape
+    g = torch.Generator().manual_seed(m + n)
+    x = (torch.randn((m, k), generator=g) * (1 + 10 * torch.rand((m, 1), generator=g))).to(torch.bfloat16)
+    w = (torch.randn((n, k), generator=g) * 0.05).to(torch.bfloat16)
+    xq, xs = quantize.fp8_block_quantize(x)
+    wq, ws = quantize.fp8_block_quantize(w)
+    ref = orc.gemm_blockwise(xq, wq, xs, ws)
+    y = ops.fp8_gemm_blockwise(*_gpu(xq, wq, xs, ws))
+    ops.check_device_status()
+    _assert_close(y, ref, f"blockwise {shape}")
+    assert torch.equal(ops.fp8_gemm_blockwise(*_gpu(xq, wq, xs, ws)), y)
+    if n % 8 == 0:
+        _assert_close(ops.fp8_gemm_blockwise(*_gpu(xq, wq, xs, ws), tma_store=False), ref, f"blockwise {shape} plain stores")
+
+
 def test_host_buffer_entry_point(cuda_device):
     ops = _ops()
     for variant, shape in (("auto", (384, 768, 512)), ("auto", (16, 2304, 2048))):

@@ -154,3 +154,22 @@ def test_builtin_shape_list_fixture(golden_dir):
     shapes = _load(golden_dir, "ref_builtin_shapes.npz")["shapes"]
     assert shapes.shape == (20, 3)
     assert tuple(shapes[7]) == (16, 13312, 13312)  # the one shape the reference's run-config tracks
+
+
+def test_block_quantizer_restatement_matches_reference_fixture(golden_dir):
+    d = _load(golden_dir, "ref_block_quantizer_200x300.npz")
+    q, s = orc.block_quantize_reference(_bf16(d["x_bf16"]))
+    assert np.array_equal(q.view(torch.uint8).numpy(), d["q"])
+    assert np.array_equal(s.numpy(), d["scale"])
+    assert s.shape == (2, 3)
+
+
+def test_blockwise_gemm_oracle_reduces_to_rowwise_when_scales_are_uniform():
+    g = torch.Generator().manual_seed(2)
+    xq, _ = orc.row_quantize(torch.randn((130, 300), generator=g))
+    wq, _ = orc.row_quantize(torch.randn((70, 300), generator=g))
+    xs = torch.full((2, 3), 0.5)
+    ws = torch.full((1, 3), 0.25)
+    a = orc.gemm_blockwise(xq, wq, xs, ws)
+    b = orc.gemm_rowwise(xq, wq, torch.full((130,), 0.5), torch.full((70,), 0.25))
+    assert torch.equal(a, b)

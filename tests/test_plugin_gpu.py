@@ -76,3 +76,19 @@ def test_grouped_operator_backend_through_the_reference_harness(cuda_device):
     assert "b200-tflops" in str(out)
     cells = out.result[0][1]
     assert cells["b200_native"].accuracy is True
+
+
+def test_blockwise_operator_backend_through_the_reference_harness(cuda_device):
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "tritonbench")):
+        pytest.skip("no installed copy of the tritonbench package on this machine")
+    sys.path.insert(0, ref)
+    from tritonbench_b200 import tritonbench_plugin as plug
+
+    out = plug.run(
+        ["--op", "fp8_gemm_blockwise", "--device", "cuda", "--metrics", "latency,tflops,speedup,accuracy", "--only",
+         "torch_dequant_ref,b200_native", "--m", "2048", "--n", "2048", "--k", "2048"]
+    )
+    assert "b200-tflops" in str(out)
+    cells = out.result[0][1]
+    assert cells["b200_native"].accuracy is True

@@ -50,3 +50,12 @@ def test_student_t_rows_have_heavy_tails_and_never_overflow():
 def test_every_row_hits_full_scale():
     q, _ = quantize.make_quantized(32, 64, seed=2)
     assert bool((orc.decode_e4m3(q).abs().amax(dim=1) == 448.0).all())
+
+
+def test_block_quantizer_matches_oracle_restatement():
+    g = torch.Generator().manual_seed(6)
+    for shape in ((200, 300), (128, 128), (1, 16), (257, 130)):
+        x = torch.randn(shape, generator=g).to(torch.bfloat16)
+        q, s = quantize.fp8_block_quantize(x)
+        qo, so = orc.block_quantize_reference(x)
+        assert torch.equal(q.view(torch.uint8), qo.view(torch.uint8)) and torch.equal(s, so)

@@ -416,6 +416,55 @@ int b200fp8_gemm_rowwise_grouped(const void* xq, const void* wq, const float* x_
   return note_cuda(launch_gemm_tc<1>(tm_x, tm_w, tm_y, tp, ctas, static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int b200fp8_gemm_blockwise(const void* xq, const void* wq, const float* x_scale, const float* w_scale, void* y_bf16,
+                           int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, int64_t ld_xs,
+                           int64_t ld_ws, void* workspace, size_t workspace_bytes, uint32_t flags, void* cuda_stream) {
+  if (xq == nullptr || wq == nullptr || x_scale == nullptr || w_scale == nullptr || y_bf16 == nullptr ||
+      workspace == nullptr) {
+    return B200FP8_BAD_ARG;
+  }
+  int st = check_sizes(M, N, K);
+  if (st != B200FP8_OK) return st;
+  const int64_t kb = (K + 127) / 128;
+  if (ldx < K || ldw < K || ldy < N || ld_xs < kb || ld_ws < kb) return B200FP8_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0 || workspace_bytes < B200FP8_WORKSPACE_HEADER_BYTES) {
+    return B200FP8_BAD_ARG;
+  }
+  DeviceInfo dev;
+  st = device_info(&dev);
+  if (st != B200FP8_OK) return st;
+  if (dev.cc_major != 10) return B200FP8_UNSUPPORTED_ARCH;
+  if (!tma_loadable(K, ldx, ldw, xq, wq)) return B200FP8_UNSUPPORTED_ALIGNMENT;
+  CUtensorMap tm_x, tm_w, tm_y;
+  memset(&tm_y, 0, sizeof(tm_y));
+  st = encode_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, M, K, ldx, TcGeometry::kBlockK, TcGeometry::kBlockM);
+  if (st != B200FP8_OK) return st;
+  st = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, N, K, ldw, TcGeometry::kBlockK, TcGeometry::kBlockN);
+  if (st != B200FP8_OK) return st;
+  const bool tma_store = (ldy % 8 == 0) && aligned16(y_bf16) && (flags & B200FP8_FLAG_NO_TMA_STORE) == 0;
+  if (tma_store) {
+    st = encode_2d(&tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y_bf16, M, N, ldy * 2, TcGeometry::kStoreCols,
+                   TcGeometry::kStoreRows);
+    if (st != B200FP8_OK) return st;
+  }
+  BlockwiseParams bp = {};
+  bp.x_scale = x_scale;
+  bp.w_scale = w_scale;
+  bp.y = static_cast<__nv_bfloat16*>(y_bf16);
+  bp.M = static_cast<int>(M);
+  bp.N = static_cast<int>(N);
+  bp.K = static_cast<int>(K);
+  bp.ldy = ldy;
+  bp.ld_xs = ld_xs;
+  bp.ld_ws = ld_ws;
+  bp.use_tma_store = tma_store ? 1 : 0;
+  bp.group_m = 8;
+  bp.status = static_cast<uint32_t*>(workspace);
+  const int64_t tiles = ((M + 127) / 128) * ((N + 255) / 256);
+  const int ctas = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
+  return note_cuda(launch_gemm_blockwise(tm_x, tm_w, tm_y, bp, ctas, static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int b200fp8_row_quantize(const void* x, int x_dtype, int recipe, int64_t rows, int64_t cols, int64_t ldx, void* q,
                          int64_t ldq, float* scale, void* cuda_stream) {
   if (x == nullptr || q == nullptr || scale == nullptr) return B200FP8_BAD_ARG;

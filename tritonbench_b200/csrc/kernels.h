@@ -58,6 +58,21 @@ cudaError_t launch_gemm_tc(const CUtensorMap& tm_x, const CUtensorMap& tm_w, con
 cudaError_t launch_gemm_splitk(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
                                const TcParams& p, int tiles, int split, cudaStream_t stream);
 
+// ------------------------ 128x128 block-scaled GEMM (gemm_blockwise.cu) ------------------------
+struct BlockwiseParams {
+  const float* x_scale;  // [ceil(M/128)][ld_xs >= ceil(K/128)]
+  const float* w_scale;  // [ceil(N/128)][ld_ws >= ceil(K/128)]
+  __nv_bfloat16* y;
+  int M, N, K;
+  long long ldy, ld_xs, ld_ws;  // elements
+  int use_tma_store;
+  int group_m;
+  uint32_t* status;
+};
+
+cudaError_t launch_gemm_blockwise(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
+                                  const BlockwiseParams& p, int num_ctas, cudaStream_t stream);
+
 // ------------------------ skinny-M stream-K kernel (gemm_skinny.cu) ------------------------
 struct SkinnyGeometry {
   static constexpr int kRowsW = 128;   // W rows per tile (MMA M, TMEM lanes)

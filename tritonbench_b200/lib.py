@@ -58,6 +58,7 @@ EXPORTED_SYMBOLS = (
     "b200fp8_row_quantize",
     "b200fp8_gemm_rowwise_grouped",
     "b200fp8_selftest_wait_timeout",
+    "b200fp8_gemm_blockwise",
 )
 
 _lib: Optional[ctypes.CDLL] = None
@@ -117,6 +118,8 @@ def load() -> ctypes.CDLL:
     )
     lib.b200fp8_selftest_wait_timeout.restype = ctypes.c_int
     lib.b200fp8_selftest_wait_timeout.argtypes = [c_void_p, c_uint32, c_void_p]
+    lib.b200fp8_gemm_blockwise.restype = ctypes.c_int
+    lib.b200fp8_gemm_blockwise.argtypes = [c_void_p] * 5 + [c_int64] * 8 + [c_void_p, c_size_t, c_uint32, c_void_p]
     lib.b200fp8_row_quantize.restype = ctypes.c_int
     lib.b200fp8_row_quantize.argtypes = [c_void_p, ctypes.c_int, ctypes.c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p]
     if lib.b200fp8_abi_version() != 1:

@@ -167,6 +167,37 @@ def fp8_gemm_rowwise_grouped(
     return out
 
 
+def fp8_gemm_blockwise(xq: torch.Tensor, wq: torch.Tensor, x_scale: torch.Tensor, w_scale: torch.Tensor,
+                       out: Optional[torch.Tensor] = None, tma_store: bool = True) -> torch.Tensor:
+    """128x128 block-scaled GEMM in the argument order of the reference's `matmul_fp8_block(xq, wq, x_scale, w_scale)`
+    (tritonbench/operators/fp8_gemm_blockwise/operator.py:139-149): x_scale [ceil(M/128), ceil(K/128)],
+    w_scale [ceil(N/128), ceil(K/128)] float32 (the reciprocal multipliers); returns bf16 [M, N]."""
+    for t, name in ((xq, "xq"), (wq, "wq"), (x_scale, "x_scale"), (w_scale, "w_scale")):
+        _require_cuda(t, name)
+    m, k = xq.shape
+    n = wq.shape[0]
+    kb = (k + 127) // 128
+    if tuple(x_scale.shape) != ((m + 127) // 128, kb) or tuple(w_scale.shape) != ((n + 127) // 128, kb):
+        raise ValueError("block scales must be [ceil(M/128), ceil(K/128)] and [ceil(N/128), ceil(K/128)]")
+    if x_scale.dtype != torch.float32 or w_scale.dtype != torch.float32:
+        raise ValueError("scales must be float32")
+    if x_scale.stride(1) != 1:
+        x_scale = x_scale.contiguous()
+    if w_scale.stride(1) != 1:
+        w_scale = w_scale.contiguous()
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=xq.device)
+    workspace = get_workspace(xq.device, _lib.WORKSPACE_HEADER_BYTES)
+    status = _lib.load().b200fp8_gemm_blockwise(
+        xq.data_ptr(), wq.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(), out.data_ptr(), m, n, k,
+        xq.stride(0), wq.stride(0), out.stride(0), x_scale.stride(0), w_scale.stride(0),
+        workspace.data_ptr(), workspace.numel(), 0 if tma_store else _lib.FLAG_NO_TMA_STORE,
+        torch.cuda.current_stream(xq.device).cuda_stream,
+    )
+    _lib.check(status, f"b200fp8_gemm_blockwise(M={m}, N={n}, K={k})")
+    return out
+
+
 def fp8_gemm(a: torch.Tensor, b: torch.Tensor, scale_a=None, scale_b=None, out_dtype: torch.dtype = torch.float16,
              **kw) -> torch.Tensor:
     """The call of TritonBench's `fp8_gemm` operator, `torch._scaled_mm(a, b, scale_a, scale_b, out_dtype=...)`

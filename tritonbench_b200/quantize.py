@@ -40,6 +40,21 @@ def fp8_row_quantize_fp32(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return xq, scale
 
 
+def fp8_block_quantize(x: torch.Tensor, block_m: int = 128, block_k: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Same contract as the reference's `fp8_block_quantize` (tritonbench/operators/fp8_gemm_blockwise/operator.py:87-120):
+    one multiplier 448 / blockmax per block_m x block_k block (1.0 where that is infinite), no clamp before the
+    e4m3 cast, returns (xq, 1 / multiplier as float32 [ceil(M/block_m), ceil(K/block_k)])."""
+    m, k = x.shape
+    grid_m, grid_k = -(-m // block_m), -(-k // block_k)
+    padded = torch.zeros(grid_m * block_m, grid_k * block_k, dtype=x.dtype, device=x.device)
+    padded[:m, :k] = x
+    block_max = padded.abs().reshape(grid_m, block_m, grid_k, block_k).amax(dim=(1, 3)).clamp(min=EPS)
+    mult = E4M3_MAX / block_max.to(torch.float32)
+    mult[mult == float("inf")] = 1.0
+    xq = (padded * mult.repeat_interleave(block_m, dim=0).repeat_interleave(block_k, dim=1))[:m, :k]
+    return xq.to(torch.float8_e4m3fn), 1 / mult
+
+
 def _draw(rows: int, cols: int, dist: str, std: float, gen: torch.Generator, device) -> torch.Tensor:
     """Seeded fp32 draw, chunked by rows so that large matrices never hold more than ~1 GiB of fp32."""
     if dist == "normal":

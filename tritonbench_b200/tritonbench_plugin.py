@@ -176,6 +176,51 @@ def register_grouped():
     return cls
 
 
+def b200_blockwise(self, xq, wq, x_scale, w_scale) -> Callable:
+    """Backend for `fp8_gemm_blockwise` (tritonbench/operators/fp8_gemm_blockwise/operator.py:139-149)."""
+    if not xq.is_cuda:
+        raise NotImplementedError("b200 backend runs on CUDA devices only; there is no CPU path")
+    from . import ops
+
+    x_scale = x_scale.to(xq.device).contiguous()  # the stock quantiser leaves the scales where it computed them
+    w_scale = w_scale.to(xq.device).contiguous()
+    out = torch.empty((xq.shape[0], wq.shape[0]), dtype=torch.bfloat16, device=xq.device)
+    ops.get_workspace(xq.device, 256)
+    return lambda: ops.fp8_gemm_blockwise(xq, wq, x_scale, w_scale, out=out)
+
+
+def torch_dequant_blockwise_ref(self, xq, wq, x_scale, w_scale) -> Callable:
+    """fp32 dequantise-then-matmul with the block scales expanded: the baseline column where FBGEMM is absent."""
+    m, k = xq.shape
+    n = wq.shape[0]
+    xs = x_scale.to(xq.device).repeat_interleave(128, dim=0).repeat_interleave(128, dim=1)[:m, :k]
+    ws = w_scale.to(xq.device).repeat_interleave(128, dim=0).repeat_interleave(128, dim=1)[:n, :k]
+    return lambda: ((xq.to(torch.float32) * xs) @ (wq.to(torch.float32) * ws).T).to(torch.bfloat16)
+
+
+def register_blockwise():
+    """Add the backends to the `fp8_gemm_blockwise` operator.  Its module imports fbgemm_gpu.experimental.gen_ai
+    for side effects only; where FBGEMM is absent an empty stand-in module lets it load (its own backends stay off)."""
+    if _install_fbgemm_standin() or getattr(sys.modules.get("fbgemm_gpu"), "__b200_standin__", False):
+        name = "fbgemm_gpu.experimental.gen_ai"
+        if name not in sys.modules:
+            mod = types.ModuleType(name)
+            mod.__b200_standin__ = True
+            sys.modules[name] = mod
+            sys.modules["fbgemm_gpu.experimental"].gen_ai = mod
+    from tritonbench.utils.triton_op import REGISTERED_BENCHMARKS, register_benchmark
+
+    op = "fp8_gemm_blockwise"
+    module = importlib.import_module(f"tritonbench.operators.{op}.operator")
+    cls = module.Operator
+    if BACKEND not in REGISTERED_BENCHMARKS.get(op, {}):
+        register_benchmark(operator_name=op, func_name=BACKEND, label="b200", enabled=torch.cuda.is_available())(b200_blockwise)
+        setattr(cls, BACKEND, b200_blockwise)
+        register_benchmark(operator_name=op, func_name="torch_dequant_ref", baseline=True)(torch_dequant_blockwise_ref)
+        setattr(cls, "torch_dequant_ref", torch_dequant_blockwise_ref)
+    return cls
+
+
 def _wrap_init(cls) -> None:
     stock_init = cls.__init__
     if getattr(stock_init, "__b200_wrapped__", False):
@@ -240,8 +285,12 @@ def run(argv: List[str]):
         register_grouped()
         if args.atol is None and args.rtol is None:
             args.atol, args.rtol = 1e-3, 1.6e-2
+    elif args.op == "fp8_gemm_blockwise":
+        register_blockwise()
+        if args.atol is None and args.rtol is None:
+            args.atol, args.rtol = 1e-3, 1.6e-2
     elif args.op != OP_NAME:
-        raise SystemExit(f"this plugin serves --op {OP_NAME}, fp8_gemm and fp8_gemm_rowwise_grouped only")
+        raise SystemExit(f"this plugin serves --op {OP_NAME}, fp8_gemm, fp8_gemm_rowwise_grouped and fp8_gemm_blockwise only")
     opbench = load_opbench_by_name(args.op)(tb_args=args, extra_args=extra)
     try:
         opbench.run(args.warmup, args.iter)
