@@ -10,8 +10,14 @@
 //
 //   warp 0      TMA producer (X box 128x128 B, W box 256x128 B per k-block, 4-stage ring, 128B swizzle)
 //   warp 1      TMEM owner + MMA issuer
-//   warps 2-9   promotion + epilogue: warp w owns TMEM lane quarter w%4 (32 rows) and column half
-//               (w-2)/4 (128 columns = one scale block of W): 128 fp32 accumulators per thread
+//   warps 2-3   idle (they complete the first warpgroup, which gives its registers away)
+//   warps 4-11  promotion + epilogue: warp w owns TMEM lane quarter w%4 (32 rows) and column half
+//               (w-4)/4 (128 columns = one scale block of W): 128 fp32 accumulators per thread
+//
+// A promotion thread holds 128 accumulators plus two 32-column read buffers, so that the next TMEM
+// read is in flight while the previous one is folded in; that needs about 210 registers.  The kernel
+// starts with 168 per thread (384 threads) and moves registers from the first warpgroup (40 each)
+// to the two promotion warpgroups (232 each) with setmaxnreg.
 //
 // Persistent over a static tile list; every mbarrier wait is bounded.
 #include "kernels.h"
@@ -21,7 +27,10 @@ namespace b200fp8 {
 namespace {
 
 using Geo = TcGeometry;
-constexpr int kThreadsBw = 320;
+constexpr int kThreadsBw = 384;
+constexpr int kFirstEpiWarp = 4;
+constexpr int kRegsRoles = 40;
+constexpr int kRegsPromotion = 232;  // 128 * 40 + 256 * 232 == 384 * 168
 constexpr int kStages = 4;
 constexpr int kBytesA = Geo::kBlockM * Geo::kBlockK;  // 16 KiB
 constexpr int kBytesB = Geo::kBlockN * Geo::kBlockK;  // 32 KiB
@@ -110,6 +119,8 @@ gemm_blockwise_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
+  if (warp < kFirstEpiWarp) {
+    setmaxnreg_dec<kRegsRoles>();
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0) {
@@ -167,9 +178,11 @@ gemm_blockwise_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         }
       }
     }
+  }
   } else {
     // ------------------------------ promotion + epilogue -----------------------------
-    const int epi = warp - 2;
+    setmaxnreg_inc<kRegsPromotion>();
+    const int epi = warp - kFirstEpiWarp;
     const int quarter = warp & 3;      // TMEM lanes [32*quarter, +32)
     const int half = epi >> 2;         // columns [128*half, +128) of the tile: one scale block of W
     const uint32_t sbuf = smem_epi + epi * (Geo::kStoreRows * Geo::kStoreCols * 2);
@@ -200,17 +213,28 @@ gemm_blockwise_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * Geo::kBlockN + half * 128;
+        // four 32-column reads through two buffers: read c+1 is in flight while read c is folded in
+        uint32_t part0[32], part1[32];
+        tmem_ld_32x32(t_addr, part0);
+        tmem_ld_wait_for(part0);
+        tmem_ld_32x32(t_addr + 32, part1);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint32_t part[16];
-          tmem_ld_32x16(t_addr + c * 16, part);
-          tmem_ld_wait();
+        for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(part0[j]), s, acc[j]);
+        tmem_ld_wait_for(part1);
+        tmem_ld_32x32(t_addr + 64, part0);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(__uint_as_float(part[j]), s, acc[c * 16 + j]);
-        }
+        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(__uint_as_float(part1[j]), s, acc[32 + j]);
+        tmem_ld_wait_for(part0);
+        tmem_ld_32x32(t_addr + 96, part1);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[64 + j] = fmaf(__uint_as_float(part0[j]), s, acc[64 + j]);
+        tmem_ld_wait_for(part1);
+        // the whole buffer is in registers: hand it back before the last quarter of the arithmetic
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[96 + j] = fmaf(__uint_as_float(part1[j]), s, acc[96 + j]);
       }
       if (!ok) break;
 
