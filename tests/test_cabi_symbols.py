@@ -56,13 +56,21 @@ def test_null_pointers_and_bad_sizes_are_rejected_before_any_device_work(cdll):
 
 def test_workspace_sizes_and_plans_need_no_device(cdll):
     assert cdll.b200fp8_workspace_bytes(8192, 8192, 8192, 0) == lib.WORKSPACE_HEADER_BYTES
-    skinny = cdll.b200fp8_workspace_bytes(16, 28672, 8192, 0)
+    assert cdll.b200fp8_workspace_bytes(16, 28672, 8192, 0) == lib.WORKSPACE_HEADER_BYTES  # partial sums stay on chip
+    skinny = cdll.b200fp8_workspace_bytes(16, 28672, 8192, lib.VARIANT_SKINNY)
     assert skinny > 256 * 1024  # counters + partial sums
     assert cdll.b200fp8_workspace_bytes(0, 1, 1, 0) == 0
     assert cdll.b200fp8_workspace_bytes(256, 256, 256, lib.VARIANT_SKINNY) == 0  # M > 128
     assert lib.describe_plan(8192, 8192, 8192).startswith("tc_2cta")
-    assert lib.describe_plan(300, 512, 512).startswith("tc_1cta")
-    assert lib.describe_plan(16, 28672, 8192).startswith("skinny")
+    assert lib.describe_plan(300, 512, 512).startswith("tc_splitk")  # 6 tiles of 128x256: far too few for 148 SMs
+    assert lib.describe_plan(16, 28672, 8192).startswith("tc_splitk tile=128x256x128 cluster=1")
+    long_k = lib.describe_plan(16, 2304, 16384)  # few tiles, long K: K is split inside a cluster
+    assert long_k.startswith("tc_splitk") and "cluster=1 " not in long_k
+    assert lib.describe_plan(16, 1 << 20, 1024).startswith("skinny")  # thousands of tiles: persistent stream-K
+    assert lib.describe_plan(100, 1 << 20, 1024).startswith("tc_1cta")
+    assert lib.describe_plan(16, 28672, 8192, lib.VARIANT_SKINNY).startswith("skinny")
+    forced = lib.describe_plan(16, 4096, 4096, lib.VARIANT_TC_SPLITK | lib.flag_splitk_config(64, 4))
+    assert forced.startswith("tc_splitk tile=128x64x128 cluster=4")
     assert lib.describe_plan(16, 28672, 8192, lib.VARIANT_SIMT).startswith("simt")
 
 

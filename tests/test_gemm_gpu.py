@@ -95,6 +95,32 @@ def test_cluster_split_k_kernel(cuda_device, shape):
                   orc.gemm_rowwise(xq, wq, xs, ws, out_dtype=torch.float16), "tc_splitk fp16")
 
 
+SPLIT_CONFIGS = [(256, 1), (256, 2), (256, 4), (256, 8), (128, 1), (128, 2), (128, 4), (128, 8), (64, 1), (64, 2), (64, 4)]
+
+
+@pytest.mark.parametrize("config", SPLIT_CONFIGS)
+def test_every_tile_width_and_cluster_size_of_the_one_tile_per_cluster_kernel(cuda_device, config):
+    """B200FP8_FLAG_SPLITK_CONFIG: each (tile width, cluster size) on a decode shape (X stage of 8 rows, deep
+    ring), a ragged mid-size shape (tails in M, N and K, several row tiles) and a K shorter than the split."""
+    for m, n, k in [(5, 1000, 2320), (300, 520, 1424), (64, 256, 128)]:
+        xq, wq, xs, ws = _inputs(m, n, k, seed=m + n + k)
+        ref = orc.gemm_rowwise(xq, wq, xs, ws)
+        y = _run("tc_splitk", xq, wq, xs, ws, split_config=config)
+        _assert_close(y, ref, f"tc_splitk {config} {(m, n, k)}")
+        assert torch.equal(_run("tc_splitk", xq, wq, xs, ws, split_config=config, overlap=True), y)
+        _assert_close(_run("tc_splitk", xq, wq, xs, ws, split_config=config, tma_store=False), ref,
+                      f"tc_splitk {config} {(m, n, k)} plain stores")
+
+
+def test_split_config_flag_rejects_impossible_combinations(cuda_device):
+    ops = _ops()
+    xq, wq, xs, ws = _gpu(*_inputs(16, 256, 512))
+    for bad in [(64, 8), (192, 1), (128, 3)]:
+        with pytest.raises(Exception):
+            ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="tc_splitk", split_config=bad)
+    ops.check_device_status()
+
+
 SKINNY_SHAPES = [
     (1, 8, 16), (1, 256, 512), (3, 1000, 1040), (8, 2304, 2304), (16, 1024, 1024), (17, 520, 400), (33, 4096, 2304),
     (64, 4096, 2048), (100, 1000, 4096), (128, 2304, 6656), (127, 129, 144),
@@ -113,7 +139,9 @@ def test_skinny_workspace_survives_changes_of_geometry(cuda_device):
     """One workspace, problem sizes with different tile counts back to back: the counters a call
     leaves behind must still be zero where the next call looks for its own."""
     ops = _ops()
-    ws_bytes = max(ops.workspace_bytes(m, n, k) for (m, n, k) in SKINNY_SHAPES)
+    from tritonbench_b200 import lib
+
+    ws_bytes = max(ops.workspace_bytes(m, n, k, lib.VARIANT_SKINNY) for (m, n, k) in SKINNY_SHAPES)
     workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
     for rep in range(2):
         for (m, n, k) in [(64, 4096, 2048), (1, 8192, 4096), (100, 1000, 4096), (8, 2304, 2304), (16, 1024, 1024)]:
@@ -329,21 +357,23 @@ def test_call_is_capturable_in_a_cuda_graph(cuda_device):
     ops.check_device_status()
 
 
-def test_overlapped_launch_of_decode_kernels_back_to_back(cuda_device):
+@pytest.mark.parametrize("variant", ["auto", "tc_splitk", "skinny"])
+def test_overlapped_launch_of_decode_kernels_back_to_back(cuda_device, variant):
     """B200FP8_FLAG_PDL: each kernel may start while the one before it still runs and reads only W that
     early.  A chain of decode GEMMs of different shapes, sharing one workspace and launched without any
     host synchronisation in between, must give the same bits as the ordinary launches."""
     ops = _ops()
+    from tritonbench_b200 import lib
     shapes = [(16, 28672, 8192), (1, 4096, 2304), (16, 28672, 8192), (64, 4096, 2048), (8, 2304, 2304), (128, 2304, 6656)]
     cases = []
     for i, (m, n, k) in enumerate(shapes):
         xq, wq, xs, ws = _gpu(*_inputs(m, n, k, seed=20 + i, w_std=0.02))
-        cases.append((xq, wq, xs, ws, ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="skinny")))
-    ws_bytes = max(ops.workspace_bytes(m, n, k) for (m, n, k) in shapes)
+        cases.append((xq, wq, xs, ws, ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant=variant)))
+    ws_bytes = max(ops.workspace_bytes(m, n, k, lib.VARIANTS[variant]) for (m, n, k) in shapes)
     workspace = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
     torch.cuda.synchronize()
     for rep in range(3):
-        outs = [ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="skinny", workspace=workspace, overlap=True)
+        outs = [ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant=variant, workspace=workspace, overlap=True)
                 for (xq, wq, xs, ws, _) in cases]
         torch.cuda.synchronize()
         for out, case in zip(outs, cases):
@@ -354,7 +384,7 @@ def test_overlapped_launch_of_decode_kernels_back_to_back(cuda_device):
     for rep in range(3):
         scratch = torch.zeros_like(x_bytes)
         scratch.copy_(x_bytes)  # the copy kernel is the immediate predecessor on the stream
-        got = ops.fp8_gemm_rowwise(scratch.view(torch.float8_e4m3fn), wq, xs, ws, variant="skinny", overlap=True)
+        got = ops.fp8_gemm_rowwise(scratch.view(torch.float8_e4m3fn), wq, xs, ws, variant=variant, overlap=True)
         assert torch.equal(got, want)
     ops.check_device_status()
 

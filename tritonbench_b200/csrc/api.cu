@@ -21,6 +21,7 @@ struct DeviceInfo {
   int cc_major = 0;
   int sm_count = 0;
   int max_pair_clusters = 0;
+  int split_clusters[4] = {0, 0, 0, 0};  // resident clusters of 1, 2, 4, 8 CTAs of the one-tile-per-cluster kernel
 };
 
 std::mutex g_mutex;
@@ -45,6 +46,11 @@ int device_info(DeviceInfo* out) {
     e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return note_cuda(e);
     d.max_pair_clusters = d.sm_count / 2;
+    d.split_clusters[0] = d.sm_count;
+    for (int i = 1; i < 4; ++i) {
+      d.split_clusters[i] = d.cc_major == 10 ? splitk_resident_clusters(1 << i, &e) : 0;
+      if (d.split_clusters[i] <= 0) d.split_clusters[i] = (d.sm_count * 7 / 8) >> i;  // query unavailable: a guess
+    }
     d.known = true;
   }
   if (g_encode == nullptr) {
@@ -88,8 +94,7 @@ struct Plan {
   bool tma_store;
   int num_ctas;      // tcgen05 variants
   int group_m;
-  int split;         // cluster split-K variant: CTAs per tile
-  int tiles;         // cluster split-K variant: 128x256 tiles
+  SplitPlan splitk;  // one-tile-per-cluster variant
   SkinnyPlan skinny;  // skinny variant
   size_t workspace_bytes;
 };
@@ -100,24 +105,85 @@ bool tma_loadable(int64_t K, int64_t ldx, int64_t ldw, const void* xq, const voi
   return ldx % 16 == 0 && ldw % 16 == 0 && aligned16(xq) && aligned16(wq);
 }
 
-// Cost model for the few-tile case, in units of one k-block of main loop: waves x (k-blocks per CTA + fixed
-// cost of a CTA) + the exchange.  Returns the number of CTAs that should share a tile's K range (1, 2 or 4).
-int best_split(int64_t M, int64_t N, int64_t K, int sm_count) {
-  const int64_t tiles = ((M + 127) / 128) * ((N + 255) / 256);
-  const int64_t kb = (K + TcGeometry::kBlockK - 1) / TcGeometry::kBlockK;
-  const int64_t fixed = 12, exchange = 6;
-  int best = 1;
-  int64_t best_cost = ((tiles + sm_count - 1) / sm_count) * (kb + fixed);
-  for (int s = 2; s <= 4; s *= 2) {
-    if (kb / s < 4) break;
-    const int64_t cost = ((tiles * s + sm_count - 1) / sm_count) * ((kb + s - 1) / s + fixed) + exchange;
-    if (cost < best_cost) {
-      best_cost = cost;
-      best = s;
+}  // namespace
+
+namespace b200fp8 {
+
+// Cost model of the one-tile-per-cluster kernel, in microseconds, fitted to graph-replay timings of every
+// (block_n, split) on 45 shapes (mean regret of the model's pick against the best measured: 6 %).
+// A CTA's main loop is the slowest of: its bytes at the rate its ring sustains (bytes in flight / latency),
+// its MMAs, and the whole wave's bytes at chip bandwidth (L2 for re-read operands, HBM for the unique bytes).
+// Then the DSMEM exchange and the epilogue; all of it once per wave of resident clusters.
+double split_plan_cost_us(long long M, long long N, long long K, int block_n, int split, int resident_clusters) {
+  const double kLaunch = 2.0, kLatency = 1.7, kRingLatency = 1.31, kMmaPerColumn = 1.28e-3;
+  const double kL2BytesPerUs = 11.4e6, kHbmBytesPerUs = 6.0e6, kL2ResidentBytes = 120.0e6;
+  const double kHbmBytesPerUsPerSm = 0.058e6;
+  const double kExchangeFixed = 0.21, kExchangePerByte = 32.2e-6, kEpilogue = 1.2;
+  const long long tiles = ((M + 127) / 128) * ((N + block_n - 1) / block_n);
+  const long long kb = (K + TcGeometry::kBlockK - 1) / TcGeometry::kBlockK;
+  const long long kb_per = (kb + split - 1) / split;
+  const long long rows_a = M >= 128 ? 128 : (M + 7) / 8 * 8;
+  const long long waves = (tiles + resident_clusters - 1) / resident_clusters;
+  const double stage_bytes = static_cast<double>((rows_a + block_n) * TcGeometry::kBlockK);
+  long long stages = SplitGeometry::kRingBytes / static_cast<long long>(stage_bytes);
+  if (stages > SplitGeometry::kMaxStages) stages = SplitGeometry::kMaxStages;
+  if (stages > kb_per) stages = kb_per;
+  const double cta_bytes = static_cast<double>(kb_per) * stage_bytes;
+  const double ring = kLatency + cta_bytes / (static_cast<double>(stages) * stage_bytes / kRingLatency);
+  const double mma = kLatency + static_cast<double>(kb_per * block_n) * kMmaPerColumn;
+  const long long concurrent = (tiles < resident_clusters ? tiles : resident_clusters) * split;
+  const double unique_bytes = static_cast<double>(M + N) * static_cast<double>(K);
+  double chip = static_cast<double>(concurrent) * cta_bytes / kL2BytesPerUs;
+  // operands beyond what L2 can hold between calls come from HBM whatever the access pattern
+  // one SM draws about 58 GB/s from HBM with 32 KiB boxes of W however deep its ring (46 with 16 KiB
+  // boxes, 29 with 8 KiB): few CTAs cannot saturate the memory
+  const double box_factor = block_n == 256 ? 1.0 : (block_n == 128 ? 0.8 : 0.5);
+  double hbm_rate = static_cast<double>(concurrent) * kHbmBytesPerUsPerSm * box_factor;
+  if (hbm_rate > kHbmBytesPerUs) hbm_rate = kHbmBytesPerUs;
+  const double hbm = unique_bytes / static_cast<double>(waves) / hbm_rate;
+  if (unique_bytes > kL2ResidentBytes && hbm > chip) chip = hbm;
+  chip += kLatency;
+  double main_loop = ring > mma ? ring : mma;
+  if (chip > main_loop) main_loop = chip;
+  const long long rows_sent = M < 128 ? M : 128;
+  const double exchange =
+      split > 1 ? kExchangeFixed + kExchangePerByte * static_cast<double>(rows_sent * block_n * 4 * (split - 1) / split)
+                : 0.0;
+  return kLaunch + static_cast<double>(waves) * (main_loop + exchange + kEpilogue);
+}
+
+// forced_block_n / forced_split: 0 = choose by the cost model
+SplitPlan make_split_plan(long long M, long long N, long long K, const int* resident_clusters, int forced_block_n,
+                          int forced_split) {
+  SplitPlan best = {256, 1, 128, 4, 0, 1, false};
+  double best_cost = 1e30;
+  const long long kb = (K + TcGeometry::kBlockK - 1) / TcGeometry::kBlockK;
+  for (int block_n = 256; block_n >= 64; block_n /= 2) {
+    if (forced_block_n != 0 && block_n != forced_block_n) continue;
+    for (int split = 1, log2_split = 0; split <= 8; split *= 2, ++log2_split) {
+      if (block_n / split < 16) break;
+      if (forced_split != 0 && split != forced_split) continue;
+      if (forced_split == 0 && split > 1 && kb / split < 2) break;
+      const double cost = split_plan_cost_us(M, N, K, block_n, split, resident_clusters[log2_split]);
+      if (cost < best_cost) {
+        best_cost = cost;
+        best.block_n = block_n;
+        best.split = split;
+        best.waves = static_cast<int>((((M + 127) / 128) * ((N + block_n - 1) / block_n) + resident_clusters[log2_split] - 1) /
+                                      resident_clusters[log2_split]);
+      }
     }
   }
+  best.rows_a = M >= 128 ? 128 : static_cast<int>((M + 7) / 8 * 8);
+  best.stages = SplitGeometry::kRingBytes / ((best.rows_a + best.block_n) * TcGeometry::kBlockK);
+  if (best.stages > SplitGeometry::kMaxStages) best.stages = SplitGeometry::kMaxStages;
+  best.tiles = static_cast<int>(((M + 127) / 128) * ((N + best.block_n - 1) / best.block_n));
   return best;
 }
+
+}  // namespace b200fp8
+
+namespace {
 
 int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma_ok, bool y_tma_ok,
               const DeviceInfo& dev, Plan* out) {
@@ -128,13 +194,18 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
     if (!operands_tma_ok) {
       v = B200FP8_VARIANT_SIMT;
     } else if (M <= SkinnyGeometry::kMaxTokens) {
-      v = B200FP8_VARIANT_SKINNY;
+      // one tile per cluster while the output is narrow enough for a wave or two of clusters; beyond
+      // that a persistent kernel: stream-K for a handful of tokens, whole tiles otherwise
+      const SplitPlan sp = make_split_plan(M, N, K, dev.split_clusters, 0, 0);
+      v = sp.waves <= 2 ? B200FP8_VARIANT_TC_SPLITK : (M <= 32 ? B200FP8_VARIANT_SKINNY : B200FP8_VARIANT_TC_1CTA);
     } else {
       // a CTA pair per 256x256 tile halves the shared-memory fill per flop; keep single CTAs when
       // the pair tiles could not occupy the SMs anyway
       const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
       v = pair_tiles >= dev.sm_count / 2 ? B200FP8_VARIANT_TC_2CTA : B200FP8_VARIANT_TC_1CTA;
-      if (v == B200FP8_VARIANT_TC_1CTA && best_split(M, N, K, dev.sm_count) > 1) v = B200FP8_VARIANT_TC_SPLITK;
+      if (v == B200FP8_VARIANT_TC_1CTA && ((M + 127) / 128) * ((N + 255) / 256) < dev.sm_count) {
+        v = B200FP8_VARIANT_TC_SPLITK;
+      }
     }
   } else if (v != B200FP8_VARIANT_SIMT && !operands_tma_ok) {
     return B200FP8_UNSUPPORTED_ALIGNMENT;
@@ -156,9 +227,15 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
     const int64_t clusters = tiles < dev.max_pair_clusters ? tiles : dev.max_pair_clusters;
     pl.num_ctas = static_cast<int>(2 * clusters);
   } else if (v == B200FP8_VARIANT_TC_SPLITK) {
-    pl.tiles = static_cast<int>(((M + 127) / 128) * ((N + 255) / 256));
-    pl.split = best_split(M, N, K, dev.sm_count);
-    if (pl.split < 2) pl.split = 2;  // forced variant on a shape the model would not split
+    const int forced_block_n = static_cast<int>((flags >> 8) & 0xFu) * 64;
+    const int forced_split = static_cast<int>((flags >> 12) & 0xFu);
+    if ((forced_block_n != 0 && forced_block_n != 64 && forced_block_n != 128 && forced_block_n != 256) ||
+        (forced_split != 0 && forced_split != 1 && forced_split != 2 && forced_split != 4 && forced_split != 8) ||
+        (forced_block_n != 0 && forced_split != 0 && forced_block_n / forced_split < 16)) {
+      return B200FP8_BAD_ARG;
+    }
+    pl.splitk = make_split_plan(M, N, K, dev.split_clusters, forced_block_n, forced_split);
+    pl.splitk.overlap_previous_kernel = (flags & B200FP8_FLAG_PDL) != 0;
   } else if (v == B200FP8_VARIANT_SKINNY) {
     pl.skinny = make_skinny_plan(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), dev.sm_count);
     pl.skinny.overlap_previous_kernel = (flags & B200FP8_FLAG_PDL) != 0;
@@ -206,6 +283,10 @@ size_t b200fp8_workspace_bytes(int64_t M, int64_t N, int64_t K, uint32_t flags) 
     // no usable device: size for the largest B200 configuration so that callers can still plan
     dev.sm_count = 148;
     dev.max_pair_clusters = 74;
+    dev.split_clusters[0] = 148;
+    dev.split_clusters[1] = 74;
+    dev.split_clusters[2] = 33;
+    dev.split_clusters[3] = 15;
   }
   Plan pl;
   if (make_plan(M, N, K, flags, true, true, dev, &pl) != B200FP8_OK) return 0;
@@ -284,10 +365,12 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
   const int cta_group = pl.variant == B200FP8_VARIANT_TC_2CTA ? 2 : 1;
   CUtensorMap tm_x, tm_w, tm_y;
   memset(&tm_y, 0, sizeof(tm_y));
-  st = encode_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, M, K, ldx, TcGeometry::kBlockK, TcGeometry::kBlockM);
+  const int x_box_rows = pl.variant == B200FP8_VARIANT_TC_SPLITK ? pl.splitk.rows_a : TcGeometry::kBlockM;
+  st = encode_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, M, K, ldx, TcGeometry::kBlockK, x_box_rows);
   if (st != B200FP8_OK) return st;
-  st = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, N, K, ldw, TcGeometry::kBlockK,
-                 TcGeometry::kBlockN / cta_group);
+  const int w_box_rows =
+      pl.variant == B200FP8_VARIANT_TC_SPLITK ? pl.splitk.block_n : TcGeometry::kBlockN / cta_group;
+  st = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, N, K, ldw, TcGeometry::kBlockK, w_box_rows);
   if (st != B200FP8_OK) return st;
   if (pl.tma_store) {
     st = encode_2d(&tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y, M, N, ldy * 2, TcGeometry::kStoreCols,
@@ -308,7 +391,7 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
   tp.group_m = pl.group_m;
   tp.status = status_word;
   if (pl.variant == B200FP8_VARIANT_TC_SPLITK) {
-    return note_cuda(launch_gemm_splitk(tm_x, tm_w, tm_y, tp, pl.tiles, pl.split, stream));
+    return note_cuda(launch_gemm_splitk(tm_x, tm_w, tm_y, tp, pl.splitk, stream));
   }
   if (cta_group == 2) return note_cuda(launch_gemm_tc<2>(tm_x, tm_w, tm_y, tp, pl.num_ctas, stream));
   return note_cuda(launch_gemm_tc<1>(tm_x, tm_w, tm_y, tp, pl.num_ctas, stream));
@@ -512,6 +595,10 @@ int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char*
   if (device_info(&dev) != B200FP8_OK) {
     dev.sm_count = 148;
     dev.max_pair_clusters = 74;
+    dev.split_clusters[0] = 148;
+    dev.split_clusters[1] = 74;
+    dev.split_clusters[2] = 33;
+    dev.split_clusters[3] = 15;
   }
   Plan pl;
   st = make_plan(M, N, K, flags, true, true, dev, &pl);
@@ -526,8 +613,12 @@ int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char*
                TcConfig<2>::kStages, pl.num_ctas, pl.group_m, TcConfig<2>::kSmemBytes, pl.workspace_bytes);
       break;
     case B200FP8_VARIANT_TC_SPLITK:
-      snprintf(buf, n, "tc_splitk tile=128x256x128 cluster=%d (K split, DSMEM reduce-scatter) stages=4 ctas=%d workspace=%zu",
-               pl.split, pl.tiles * pl.split, pl.workspace_bytes);
+      snprintf(buf, n,
+               "tc_splitk tile=128x%dx128 cluster=%d (K split, DSMEM reduce-scatter) x_rows=%d stages=%d ctas=%d "
+               "resident_clusters=%d/%d/%d/%d workspace=%zu",
+               pl.splitk.block_n, pl.splitk.split, pl.splitk.rows_a, pl.splitk.stages,
+               pl.splitk.tiles * pl.splitk.split, dev.split_clusters[0],
+               dev.split_clusters[1], dev.split_clusters[2], dev.split_clusters[3], pl.workspace_bytes);
       break;
     case B200FP8_VARIANT_SKINNY:
       snprintf(buf, n,

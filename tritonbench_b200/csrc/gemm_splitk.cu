@@ -1,18 +1,28 @@
-// FP8 rowwise GEMM for problems with few output tiles and a long K: split-K inside a thread-block
-// cluster, reduced over distributed shared memory.
+// FP8 rowwise GEMM for problems whose output has too few 128x256 tiles to occupy the GPU with the
+// persistent kernels: narrower tiles, and split-K inside a thread-block cluster, reduced over
+// distributed shared memory.
 //
-// A cluster of S CTAs (S = 2 or 4) owns one 128x256 tile of Y.  CTA r multiplies the r-th slice of K
-// with the usual pipeline (TMA -> 128B-swizzled ring -> tcgen05.mma -> TMEM).  Then
+// A cluster of S CTAs (S = 1, 2, 4 or 8) owns one 128 x BN tile of Y (BN = 64, 128 or 256).  CTA r
+// multiplies the r-th slice of K with the usual pipeline (TMA -> 128B-swizzled ring -> tcgen05.mma ->
+// TMEM); the ring is deep enough that a short slice is requested from memory all at once.  Then, S > 1:
 //   (A) cluster barrier: every CTA's MMAs have finished, so every operand ring is free;
-//   exchange: each CTA writes its fp32 partial tile, column slice j (256/S columns) to CTA j,
+//   exchange: each CTA writes its fp32 partial tile, column slice j (BN/S columns) to CTA j,
 //   into CTA j's (now idle) operand ring through shared::cluster stores - a reduce-scatter;
 //   (B) cluster barrier: all partials have landed;
 //   each CTA adds the S partials of its column slice in CTA order (fixed, deterministic),
-//   applies the scales, rounds and stores its 128 x 256/S part of the tile.
-// Partial sums never leave the SMs, and the epilogue is spread over the S CTAs.
+//   applies the scales, rounds and stores its 128 x BN/S part of the tile.
+// Partial sums never leave the SMs, and the epilogue is spread over the S CTAs.  With S = 1 the
+// epilogue reads the accumulator straight from TMEM.  Rows of the tile beyond M are neither exchanged
+// nor stored, so a decode-sized M costs a decode-sized epilogue.
+//
+// With `overlap_previous_kernel` the kernel is launched with programmatic stream serialization: its
+// set-up and its first W loads run while the previous kernel on the stream drains; X is read, and Y
+// written, only after that kernel has completed.
 //
 // Every mbarrier wait is bounded; a CTA that gives up still arrives at both cluster barriers so
 // that its peers are never left waiting.
+#include <type_traits>
+
 #include "kernels.h"
 #include "ptx.cuh"
 
@@ -20,14 +30,23 @@ namespace b200fp8 {
 namespace {
 
 using Geo = TcGeometry;
-constexpr int kStages = 4;
-constexpr int kBytesA = Geo::kBlockM * Geo::kBlockK;   // 16 KiB
-constexpr int kBytesB = Geo::kBlockN * Geo::kBlockK;   // 32 KiB
-constexpr int kRingBytes = kStages * (kBytesA + kBytesB);            // 192 KiB, reused for the exchange
-constexpr int kExchangeBytes = Geo::kBlockM * Geo::kBlockN * 4;      // 128 KiB of fp32 partials per CTA
-constexpr int kEpiBytes = 4 * 2 * Geo::kStoreRows * Geo::kStoreCols * 2;
-constexpr int kBarBytes = 256;
-static_assert(kExchangeBytes <= kRingBytes, "the exchange buffer lives in the operand ring");
+
+// The operand ring is 192 KiB whatever the tile: a stage is `rows_a` rows of X (M rounded up to 8, at most
+// 128; the MMA reads 128 rows, the rows never loaded only feed output rows that do not exist) and kBlockN
+// rows of W, and as many stages as fit are kept in flight - for a decode-sized M almost all of them W.
+template <int kBlockN>
+struct Cfg {
+  static constexpr int kBytesB = kBlockN * Geo::kBlockK;       // 8 / 16 / 32 KiB
+  static constexpr int kRingBytes = 192 * 1024;                // reused for the exchange
+  static constexpr int kExchangeBytes = Geo::kBlockM * kBlockN * 4; // fp32 partials a CTA receives
+  static constexpr int kEpiBytes = 4 * 2 * Geo::kStoreRows * Geo::kStoreCols * 2;
+  static constexpr int kScaleBytes = kBlockN * 4;  // w_scale of the CTA's column slice
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSmemBytes = kRingBytes + kEpiBytes + kScaleBytes + kBarBytes + 1024;
+  static_assert(kExchangeBytes <= kRingBytes, "the exchange buffer lives in the operand ring");
+  static_assert(16 * SplitGeometry::kMaxStages + 16 <= kBarBytes, "barrier block");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
+};
 
 enum WaitSite : uint32_t {
   kSiteProducerEmpty = 0x301,
@@ -46,27 +65,130 @@ __device__ __forceinline__ float4 ld_shared_v4(uint32_t addr) {
   return v;
 }
 
+template <int kCols>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[kCols]) {
+  if constexpr (kCols == 32) {
+    tmem_ld_32x32(taddr, r);
+  } else {
+    tmem_ld_32x16(taddr, r);
+  }
+}
+
 // Exchange buffer of a CTA: [sender][group of 4 columns of its slice][row][4 columns] fp32, so that a warp
 // (32 consecutive rows) moves 512 contiguous bytes per instruction.
 __device__ __forceinline__ uint32_t exchange_offset(int sender, int slice_cols, int col_in_slice, int row) {
   return static_cast<uint32_t>((((sender * (slice_cols / 4) + col_in_slice / 4) * Geo::kBlockM) + row) * 16);
 }
 
+// Everything one epilogue warp needs to finish columns of its 32 rows, by value: a pointer to the
+// kernel's parameter block would turn every field access into a load the compiler cannot keep in a register.
+struct Finish {
+  uint16_t* y_row;         // &Y[row][first column of this CTA's slice]
+  uint32_t scales;         // shared address: w_scale of the slice, zero beyond N
+  const __nv_bfloat16* bias;  // bias of the slice's first column, or null
+  uint32_t exchange_base;  // shared address of the exchange buffer (split > 1)
+  uint32_t t_addr;         // TMEM address of this warp's lanes at the slice's first column (split == 1)
+  int split, slice_cols, tile_row, lane;
+  int cols_valid;          // columns of the slice that exist in Y
+  float xs;
+  bool row_valid;
+  bool out_fp16;
+  bool boxed;              // slice is a multiple of 64 columns and Y can take TMA stores
+  bool vector_ok;          // rows of Y start on 16-byte boundaries
+};
+
+// Sum (or read), scale and round `kCols` columns starting at `c_in_slice`, then store them: into the
+// staging box (flushed by the caller every 64 columns), or straight to Y.
+template <int kCols>
+__device__ __forceinline__ void finish_columns(const Finish& f, int c_in_slice, uint32_t sbuf) {
+  float v[kCols];
+  if (f.split == 1) {
+    uint32_t raw[kCols];
+    tmem_ld_cols<kCols>(f.t_addr + c_in_slice, raw);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) v[j] = __uint_as_float(raw[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) v[j] = 0.0f;
+    for (int sender = 0; sender < f.split; ++sender) {  // CTA order: the sum does not depend on timing
+      const uint32_t src = f.exchange_base + exchange_offset(sender, f.slice_cols, c_in_slice, f.tile_row);
+#pragma unroll
+      for (int j = 0; j < kCols / 4; ++j) {
+        const float4 t = ld_shared_v4(src + j * Geo::kBlockM * 16);
+        v[4 * j + 0] += t.x;
+        v[4 * j + 1] += t.y;
+        v[4 * j + 2] += t.z;
+        v[4 * j + 3] += t.w;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kCols / 4; ++j) {  // columns beyond N carry a zero scale
+    const float4 ws = ld_shared_v4(f.scales + (c_in_slice + 4 * j) * 4);
+    v[4 * j + 0] *= f.xs * ws.x;
+    v[4 * j + 1] *= f.xs * ws.y;
+    v[4 * j + 2] *= f.xs * ws.z;
+    v[4 * j + 3] *= f.xs * ws.w;
+  }
+  if (f.bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) {
+      if (c_in_slice + j < f.cols_valid) v[j] += __bfloat162float(f.bias[c_in_slice + j]);
+    }
+  }
+  uint32_t packed[kCols / 2];
+#pragma unroll
+  for (int j = 0; j < kCols / 2; ++j) {
+    packed[j] = f.out_fp16 ? pack_f16x2(v[2 * j], v[2 * j + 1]) : pack_bf16x2(v[2 * j], v[2 * j + 1]);
+  }
+  if (f.boxed) {
+    const uint32_t row_addr = sbuf + f.lane * 128;
+    const int chunk0 = (c_in_slice % Geo::kStoreCols) / 8;  // 16-byte chunk inside the 128-byte box row
+#pragma unroll
+    for (int j = 0; j < kCols / 8; ++j) {
+      const uint32_t chunk = static_cast<uint32_t>((chunk0 + j) ^ (f.lane & 7));
+      st_shared_v4(row_addr + chunk * 16, packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+    }
+  } else if (f.row_valid) {
+    uint16_t* dst = f.y_row + c_in_slice;
+    if (f.vector_ok && c_in_slice + kCols <= f.cols_valid) {
+#pragma unroll
+      for (int j = 0; j < kCols / 8; ++j) {
+        *reinterpret_cast<uint4*>(dst + 8 * j) =
+            make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kCols; ++j) {
+        if (c_in_slice + j < f.cols_valid) dst[j] = static_cast<uint16_t>(packed[j / 2] >> (16 * (j & 1)));
+      }
+    }
+  }
+}
+
+template <int kBlockN>
 __global__ void __launch_bounds__(Geo::kThreads, 1)
 gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                   const __grid_constant__ CUtensorMap tm_y, const TcParams p, const int split) {
+                   const __grid_constant__ CUtensorMap tm_y, const TcParams p, const int split, const int overlap,
+                   const int rows_a, const int stages) {
+  using C = Cfg<kBlockN>;
+  constexpr int kMaxStages = SplitGeometry::kMaxStages;
+  const int bytes_a = rows_a * Geo::kBlockK;  // a multiple of 1024: whole 8-row swizzle atoms
+  const uint32_t stage_tx = static_cast<uint32_t>(bytes_a + C::kBytesB);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw_addr);
 
   const uint32_t smem_a = base;
-  const uint32_t smem_b = smem_a + kStages * kBytesA;
-  const uint32_t smem_epi = base + kRingBytes;
-  const uint32_t bars = smem_epi + kEpiBytes;
-  const uint32_t bar_full = bars;                  // [kStages]
-  const uint32_t bar_empty = bars + 8 * kStages;   // [kStages]
-  const uint32_t bar_tmem_full = bars + 16 * kStages;
+  const uint32_t smem_b = smem_a + stages * bytes_a;  // the MMA's 128-row reads of a short X stage end in here
+  const uint32_t smem_epi = base + C::kRingBytes;
+  const uint32_t smem_scales = smem_epi + C::kEpiBytes;
+  const uint32_t bars = smem_scales + C::kScaleBytes;
+  const uint32_t bar_full = bars;                     // [stages]
+  const uint32_t bar_empty = bars + 8 * kMaxStages;   // [stages]
+  const uint32_t bar_tmem_full = bars + 16 * kMaxStages;
   const uint32_t tmem_slot = bar_tmem_full + 8;
   uint8_t* tail_ptr = base_ptr + (tmem_slot - base);
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(tail_ptr);
@@ -74,23 +196,31 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int rank = static_cast<int>(cluster_ctarank());
+  const int rank = split > 1 ? static_cast<int>(cluster_ctarank()) : 0;
   const int tile = blockIdx.x / split;
   const int tiles_m = (p.M + Geo::kBlockM - 1) / Geo::kBlockM;
   const int m_tile = tile % tiles_m;
   const int n_tile = tile / tiles_m;
   const int row_base = m_tile * Geo::kBlockM;
-  const int col_base = n_tile * Geo::kBlockN;
+  const int col_base = n_tile * kBlockN;
 
   const int num_kb = (p.K + Geo::kBlockK - 1) / Geo::kBlockK;
   const int kb_per = (num_kb + split - 1) / split;
   const int kb0 = rank * kb_per < num_kb ? rank * kb_per : num_kb;
   const int kb1 = kb0 + kb_per < num_kb ? kb0 + kb_per : num_kb;
   const bool has_work = kb1 > kb0;
-  const int slice_cols = Geo::kBlockN / split;  // columns of the tile this CTA finishes
+  // Tiles of one row of tiles read the same X boxes.  Each starts its K slice at a different k-block and
+  // wraps around, so that at any moment the CTAs ask different L2 lines for X instead of all the same one.
+  const int kb_len = kb1 - kb0;
+  const int kb_rot = has_work ? (n_tile * 5) % kb_len : 0;
+  auto kb_at = [&](int i) {  // the i-th k-block this CTA multiplies
+    const int j = i + kb_rot;
+    return kb0 + (j >= kb_len ? j - kb_len : j);
+  };
+  const int slice_cols = kBlockN / split;  // columns of the tile this CTA finishes (16, 32 or a multiple of 64)
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
@@ -100,36 +230,44 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     prefetch_tensormap(&tm_x);
     prefetch_tensormap(&tm_w);
     if (p.use_tma_store) prefetch_tensormap(&tm_y);
-    // the first pass over the ring needs no waiting: start it before the set-up barrier
-    for (int kb = kb0; kb < kb1 && kb < kb0 + kStages; ++kb) {
-      const int stage = kb - kb0;
-      const uint32_t full = bar_full + 8 * stage;
-      mbar_arrive_expect_tx(full, kBytesA + kBytesB);
-      tma_load_2d(smem_a + stage * kBytesA, &tm_x, full, kb * Geo::kBlockK, row_base);
-      tma_load_2d(smem_b + stage * kBytesB, &tm_w, full, kb * Geo::kBlockK, col_base);
+    // the first pass over the ring needs no waiting: start it before the set-up barrier.  W (weights) may
+    // be read while the previous kernel still runs; X only after it has completed.
+    for (int i = 0; i < kb_len && i < stages; ++i) {
+      const uint32_t full = bar_full + 8 * i;
+      mbar_arrive_expect_tx(full, stage_tx);
+      tma_load_2d(smem_b + i * C::kBytesB, &tm_w, full, kb_at(i) * Geo::kBlockK, col_base);
+    }
+    if (overlap) griddep_wait();
+    for (int i = 0; i < kb_len && i < stages; ++i) {
+      tma_load_2d(smem_a + i * bytes_a, &tm_x, bar_full + 8 * i, kb_at(i) * Geo::kBlockK, row_base);
     }
   }
   if (warp == 1) {
-    tmem_alloc<1>(tmem_slot, 256);
+    tmem_alloc<1>(tmem_slot, kBlockN);
     tmem_relinquish<1>();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  if (overlap) {
+    griddep_launch_dependents();
+    griddep_wait();  // thread 0 has passed it already: everything below may touch X, the scales and Y
+  }
 
   bool ok = true;
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t stage = 0, phase = 1;  // the first kStages k-blocks were issued before the set-up barrier
-      for (int kb = kb0 + kStages; kb < kb1; ++kb) {
+      uint32_t stage = 0, phase = 1;  // the first `stages` k-blocks were issued before the set-up barrier
+      for (int i = stages; i < kb_len; ++i) {
+        const int kb = kb_at(i);
         ok = mbar_wait<false>(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, kSiteProducerEmpty);
         if (!ok) break;
         const uint32_t full = bar_full + 8 * stage;
-        mbar_arrive_expect_tx(full, kBytesA + kBytesB);
-        tma_load_2d(smem_a + stage * kBytesA, &tm_x, full, kb * Geo::kBlockK, row_base);
-        tma_load_2d(smem_b + stage * kBytesB, &tm_w, full, kb * Geo::kBlockK, col_base);
-        if (++stage == kStages) {
+        mbar_arrive_expect_tx(full, stage_tx);
+        tma_load_2d(smem_a + stage * bytes_a, &tm_x, full, kb * Geo::kBlockK, row_base);
+        tma_load_2d(smem_b + stage * C::kBytesB, &tm_w, full, kb * Geo::kBlockK, col_base);
+        if (++stage == static_cast<uint32_t>(stages)) {
           stage = 0;
           phase ^= 1u;
         }
@@ -137,166 +275,201 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0 && has_work) {
-      constexpr uint32_t idesc = instr_desc_e4m3(Geo::kBlockM, Geo::kBlockN);
+      constexpr uint32_t idesc = instr_desc_e4m3(Geo::kBlockM, kBlockN);
       uint32_t stage = 0, phase = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      for (int i = 0; i < kb_len; ++i) {
         ok = mbar_wait<false>(bar_full + 8 * stage, phase, abort_flag, p.status, kSiteMmaFull);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint64_t a_desc = smem_desc_k_sw128(smem_a + stage * kBytesA);
-        const uint64_t b_desc = smem_desc_k_sw128(smem_b + stage * kBytesB);
+        const uint64_t a_desc = smem_desc_k_sw128(smem_a + stage * bytes_a);
+        const uint64_t b_desc = smem_desc_k_sw128(smem_b + stage * C::kBytesB);
 #pragma unroll
         for (int k = 0; k < Geo::kBlockK / 32; ++k) {
-          tc_mma_f8<1>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          tc_mma_f8<1>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(bar_empty + 8 * stage);
-        if (++stage == kStages) {
+        if (++stage == static_cast<uint32_t>(stages)) {
           stage = 0;
           phase ^= 1u;
         }
       }
       if (ok) tc_commit(bar_tmem_full);
     }
-  } else if (has_work) {
-    // the accumulator is complete (and this CTA's operand ring idle) once the last commit arrives
-    ok = mbar_wait<false>(bar_tmem_full, 0u, abort_flag, p.status, kSiteEpiTmemFull);
-    tc_fence_after_sync();
+  } else {
+    // while the main loop runs: the W scales of this CTA's column slice go to shared memory, zero
+    // beyond N, so that the tail of the kernel waits on nothing but the accumulator
+    const int first = col_base + rank * slice_cols;
+    for (int c = static_cast<int>(threadIdx.x) - 64; c < slice_cols; c += Geo::kThreads - 64) {
+      st_shared_f32(smem_scales + c * 4, first + c < p.N ? __ldg(p.w_scale + first + c) : 0.0f);
+    }
+    if (has_work) {
+      // the accumulator is complete (and this CTA's operand ring idle) once the last commit arrives
+      ok = mbar_wait<false>(bar_tmem_full, 0u, abort_flag, p.status, kSiteEpiTmemFull);
+      tc_fence_after_sync();
+    }
+    named_barrier_sync(1, Geo::kThreads - 64);  // the four epilogue warps: the scales are in place
   }
   __syncwarp();
   // a CTA that gave up neither sends nor adds (its output is garbage and the status word says so)
   const bool cta_ok = __all_sync(0xffffffffu, *abort_flag == 0u) != 0;
 
-  // ---- (A) every CTA of the cluster has finished reading its operand ring ----
-  cluster_sync_all();
-
   const int quarter = warp & 3;
   const int tile_row = quarter * 32 + lane;  // row inside the 128-row tile = TMEM lane
-  if (warp >= 2 && cta_ok) {
-    // exchange: columns [j*slice_cols, (j+1)*slice_cols) of this CTA's partial go to CTA j
-    const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+  const int row0 = row_base + quarter * 32;
+  const int row = row0 + lane;
+  const bool warp_has_rows = row0 < p.M;  // warp-uniform: the whole 32-row group lies beyond M otherwise
+  const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+
+  if (split > 1) {
+    // ---- (A) every CTA of the cluster has finished reading its operand ring ----
+    cluster_sync_all();
+
+    if (warp >= 2 && cta_ok && warp_has_rows) {
+      // exchange: columns [j*slice_cols, (j+1)*slice_cols) of this CTA's partial go to CTA j
+      auto send = [&](auto cols_tag, int c0) {
+        constexpr int kCols = decltype(cols_tag)::value;
+        uint32_t acc[kCols];
+        if (has_work) {
+          tmem_ld_cols<kCols>(t_addr + c0, acc);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < kCols; ++j) acc[j] = 0u;  // K shorter than the split: an empty slice adds nothing
+        }
+        const int dest = c0 / slice_cols;  // kCols | slice_cols: one destination per chunk
+        const int c_in_slice = c0 - dest * slice_cols;
+        const uint32_t local = smem_a + exchange_offset(rank, slice_cols, c_in_slice, tile_row);
+        const uint32_t remote = mapa_cluster(local, static_cast<uint32_t>(dest));
+        if (row < p.M) {
+#pragma unroll
+          for (int j = 0; j < kCols / 4; ++j) {
+            st_cluster_v4(remote + j * Geo::kBlockM * 16, acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+          }
+        }
+      };
+      if (slice_cols >= 32) {
 #pragma unroll 1
-    for (int c0 = 0; c0 < Geo::kBlockN; c0 += 32) {
-      uint32_t acc[32];
-      if (has_work) {
-        tmem_ld_32x32(t_addr + c0, acc);
-        tmem_ld_wait();
+        for (int c0 = 0; c0 < kBlockN; c0 += 32) send(std::integral_constant<int, 32>{}, c0);
       } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = 0u;  // K shorter than the split: an empty slice adds nothing
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBlockN; c0 += 16) send(std::integral_constant<int, 16>{}, c0);
       }
-      const int dest = c0 / slice_cols;  // 32 | slice_cols: one destination per chunk
-      const int c_in_slice = c0 - dest * slice_cols;
-      const uint32_t local = smem_a + exchange_offset(rank, slice_cols, c_in_slice, tile_row);
-      const uint32_t remote = mapa_cluster(local, static_cast<uint32_t>(dest));
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        st_cluster_v4(remote + j * Geo::kBlockM * 16, acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
-      }
+      tc_fence_before_sync();
     }
-    tc_fence_before_sync();
+
+    // ---- (B) all partial sums have landed ----
+    cluster_sync_all();
   }
 
-  // ---- (B) all partial sums have landed ----
-  cluster_sync_all();
-
-  if (warp >= 2 && cta_ok) {
-    const int row0 = row_base + quarter * 32;
-    const int row = row0 + lane;
-    const float xs = row < p.M ? __ldg(p.x_scale + row) : 0.0f;
+  if (warp >= 2 && cta_ok && warp_has_rows) {
+    const int col_first = col_base + rank * slice_cols;
+    Finish f;
+    f.y_row = reinterpret_cast<uint16_t*>(p.y) + static_cast<long long>(row) * p.ldy + col_first;
+    f.scales = smem_scales;
+    f.exchange_base = smem_a;
+    f.t_addr = t_addr + rank * slice_cols;
+    f.split = split;
+    f.slice_cols = slice_cols;
+    f.tile_row = tile_row;
+    f.lane = lane;
+    f.cols_valid = p.N - col_first < slice_cols ? p.N - col_first : slice_cols;
+    f.xs = row < p.M ? __ldg(p.x_scale + row) : 0.0f;
+    f.row_valid = row < p.M;
+    f.bias = p.bias != nullptr ? p.bias + col_first : nullptr;
+    f.out_fp16 = p.out_fp16 != 0;
+    f.boxed = p.use_tma_store != 0 && slice_cols % Geo::kStoreCols == 0;
+    f.vector_ok = p.use_tma_store != 0;  // same condition: 16-byte aligned rows of Y
     const uint32_t stage_buf = smem_epi + quarter * (2 * Geo::kStoreRows * Geo::kStoreCols * 2);
-    uint32_t store_count = 0;
+    const bool use_tma = f.boxed;
+
+    if (slice_cols >= 32) {
+      uint32_t store_count = 0;
 #pragma unroll 1
-    for (int box = 0; box < slice_cols / Geo::kStoreCols; ++box) {
-      const int box_col = col_base + rank * slice_cols + box * Geo::kStoreCols;
-      const uint32_t sbuf = stage_buf + (store_count & 1u) * (Geo::kStoreRows * Geo::kStoreCols * 2);
-      if (p.use_tma_store) {
-        if (lane == 0) tma_store_wait_read<1>();
-        __syncwarp();
-      }
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int c_in_slice = box * Geo::kStoreCols + half * 32;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = 0.0f;
-        for (int sender = 0; sender < split; ++sender) {  // CTA order: the sum does not depend on timing
-          const uint32_t src = smem_a + exchange_offset(sender, slice_cols, c_in_slice, tile_row);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 t = ld_shared_v4(src + j * Geo::kBlockM * 16);
-            v[4 * j + 0] += t.x;
-            v[4 * j + 1] += t.y;
-            v[4 * j + 2] += t.z;
-            v[4 * j + 3] += t.w;
-          }
+      for (int c = 0; c < slice_cols; c += 32) {
+        const uint32_t sbuf = stage_buf + (store_count & 1u) * (Geo::kStoreRows * Geo::kStoreCols * 2);
+        if (f.boxed && c % Geo::kStoreCols == 0) {
+          if (lane == 0) tma_store_wait_read<1>();  // the box used two stores ago has been read
+          __syncwarp();
         }
-        const int c_first = box_col + half * 32;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float ws = (c_first + j < p.N) ? __ldg(p.w_scale + c_first + j) : 0.0f;
-          v[j] *= xs * ws;
-          if (p.bias != nullptr && c_first + j < p.N) v[j] += __bfloat162float(p.bias[c_first + j]);
-        }
-        if (p.use_tma_store) {
-          const uint32_t row_addr = sbuf + lane * 128;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t chunk = static_cast<uint32_t>((half * 4 + j) ^ (lane & 7));
-            if (p.out_fp16) {
-              st_shared_v4(row_addr + chunk * 16, pack_f16x2(v[8 * j + 0], v[8 * j + 1]),
-                           pack_f16x2(v[8 * j + 2], v[8 * j + 3]), pack_f16x2(v[8 * j + 4], v[8 * j + 5]),
-                           pack_f16x2(v[8 * j + 6], v[8 * j + 7]));
-            } else {
-              st_shared_v4(row_addr + chunk * 16, pack_bf16x2(v[8 * j + 0], v[8 * j + 1]),
-                           pack_bf16x2(v[8 * j + 2], v[8 * j + 3]), pack_bf16x2(v[8 * j + 4], v[8 * j + 5]),
-                           pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
-            }
-          }
-        } else if (row < p.M) {
-          uint16_t* dst = reinterpret_cast<uint16_t*>(p.y) + static_cast<long long>(row) * p.ldy + c_first;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (c_first + j < p.N) dst[j] = to_out16(v[j], p.out_fp16);
-          }
+        finish_columns<32>(f, c, sbuf);
+        if (f.boxed && c % Geo::kStoreCols == Geo::kStoreCols - 32) {
+          const int box_col = col_first + c - (Geo::kStoreCols - 32);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && box_col < p.N) tma_store_2d(&tm_y, sbuf, box_col, row0);
+          if (lane == 0) tma_store_commit();
+          ++store_count;
         }
       }
-      if (p.use_tma_store) {
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0 && row0 < p.M && box_col < p.N) tma_store_2d(&tm_y, sbuf, box_col, row0);
-        if (lane == 0) tma_store_commit();
-        ++store_count;
-      }
+      if (use_tma && lane == 0) tma_store_wait_all();
+    } else {
+      finish_columns<16>(f, 0, 0u);
     }
-    if (p.use_tma_store && lane == 0) tma_store_wait_all();
   }
 
   __syncwarp();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc<1>(tmem_base, 256);
+  if (warp == 1) tmem_dealloc<1>(tmem_base, kBlockN);
+}
+
+template <int kBlockN>
+cudaError_t configure(int dev) {
+  static bool configured[64] = {};
+  if (dev >= 0 && dev < 64 && configured[dev]) return cudaSuccess;
+  const cudaError_t err = cudaFuncSetAttribute(gemm_splitk_kernel<kBlockN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               Cfg<kBlockN>::kSmemBytes);
+  if (err == cudaSuccess && dev >= 0 && dev < 64) configured[dev] = true;
+  return err;
+}
+
+template <int kBlockN>
+cudaError_t launch_one(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y, const TcParams& p,
+                       int tiles, int split, bool overlap, int rows_a, int stages, cudaStream_t stream) {
+  using C = Cfg<kBlockN>;
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  err = configure<kBlockN>(dev);
+  if (err != cudaSuccess) return err;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * split), 1, 1);
+  cfg.blockDim = dim3(Geo::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned num_attrs = 0;
+  if (split > 1) {
+    attr[num_attrs].id = cudaLaunchAttributeClusterDimension;
+    attr[num_attrs].val.clusterDim.x = static_cast<unsigned>(split);
+    attr[num_attrs].val.clusterDim.y = 1;
+    attr[num_attrs].val.clusterDim.z = 1;
+    ++num_attrs;
+  }
+  if (overlap) {
+    attr[num_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[num_attrs].val.programmaticStreamSerializationAllowed = 1;
+    ++num_attrs;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = num_attrs;
+  return cudaLaunchKernelEx(&cfg, gemm_splitk_kernel<kBlockN>, tm_x, tm_w, tm_y, p, split, overlap ? 1 : 0, rows_a,
+                            stages);
 }
 
 }  // namespace
 
-cudaError_t launch_gemm_splitk(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
-                               const TcParams& p, int tiles, int split, cudaStream_t stream) {
-  constexpr int kSmemBytes = kRingBytes + kEpiBytes + kBarBytes + 1024;
-  static bool configured[64] = {};
+int splitk_resident_clusters(int split, cudaError_t* err) {
   int dev = 0;
-  cudaError_t err = cudaGetDevice(&dev);
-  if (err != cudaSuccess) return err;
-  if (dev < 64 && !configured[dev]) {
-    err = cudaFuncSetAttribute(gemm_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (err != cudaSuccess) return err;
-    configured[dev] = true;
-  }
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess) return 0;
+  *err = configure<128>(dev);  // the three widths use the same shared memory, one CTA per SM
+  if (*err != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(tiles * split), 1, 1);
+  cfg.gridDim = dim3(static_cast<unsigned>(split * 64), 1, 1);
   cfg.blockDim = dim3(Geo::kThreads, 1, 1);
-  cfg.dynamicSmemBytes = kSmemBytes;
-  cfg.stream = stream;
+  cfg.dynamicSmemBytes = Cfg<128>::kSmemBytes;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = static_cast<unsigned>(split);
@@ -304,7 +477,25 @@ cudaError_t launch_gemm_splitk(const CUtensorMap& tm_x, const CUtensorMap& tm_w,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gemm_splitk_kernel, tm_x, tm_w, tm_y, p, split);
+  int clusters = 0;
+  *err = cudaOccupancyMaxActiveClusters(&clusters, gemm_splitk_kernel<128>, &cfg);
+  return *err == cudaSuccess ? clusters : 0;
+}
+
+cudaError_t launch_gemm_splitk(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
+                               const TcParams& p, const SplitPlan& plan, cudaStream_t stream) {
+  switch (plan.block_n) {
+    case 64:
+      return launch_one<64>(tm_x, tm_w, tm_y, p, plan.tiles, plan.split, plan.overlap_previous_kernel, plan.rows_a,
+                             plan.stages, stream);
+    case 128:
+      return launch_one<128>(tm_x, tm_w, tm_y, p, plan.tiles, plan.split, plan.overlap_previous_kernel, plan.rows_a,
+                             plan.stages, stream);
+    case 256:
+      return launch_one<256>(tm_x, tm_w, tm_y, p, plan.tiles, plan.split, plan.overlap_previous_kernel, plan.rows_a,
+                             plan.stages, stream);
+    default: return cudaErrorInvalidValue;
+  }
 }
 
 }  // namespace b200fp8

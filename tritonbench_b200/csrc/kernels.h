@@ -54,9 +54,30 @@ template <int kCtaGroup>
 cudaError_t launch_gemm_tc(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
                            const TcParams& p, int num_ctas, cudaStream_t stream);
 
-// split-K inside a cluster of `split` CTAs per 128x256 tile, reduced over distributed shared memory (gemm_splitk.cu)
+// One 128 x block_n tile per cluster of `split` CTAs, K split over the cluster and reduced over distributed
+// shared memory (gemm_splitk.cu).  block_n is 64, 128 or 256; split is 1, 2, 4 or 8 with block_n / split >= 16.
+struct SplitGeometry {
+  static constexpr int kRingBytes = 192 * 1024;
+  static constexpr int kMaxStages = 14;
+};
+struct SplitPlan {
+  int block_n;
+  int split;
+  int rows_a;                    // rows of X per stage: M rounded up to 8, at most 128
+  int stages;                    // operand stages in the 192 KiB ring
+  int tiles;                     // clusters
+  int waves;                     // tiles / clusters resident at once, rounded up
+  bool overlap_previous_kernel;  // programmatic stream serialization: W is prefetched under the previous kernel
+};
+// resident_clusters[i]: clusters of 2^i CTAs of this kernel the device runs at once (i = 0..3)
+SplitPlan make_split_plan(long long M, long long N, long long K, const int* resident_clusters, int forced_block_n,
+                          int forced_split);
+double split_plan_cost_us(long long M, long long N, long long K, int block_n, int split, int resident_clusters);
+// Clusters of `split` CTAs the current device can run at once (a cluster must fit inside one GPC, so this
+// is less than SMs / split); 0 with the error left in *err when the query fails.
+int splitk_resident_clusters(int split, cudaError_t* err);
 cudaError_t launch_gemm_splitk(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
-                               const TcParams& p, int tiles, int split, cudaStream_t stream);
+                               const TcParams& p, const SplitPlan& plan, cudaStream_t stream);
 
 // ------------------------ 128x128 block-scaled GEMM (gemm_blockwise.cu) ------------------------
 struct BlockwiseParams {

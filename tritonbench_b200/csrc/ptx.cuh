@@ -309,6 +309,15 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
       : "memory");
 }
 
+__device__ __forceinline__ void st_shared_f32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+// Barrier among `threads` threads (a multiple of 32) of the CTA, on hardware barrier `id` (1..15; 0 is __syncthreads).
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // Wait for the TMEM loads in flight and tie the wait to the 32 registers one of them wrote: code that
 // reads `r` cannot be scheduled above the wait, although the load that wrote `r` was issued earlier.
 __device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {

@@ -28,6 +28,13 @@ VARIANT_TC_SPLITK = 5
 FLAG_NO_TMA_STORE = 0x10
 FLAG_PDL = 0x20
 FLAG_OUT_FP16 = 0x40
+
+
+def flag_splitk_config(block_n: int, split: int) -> int:
+    """B200FP8_FLAG_SPLITK_CONFIG(block_n, split): force the tc_splitk tile width and cluster size (0 = library's choice)."""
+    return ((block_n // 64) << 8) | (split << 12)
+
+
 DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2
 QUANT_OPERATOR, QUANT_FP32 = 0, 1
 VARIANTS = {

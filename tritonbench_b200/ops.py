@@ -40,10 +40,13 @@ def workspace_bytes(m: int, n: int, k: int, flags: int = 0) -> int:
     return nbytes
 
 
-def _flags(variant: str, tma_store: bool, overlap: bool = False) -> int:
+def _flags(variant: str, tma_store: bool, overlap: bool = False, split_config: Optional[Tuple[int, int]] = None) -> int:
     if variant not in _lib.VARIANTS:
         raise ValueError(f"unknown variant {variant!r}; one of {sorted(_lib.VARIANTS)}")
-    return _lib.VARIANTS[variant] | (0 if tma_store else _lib.FLAG_NO_TMA_STORE) | (_lib.FLAG_PDL if overlap else 0)
+    flags = _lib.VARIANTS[variant] | (0 if tma_store else _lib.FLAG_NO_TMA_STORE) | (_lib.FLAG_PDL if overlap else 0)
+    if split_config is not None:
+        flags |= _lib.flag_splitk_config(*split_config)
+    return flags
 
 
 def fp8_gemm_rowwise(
@@ -58,12 +61,14 @@ def fp8_gemm_rowwise(
     workspace: Optional[torch.Tensor] = None,
     overlap: bool = False,
     out_dtype: torch.dtype = torch.bfloat16,
+    split_config: Optional[Tuple[int, int]] = None,
 ) -> torch.Tensor:
     """Y = bf16((xq @ wq.T) * x_scale[:, None] * w_scale[None, :] (+ bias)), fp32 accumulation.
     out_dtype=torch.float16 rounds the result to IEEE fp16 instead of bf16.
 
     overlap=True (decode shapes): the kernel may start before the previous kernel on the stream has
     finished and reads wq - nothing else - that early; pass it only when nothing in flight writes wq.
+    split_config=(block_n, split) forces the tile width and cluster size of the tc_splitk kernel.
 
     xq [M, K] and wq [N, K] are float8_e4m3fn (or uint8 holding e4m3 bytes) with K contiguous;
     x_scale [M], w_scale [N] float32; bias [N] bfloat16 or None.  Asynchronous on the current stream.
@@ -96,7 +101,7 @@ def fp8_gemm_rowwise(
     elif out.dtype != out_dtype or tuple(out.shape) != (m, n) or out.stride(1) != 1:
         raise ValueError(f"out must be {out_dtype} [M, N] with N contiguous")
 
-    flags = _flags(variant, tma_store, overlap) | (_lib.FLAG_OUT_FP16 if out_dtype == torch.float16 else 0)
+    flags = _flags(variant, tma_store, overlap, split_config) | (_lib.FLAG_OUT_FP16 if out_dtype == torch.float16 else 0)
     lib = _lib.load()
     if workspace is None:
         workspace = get_workspace(xq.device, workspace_bytes(m, n, k, flags))
@@ -217,7 +222,8 @@ def fp8_gemm(a: torch.Tensor, b: torch.Tensor, scale_a=None, scale_b=None, out_d
 
 
 def make_gemm_fn(xq, wq, x_scale, w_scale, bias=None, variant: str = "auto", reuse_out: bool = False,
-                 overlap: bool = False, out_dtype: torch.dtype = torch.bfloat16) -> Callable:
+                 overlap: bool = False, out_dtype: torch.dtype = torch.bfloat16,
+                 split_config: Optional[Tuple[int, int]] = None) -> Callable:
     """Zero-argument closure in the shape the TritonBench harness wants from a backend
     (triton_op.py:765-785).  The workspace is allocated here, outside any timed or captured
     region; each call of the closure only enqueues the kernel."""
@@ -229,7 +235,7 @@ def make_gemm_fn(xq, wq, x_scale, w_scale, bias=None, variant: str = "auto", reu
 
     def fn():
         return fp8_gemm_rowwise(xq, wq, x_scale, w_scale, bias, out=out, variant=variant, workspace=ws, overlap=overlap,
-                                out_dtype=out_dtype)
+                                out_dtype=out_dtype, split_config=split_config)
 
     return fn
 
