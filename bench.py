@@ -50,7 +50,7 @@ WORKLOADS = {
 # summarised under profiles/; None where no capture of that workload exists
 NCU_TRAFFIC_BYTES = {
     "square_8192": 462.2e6,
-    "decode_m16": 243.3e6,
+    "decode_m16": 241.3e6,
 }
 
 

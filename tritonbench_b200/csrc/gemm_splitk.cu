@@ -401,7 +401,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           ++store_count;
         }
       }
-      if (use_tma && lane == 0) tma_store_wait_all();
+      // the CTA may end once the boxes have been read out of shared memory; the writes complete with the kernel
+      if (use_tma && lane == 0) tma_store_wait_read<0>();
     } else {
       finish_columns<16>(f, 0, 0u);
     }

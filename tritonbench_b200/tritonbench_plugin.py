@@ -6,7 +6,10 @@
 is `python run.py --op fp8_gemm_rowwise ...` with three more columns in the result table:
 
     b200               this library (b200fp8_gemm_rowwise through ctypes), CUDA devices only
-    torch_dequant_ref  (xq.float() * x_scale[:, None]) @ (wq.float() * w_scale[:, None]).T in fp32 -> bf16,
+    torch_dequant_ref  (xq.float() @ wq.float().T) * x_scale[:, None] * w_scale[None, :] in fp32 -> bf16 (the
+                       products of e4m3 values are exact in fp32, so only the order of the fp32 additions
+                       differs from a tensor-core kernel's; scaling the operands first instead rounds every
+                       product and fails the harness's tolerance on one element in 10^8 at K = 13312),
                        registered as the BASELINE so that `speedup` and `accuracy` have a reference column
                        on machines where every stock backend is disabled (all of them are on a B200:
                        tritonbench/operators/fp8_gemm_rowwise/operator.py:88-91,101-102)
@@ -79,7 +82,7 @@ def b200_native(self, xq, wq, x_scale, w_scale, bias) -> Callable:
 
 def torch_dequant_ref(self, xq, wq, x_scale, w_scale, bias) -> Callable:
     def fn():
-        y = (xq.to(torch.float32) * x_scale[:, None]) @ (wq.to(torch.float32) * w_scale[:, None]).T
+        y = (xq.to(torch.float32) @ wq.to(torch.float32).T) * (x_scale[:, None] * w_scale[None, :])
         if bias is not None:
             y = y + bias.to(torch.float32)
         return y.to(torch.bfloat16)
