@@ -95,7 +95,8 @@ def test_cluster_split_k_kernel(cuda_device, shape):
                   orc.gemm_rowwise(xq, wq, xs, ws, out_dtype=torch.float16), "tc_splitk fp16")
 
 
-SPLIT_CONFIGS = [(256, 1), (256, 2), (256, 4), (256, 8), (128, 1), (128, 2), (128, 4), (128, 8), (64, 1), (64, 2), (64, 4)]
+SPLIT_CONFIGS = [(256, 1), (256, 2), (256, 4), (256, 8), (128, 1), (128, 2), (128, 4), (128, 8), (64, 1), (64, 2), (64, 4),
+                 (208, 1), (16, 1), (48, 1), (96, 2), (192, 4), (160, 2)]
 
 
 @pytest.mark.parametrize("config", SPLIT_CONFIGS)
@@ -115,7 +116,7 @@ def test_every_tile_width_and_cluster_size_of_the_one_tile_per_cluster_kernel(cu
 def test_split_config_flag_rejects_impossible_combinations(cuda_device):
     ops = _ops()
     xq, wq, xs, ws = _gpu(*_inputs(16, 256, 512))
-    for bad in [(64, 8), (192, 1), (128, 3)]:
+    for bad in [(64, 8), (128, 3), (272, 1), (48, 2)]:  # 64 / 8 < 16; 3 CTAs; wider than 256; 48 is not a multiple of 32
         with pytest.raises(Exception):
             ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="tc_splitk", split_config=bad)
     ops.check_device_status()

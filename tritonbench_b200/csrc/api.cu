@@ -110,15 +110,15 @@ bool tma_loadable(int64_t K, int64_t ldx, int64_t ldw, const void* xq, const voi
 namespace b200fp8 {
 
 // Cost model of the one-tile-per-cluster kernel, in microseconds, fitted to graph-replay timings of every
-// (block_n, split) on 45 shapes (mean regret of the model's pick against the best measured: 6 %).
+// (block_n, split) on 45 shapes (mean regret of the model's pick against the best measured: 2 %, worst 14 %).
 // A CTA's main loop is the slowest of: its bytes at the rate its ring sustains (bytes in flight / latency),
 // its MMAs, and the whole wave's bytes at chip bandwidth (L2 for re-read operands, HBM for the unique bytes).
 // Then the DSMEM exchange and the epilogue; all of it once per wave of resident clusters.
 double split_plan_cost_us(long long M, long long N, long long K, int block_n, int split, int resident_clusters) {
-  const double kLaunch = 2.0, kLatency = 1.7, kRingLatency = 1.31, kMmaPerColumn = 1.28e-3;
-  const double kL2BytesPerUs = 11.4e6, kHbmBytesPerUs = 6.0e6, kL2ResidentBytes = 120.0e6;
+  const double kLaunch = 1.0, kLatency = 2.17, kRingLatency = 0.81, kMmaPerColumn = 0.9e-3, kPerKBlock = 0.151;
+  const double kL2BytesPerUs = 13.5e6, kHbmBytesPerUs = 6.0e6, kL2ResidentBytes = 120.0e6;
   const double kHbmBytesPerUsPerSm = 0.058e6;
-  const double kExchangeFixed = 0.21, kExchangePerByte = 32.2e-6, kEpilogue = 1.2;
+  const double kExchangeFixed = 0.93, kExchangePerByte = 41.5e-6, kEpilogue = 0.11;
   const long long tiles = ((M + 127) / 128) * ((N + block_n - 1) / block_n);
   const long long kb = (K + TcGeometry::kBlockK - 1) / TcGeometry::kBlockK;
   const long long kb_per = (kb + split - 1) / split;
@@ -129,15 +129,17 @@ double split_plan_cost_us(long long M, long long N, long long K, int block_n, in
   if (stages > SplitGeometry::kMaxStages) stages = SplitGeometry::kMaxStages;
   if (stages > kb_per) stages = kb_per;
   const double cta_bytes = static_cast<double>(kb_per) * stage_bytes;
-  const double ring = kLatency + cta_bytes / (static_cast<double>(stages) * stage_bytes / kRingLatency);
-  const double mma = kLatency + static_cast<double>(kb_per * block_n) * kMmaPerColumn;
+  const double per_kb = kPerKBlock * static_cast<double>(kb_per);  // issue and hand-over cost of a k-block
+  const double ring = kLatency + per_kb + cta_bytes / (static_cast<double>(stages) * stage_bytes / kRingLatency);
+  const double mma = kLatency + per_kb + static_cast<double>(kb_per * block_n) * kMmaPerColumn;
   const long long concurrent = (tiles < resident_clusters ? tiles : resident_clusters) * split;
   const double unique_bytes = static_cast<double>(M + N) * static_cast<double>(K);
   double chip = static_cast<double>(concurrent) * cta_bytes / kL2BytesPerUs;
   // operands beyond what L2 can hold between calls come from HBM whatever the access pattern
   // one SM draws about 58 GB/s from HBM with 32 KiB boxes of W however deep its ring (46 with 16 KiB
   // boxes, 29 with 8 KiB): few CTAs cannot saturate the memory
-  const double box_factor = block_n == 256 ? 1.0 : (block_n == 128 ? 0.8 : 0.5);
+  const double box_factor = block_n >= 128 ? 0.8 + 0.2 * (block_n - 128) / 128.0
+                                           : (block_n >= 64 ? 0.5 + 0.3 * (block_n - 64) / 64.0 : 0.5 * block_n / 64.0);
   double hbm_rate = static_cast<double>(concurrent) * kHbmBytesPerUsPerSm * box_factor;
   if (hbm_rate > kHbmBytesPerUs) hbm_rate = kHbmBytesPerUs;
   const double hbm = unique_bytes / static_cast<double>(waves) / hbm_rate;
@@ -152,32 +154,43 @@ double split_plan_cost_us(long long M, long long N, long long K, int block_n, in
   return kLaunch + static_cast<double>(waves) * (main_loop + exchange + kEpilogue);
 }
 
-// forced_block_n / forced_split: 0 = choose by the cost model
+// forced_block_n / forced_split: 0 = choose by the cost model.  Candidate widths: 256, 128, 64, and for
+// each cluster size the narrowest tile that still gives one wave (every SM, or as many as can hold a
+// cluster, gets exactly one tile).
 SplitPlan make_split_plan(long long M, long long N, long long K, const int* resident_clusters, int forced_block_n,
                           int forced_split) {
   SplitPlan best = {256, 1, 128, 4, 0, 1, false};
   double best_cost = 1e30;
   const long long kb = (K + TcGeometry::kBlockK - 1) / TcGeometry::kBlockK;
-  for (int block_n = 256; block_n >= 64; block_n /= 2) {
-    if (forced_block_n != 0 && block_n != forced_block_n) continue;
-    for (int split = 1, log2_split = 0; split <= 8; split *= 2, ++log2_split) {
-      if (block_n / split < 16) break;
-      if (forced_split != 0 && split != forced_split) continue;
-      if (forced_split == 0 && split > 1 && kb / split < 2) break;
-      const double cost = split_plan_cost_us(M, N, K, block_n, split, resident_clusters[log2_split]);
+  const long long tiles_m = (M + 127) / 128;
+  for (int split = 1, log2_split = 0; split <= 8; split *= 2, ++log2_split) {
+    if (forced_split != 0 && split != forced_split) continue;
+    if (forced_split == 0 && split > 1 && kb / split < 2) break;
+    const int resident = resident_clusters[log2_split];
+    const int step = 16 * split;  // a CTA finishes block_n / split columns, a multiple of 16
+    int candidates[4] = {256, 128, 64, 0};
+    if (resident >= tiles_m) {
+      const long long tiles_n = resident / tiles_m;                  // tiles along N that fit in one wave
+      long long fit = ((N + tiles_n - 1) / tiles_n + step - 1) / step * step;  // narrowest width that needs no more
+      if (fit <= 256 && fit != 256 && fit != 128 && fit != 64) candidates[3] = static_cast<int>(fit);
+    }
+    for (int i = 0; i < 4; ++i) {
+      const int block_n = forced_block_n != 0 ? forced_block_n : candidates[i];
+      if (block_n == 0 || block_n % step != 0) continue;
+      const double cost = split_plan_cost_us(M, N, K, block_n, split, resident);
       if (cost < best_cost) {
         best_cost = cost;
         best.block_n = block_n;
         best.split = split;
-        best.waves = static_cast<int>((((M + 127) / 128) * ((N + block_n - 1) / block_n) + resident_clusters[log2_split] - 1) /
-                                      resident_clusters[log2_split]);
+        best.waves = static_cast<int>((tiles_m * ((N + block_n - 1) / block_n) + resident - 1) / resident);
       }
+      if (forced_block_n != 0) break;
     }
   }
   best.rows_a = M >= 128 ? 128 : static_cast<int>((M + 7) / 8 * 8);
   best.stages = SplitGeometry::kRingBytes / ((best.rows_a + best.block_n) * TcGeometry::kBlockK);
   if (best.stages > SplitGeometry::kMaxStages) best.stages = SplitGeometry::kMaxStages;
-  best.tiles = static_cast<int>(((M + 127) / 128) * ((N + best.block_n - 1) / best.block_n));
+  best.tiles = static_cast<int>(tiles_m * ((N + best.block_n - 1) / best.block_n));
   return best;
 }
 
@@ -227,11 +240,11 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
     const int64_t clusters = tiles < dev.max_pair_clusters ? tiles : dev.max_pair_clusters;
     pl.num_ctas = static_cast<int>(2 * clusters);
   } else if (v == B200FP8_VARIANT_TC_SPLITK) {
-    const int forced_block_n = static_cast<int>((flags >> 8) & 0xFu) * 64;
-    const int forced_split = static_cast<int>((flags >> 12) & 0xFu);
-    if ((forced_block_n != 0 && forced_block_n != 64 && forced_block_n != 128 && forced_block_n != 256) ||
+    const int forced_block_n = static_cast<int>((flags >> 8) & 0x1Fu) * 16;
+    const int forced_split = static_cast<int>((flags >> 13) & 0xFu);
+    if (forced_block_n > 256 ||
         (forced_split != 0 && forced_split != 1 && forced_split != 2 && forced_split != 4 && forced_split != 8) ||
-        (forced_block_n != 0 && forced_split != 0 && forced_block_n / forced_split < 16)) {
+        (forced_block_n != 0 && forced_block_n % (16 * (forced_split != 0 ? forced_split : 1)) != 0)) {
       return B200FP8_BAD_ARG;
     }
     pl.splitk = make_split_plan(M, N, K, dev.split_clusters, forced_block_n, forced_split);

@@ -2,7 +2,8 @@
 // persistent kernels: narrower tiles, and split-K inside a thread-block cluster, reduced over
 // distributed shared memory.
 //
-// A cluster of S CTAs (S = 1, 2, 4 or 8) owns one 128 x BN tile of Y (BN = 64, 128 or 256).  CTA r
+// A cluster of S CTAs (S = 1, 2, 4 or 8) owns one 128 x BN tile of Y (BN a multiple of 16 S, at most 256: the
+// host picks the width that gives every SM a tile where it can).  CTA r
 // multiplies the r-th slice of K with the usual pipeline (TMA -> 128B-swizzled ring -> tcgen05.mma ->
 // TMEM); the ring is deep enough that a short slice is requested from memory all at once.  Then, S > 1:
 //   (A) cluster barrier: every CTA's MMAs have finished, so every operand ring is free;
@@ -32,15 +33,13 @@ namespace {
 using Geo = TcGeometry;
 
 // The operand ring is 192 KiB whatever the tile: a stage is `rows_a` rows of X (M rounded up to 8, at most
-// 128; the MMA reads 128 rows, the rows never loaded only feed output rows that do not exist) and kBlockN
+// 128; the MMA reads 128 rows, the rows never loaded only feed output rows that do not exist) and block_n
 // rows of W, and as many stages as fit are kept in flight - for a decode-sized M almost all of them W.
-template <int kBlockN>
-struct Cfg {
-  static constexpr int kBytesB = kBlockN * Geo::kBlockK;       // 8 / 16 / 32 KiB
-  static constexpr int kRingBytes = 192 * 1024;                // reused for the exchange
-  static constexpr int kExchangeBytes = Geo::kBlockM * kBlockN * 4; // fp32 partials a CTA receives
+struct C {
+  static constexpr int kRingBytes = SplitGeometry::kRingBytes;  // reused for the exchange
+  static constexpr int kExchangeBytes = Geo::kBlockM * 256 * 4;  // fp32 partials a CTA receives, widest tile
   static constexpr int kEpiBytes = 4 * 2 * Geo::kStoreRows * Geo::kStoreCols * 2;
-  static constexpr int kScaleBytes = kBlockN * 4;  // w_scale of the CTA's column slice
+  static constexpr int kScaleBytes = 256 * 4;  // w_scale of the CTA's column slice
   static constexpr int kBarBytes = 256;
   static constexpr int kSmemBytes = kRingBytes + kEpiBytes + kScaleBytes + kBarBytes + 1024;
   static_assert(kExchangeBytes <= kRingBytes, "the exchange buffer lives in the operand ring");
@@ -167,15 +166,18 @@ __device__ __forceinline__ void finish_columns(const Finish& f, int c_in_slice, 
   }
 }
 
-template <int kBlockN>
 __global__ void __launch_bounds__(Geo::kThreads, 1)
 gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                   const __grid_constant__ CUtensorMap tm_y, const TcParams p, const int split, const int overlap,
-                   const int rows_a, const int stages) {
-  using C = Cfg<kBlockN>;
+                   const __grid_constant__ CUtensorMap tm_y, const TcParams p, const SplitPlan plan) {
   constexpr int kMaxStages = SplitGeometry::kMaxStages;
-  const int bytes_a = rows_a * Geo::kBlockK;  // a multiple of 1024: whole 8-row swizzle atoms
-  const uint32_t stage_tx = static_cast<uint32_t>(bytes_a + C::kBytesB);
+  const int split = plan.split;
+  const int stages = plan.stages;
+  const int block_n = plan.block_n;
+  const bool overlap = plan.overlap_previous_kernel;
+  const int bytes_a = plan.rows_a * Geo::kBlockK;  // multiples of 1024: whole 8-row swizzle atoms
+  const int bytes_b = block_n * Geo::kBlockK;
+  const uint32_t stage_tx = static_cast<uint32_t>(bytes_a + bytes_b);
+  const uint32_t tmem_cols = block_n <= 32 ? 32u : (block_n <= 64 ? 64u : (block_n <= 128 ? 128u : 256u));
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -202,7 +204,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const int m_tile = tile % tiles_m;
   const int n_tile = tile / tiles_m;
   const int row_base = m_tile * Geo::kBlockM;
-  const int col_base = n_tile * kBlockN;
+  const int col_base = n_tile * block_n;
 
   const int num_kb = (p.K + Geo::kBlockK - 1) / Geo::kBlockK;
   const int kb_per = (num_kb + split - 1) / split;
@@ -217,7 +219,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const int j = i + kb_rot;
     return kb0 + (j >= kb_len ? j - kb_len : j);
   };
-  const int slice_cols = kBlockN / split;  // columns of the tile this CTA finishes (16, 32 or a multiple of 64)
+  const int slice_cols = block_n / split;  // columns of the tile this CTA finishes: a multiple of 16
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -235,7 +237,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     for (int i = 0; i < kb_len && i < stages; ++i) {
       const uint32_t full = bar_full + 8 * i;
       mbar_arrive_expect_tx(full, stage_tx);
-      tma_load_2d(smem_b + i * C::kBytesB, &tm_w, full, kb_at(i) * Geo::kBlockK, col_base);
+      tma_load_2d(smem_b + i * bytes_b, &tm_w, full, kb_at(i) * Geo::kBlockK, col_base);
     }
     if (overlap) griddep_wait();
     for (int i = 0; i < kb_len && i < stages; ++i) {
@@ -243,7 +245,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
   }
   if (warp == 1) {
-    tmem_alloc<1>(tmem_slot, kBlockN);
+    tmem_alloc<1>(tmem_slot, tmem_cols);
     tmem_relinquish<1>();
   }
   tc_fence_before_sync();
@@ -266,7 +268,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const uint32_t full = bar_full + 8 * stage;
         mbar_arrive_expect_tx(full, stage_tx);
         tma_load_2d(smem_a + stage * bytes_a, &tm_x, full, kb * Geo::kBlockK, row_base);
-        tma_load_2d(smem_b + stage * C::kBytesB, &tm_w, full, kb * Geo::kBlockK, col_base);
+        tma_load_2d(smem_b + stage * bytes_b, &tm_w, full, kb * Geo::kBlockK, col_base);
         if (++stage == static_cast<uint32_t>(stages)) {
           stage = 0;
           phase ^= 1u;
@@ -275,14 +277,14 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0 && has_work) {
-      constexpr uint32_t idesc = instr_desc_e4m3(Geo::kBlockM, kBlockN);
+      const uint32_t idesc = instr_desc_e4m3(Geo::kBlockM, static_cast<uint32_t>(block_n));
       uint32_t stage = 0, phase = 0;
       for (int i = 0; i < kb_len; ++i) {
         ok = mbar_wait<false>(bar_full + 8 * stage, phase, abort_flag, p.status, kSiteMmaFull);
         if (!ok) break;
         tc_fence_after_sync();
         const uint64_t a_desc = smem_desc_k_sw128(smem_a + stage * bytes_a);
-        const uint64_t b_desc = smem_desc_k_sw128(smem_b + stage * C::kBytesB);
+        const uint64_t b_desc = smem_desc_k_sw128(smem_b + stage * bytes_b);
 #pragma unroll
         for (int k = 0; k < Geo::kBlockK / 32; ++k) {
           tc_mma_f8<1>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
@@ -326,18 +328,16 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
     if (warp >= 2 && cta_ok && warp_has_rows) {
       // exchange: columns [j*slice_cols, (j+1)*slice_cols) of this CTA's partial go to CTA j
-      auto send = [&](auto cols_tag, int c0) {
+      auto send = [&](auto cols_tag, int dest, int c_in_slice) {
         constexpr int kCols = decltype(cols_tag)::value;
         uint32_t acc[kCols];
         if (has_work) {
-          tmem_ld_cols<kCols>(t_addr + c0, acc);
+          tmem_ld_cols<kCols>(t_addr + dest * slice_cols + c_in_slice, acc);
           tmem_ld_wait();
         } else {
 #pragma unroll
           for (int j = 0; j < kCols; ++j) acc[j] = 0u;  // K shorter than the split: an empty slice adds nothing
         }
-        const int dest = c0 / slice_cols;  // kCols | slice_cols: one destination per chunk
-        const int c_in_slice = c0 - dest * slice_cols;
         const uint32_t local = smem_a + exchange_offset(rank, slice_cols, c_in_slice, tile_row);
         const uint32_t remote = mapa_cluster(local, static_cast<uint32_t>(dest));
         if (row < p.M) {
@@ -347,12 +347,12 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           }
         }
       };
-      if (slice_cols >= 32) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < kBlockN; c0 += 32) send(std::integral_constant<int, 32>{}, c0);
-      } else {
+      for (int dest = 0; dest < split; ++dest) {  // 32 columns at a time, a last 16 where the slice ends on them
+        int c = 0;
 #pragma unroll 1
-        for (int c0 = 0; c0 < kBlockN; c0 += 16) send(std::integral_constant<int, 16>{}, c0);
+        for (; c + 32 <= slice_cols; c += 32) send(std::integral_constant<int, 32>{}, dest, c);
+        if (c < slice_cols) send(std::integral_constant<int, 16>{}, dest, c);
       }
       tc_fence_before_sync();
     }
@@ -382,10 +382,11 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const uint32_t stage_buf = smem_epi + quarter * (2 * Geo::kStoreRows * Geo::kStoreCols * 2);
     const bool use_tma = f.boxed;
 
-    if (slice_cols >= 32) {
+    {
       uint32_t store_count = 0;
+      int c = 0;
 #pragma unroll 1
-      for (int c = 0; c < slice_cols; c += 32) {
+      for (; c + 32 <= slice_cols; c += 32) {
         const uint32_t sbuf = stage_buf + (store_count & 1u) * (Geo::kStoreRows * Geo::kStoreCols * 2);
         if (f.boxed && c % Geo::kStoreCols == 0) {
           if (lane == 0) tma_store_wait_read<1>();  // the box used two stores ago has been read
@@ -401,10 +402,9 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           ++store_count;
         }
       }
+      if (c < slice_cols) finish_columns<16>(f, c, 0u);  // never boxed: a boxed slice is a multiple of 64 columns
       // the CTA may end once the boxes have been read out of shared memory; the writes complete with the kernel
       if (use_tma && lane == 0) tma_store_wait_read<0>();
-    } else {
-      finish_columns<16>(f, 0, 0u);
     }
   }
 
@@ -412,51 +412,16 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc<1>(tmem_base, kBlockN);
+  if (warp == 1) tmem_dealloc<1>(tmem_base, tmem_cols);
 }
 
-template <int kBlockN>
 cudaError_t configure(int dev) {
   static bool configured[64] = {};
   if (dev >= 0 && dev < 64 && configured[dev]) return cudaSuccess;
-  const cudaError_t err = cudaFuncSetAttribute(gemm_splitk_kernel<kBlockN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               Cfg<kBlockN>::kSmemBytes);
+  const cudaError_t err =
+      cudaFuncSetAttribute(gemm_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (err == cudaSuccess && dev >= 0 && dev < 64) configured[dev] = true;
   return err;
-}
-
-template <int kBlockN>
-cudaError_t launch_one(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y, const TcParams& p,
-                       int tiles, int split, bool overlap, int rows_a, int stages, cudaStream_t stream) {
-  using C = Cfg<kBlockN>;
-  int dev = 0;
-  cudaError_t err = cudaGetDevice(&dev);
-  if (err != cudaSuccess) return err;
-  err = configure<kBlockN>(dev);
-  if (err != cudaSuccess) return err;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(tiles * split), 1, 1);
-  cfg.blockDim = dim3(Geo::kThreads, 1, 1);
-  cfg.dynamicSmemBytes = C::kSmemBytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  unsigned num_attrs = 0;
-  if (split > 1) {
-    attr[num_attrs].id = cudaLaunchAttributeClusterDimension;
-    attr[num_attrs].val.clusterDim.x = static_cast<unsigned>(split);
-    attr[num_attrs].val.clusterDim.y = 1;
-    attr[num_attrs].val.clusterDim.z = 1;
-    ++num_attrs;
-  }
-  if (overlap) {
-    attr[num_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[num_attrs].val.programmaticStreamSerializationAllowed = 1;
-    ++num_attrs;
-  }
-  cfg.attrs = attr;
-  cfg.numAttrs = num_attrs;
-  return cudaLaunchKernelEx(&cfg, gemm_splitk_kernel<kBlockN>, tm_x, tm_w, tm_y, p, split, overlap ? 1 : 0, rows_a,
-                            stages);
 }
 
 }  // namespace
@@ -465,12 +430,12 @@ int splitk_resident_clusters(int split, cudaError_t* err) {
   int dev = 0;
   *err = cudaGetDevice(&dev);
   if (*err != cudaSuccess) return 0;
-  *err = configure<128>(dev);  // the three widths use the same shared memory, one CTA per SM
+  *err = configure(dev);
   if (*err != cudaSuccess) return 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(split * 64), 1, 1);
   cfg.blockDim = dim3(Geo::kThreads, 1, 1);
-  cfg.dynamicSmemBytes = Cfg<128>::kSmemBytes;
+  cfg.dynamicSmemBytes = C::kSmemBytes;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = static_cast<unsigned>(split);
@@ -479,24 +444,42 @@ int splitk_resident_clusters(int split, cudaError_t* err) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int clusters = 0;
-  *err = cudaOccupancyMaxActiveClusters(&clusters, gemm_splitk_kernel<128>, &cfg);
+  *err = cudaOccupancyMaxActiveClusters(&clusters, gemm_splitk_kernel, &cfg);
   return *err == cudaSuccess ? clusters : 0;
 }
 
 cudaError_t launch_gemm_splitk(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
                                const TcParams& p, const SplitPlan& plan, cudaStream_t stream) {
-  switch (plan.block_n) {
-    case 64:
-      return launch_one<64>(tm_x, tm_w, tm_y, p, plan.tiles, plan.split, plan.overlap_previous_kernel, plan.rows_a,
-                             plan.stages, stream);
-    case 128:
-      return launch_one<128>(tm_x, tm_w, tm_y, p, plan.tiles, plan.split, plan.overlap_previous_kernel, plan.rows_a,
-                             plan.stages, stream);
-    case 256:
-      return launch_one<256>(tm_x, tm_w, tm_y, p, plan.tiles, plan.split, plan.overlap_previous_kernel, plan.rows_a,
-                             plan.stages, stream);
-    default: return cudaErrorInvalidValue;
+  if (plan.block_n < 16 || plan.block_n > 256 || plan.split < 1 || plan.block_n % (16 * plan.split) != 0) {
+    return cudaErrorInvalidValue;
   }
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  err = configure(dev);
+  if (err != cudaSuccess) return err;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(plan.tiles * plan.split), 1, 1);
+  cfg.blockDim = dim3(Geo::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned num_attrs = 0;
+  if (plan.split > 1) {
+    attr[num_attrs].id = cudaLaunchAttributeClusterDimension;
+    attr[num_attrs].val.clusterDim.x = static_cast<unsigned>(plan.split);
+    attr[num_attrs].val.clusterDim.y = 1;
+    attr[num_attrs].val.clusterDim.z = 1;
+    ++num_attrs;
+  }
+  if (plan.overlap_previous_kernel) {
+    attr[num_attrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[num_attrs].val.programmaticStreamSerializationAllowed = 1;
+    ++num_attrs;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = num_attrs;
+  return cudaLaunchKernelEx(&cfg, gemm_splitk_kernel, tm_x, tm_w, tm_y, p, plan);
 }
 
 }  // namespace b200fp8

@@ -55,7 +55,7 @@ cudaError_t launch_gemm_tc(const CUtensorMap& tm_x, const CUtensorMap& tm_w, con
                            const TcParams& p, int num_ctas, cudaStream_t stream);
 
 // One 128 x block_n tile per cluster of `split` CTAs, K split over the cluster and reduced over distributed
-// shared memory (gemm_splitk.cu).  block_n is 64, 128 or 256; split is 1, 2, 4 or 8 with block_n / split >= 16.
+// shared memory (gemm_splitk.cu).  split is 1, 2, 4 or 8; block_n a multiple of 16 * split, at most 256.
 struct SplitGeometry {
   static constexpr int kRingBytes = 192 * 1024;
   static constexpr int kMaxStages = 14;

@@ -32,7 +32,7 @@ FLAG_OUT_FP16 = 0x40
 
 def flag_splitk_config(block_n: int, split: int) -> int:
     """B200FP8_FLAG_SPLITK_CONFIG(block_n, split): force the tc_splitk tile width and cluster size (0 = library's choice)."""
-    return ((block_n // 64) << 8) | (split << 12)
+    return ((block_n // 16) << 8) | (split << 13)
 
 
 DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2
