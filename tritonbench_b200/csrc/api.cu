@@ -159,7 +159,9 @@ double split_plan_cost_us(long long M, long long N, long long K, int block_n, in
 // cluster, gets exactly one tile).
 SplitPlan make_split_plan(long long M, long long N, long long K, const int* resident_clusters, int forced_block_n,
                           int forced_split) {
-  SplitPlan best = {256, 1, 128, 4, 0, 1, false};
+  SplitPlan best = {};
+  best.block_n = 256;
+  best.split = 1;
   double best_cost = 1e30;
   const long long kb = (K + TcGeometry::kBlockK - 1) / TcGeometry::kBlockK;
   const long long tiles_m = (M + 127) / 128;
@@ -188,8 +190,20 @@ SplitPlan make_split_plan(long long M, long long N, long long K, const int* resi
     }
   }
   best.rows_a = M >= 128 ? 128 : static_cast<int>((M + 7) / 8 * 8);
-  best.stages = SplitGeometry::kRingBytes / ((best.rows_a + best.block_n) * TcGeometry::kBlockK);
+  const int bytes_a = best.rows_a * TcGeometry::kBlockK, bytes_b = best.block_n * TcGeometry::kBlockK;
+  const long long kb_per = (kb + best.split - 1) / best.split;
+  best.stages = SplitGeometry::kRingBytes / (bytes_a + bytes_b);
   if (best.stages > SplitGeometry::kMaxStages) best.stages = SplitGeometry::kMaxStages;
+  if (best.stages > kb_per) best.stages = static_cast<int>(kb_per > 0 ? kb_per : 1);
+  // the ring: the stages; room for the MMA's 128-row read of the last X stage; the exchange buffer
+  int ring = best.stages * (bytes_a + bytes_b);
+  const int a_overread = best.stages * bytes_a + TcGeometry::kBlockM * TcGeometry::kBlockK;
+  if (ring < a_overread) ring = a_overread;
+  const int exchange = best.split > 1 ? best.block_n * best.rows_a * 4 : 0;
+  if (ring < exchange) ring = exchange;
+  best.ring_bytes = (ring + 1023) / 1024 * 1024;
+  best.staged_stores = M > 64 ? 1 : 0;  // short outputs leave in 16-byte stores straight from registers
+  best.smem_bytes = best.ring_bytes + (best.staged_stores ? 32 * 1024 : 0) + 1024 + 256 + 1024;
   best.tiles = static_cast<int>(tiles_m * ((N + best.block_n - 1) / best.block_n));
   return best;
 }

@@ -32,9 +32,11 @@ namespace {
 
 using Geo = TcGeometry;
 
-// The operand ring is 192 KiB whatever the tile: a stage is `rows_a` rows of X (M rounded up to 8, at most
-// 128; the MMA reads 128 rows, the rows never loaded only feed output rows that do not exist) and block_n
-// rows of W, and as many stages as fit are kept in flight - for a decode-sized M almost all of them W.
+// The operand ring holds at most 192 KiB: a stage is `rows_a` rows of X (M rounded up to 8, at most 128;
+// the MMA reads 128 rows, the rows never loaded only feed output rows that do not exist) and block_n rows
+// of W, and as many stages as fit (and as the CTA has k-blocks) are kept in flight - for a decode-sized M
+// almost all of them W.  A CTA with few k-blocks asks for a small ring, and two CTAs then fit on an SM:
+// with overlapped launches the next kernel's CTA loads its W while this one is still in its epilogue.
 struct C {
   static constexpr int kRingBytes = SplitGeometry::kRingBytes;  // reused for the exchange
   static constexpr int kExchangeBytes = Geo::kBlockM * 256 * 4;  // fp32 partials a CTA receives, widest tile
@@ -73,10 +75,11 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[kCols
   }
 }
 
-// Exchange buffer of a CTA: [sender][group of 4 columns of its slice][row][4 columns] fp32, so that a warp
-// (32 consecutive rows) moves 512 contiguous bytes per instruction.
-__device__ __forceinline__ uint32_t exchange_offset(int sender, int slice_cols, int col_in_slice, int row) {
-  return static_cast<uint32_t>((((sender * (slice_cols / 4) + col_in_slice / 4) * Geo::kBlockM) + row) * 16);
+// Exchange buffer of a CTA: [sender][group of 4 columns of its slice][row][4 columns] fp32 with `rows` rows
+// (the rows of the tile that exist, rounded up to 8), so that a warp (32 consecutive rows) moves 512
+// contiguous bytes per instruction.
+__device__ __forceinline__ uint32_t exchange_offset(int sender, int slice_cols, int col_in_slice, int row, int rows) {
+  return static_cast<uint32_t>((((sender * (slice_cols / 4) + col_in_slice / 4) * rows) + row) * 16);
 }
 
 // Everything one epilogue warp needs to finish columns of its 32 rows, by value: a pointer to the
@@ -88,6 +91,7 @@ struct Finish {
   uint32_t exchange_base;  // shared address of the exchange buffer (split > 1)
   uint32_t t_addr;         // TMEM address of this warp's lanes at the slice's first column (split == 1)
   int split, slice_cols, tile_row, lane;
+  int exchange_rows;       // rows per column group in the exchange buffer
   int cols_valid;          // columns of the slice that exist in Y
   float xs;
   bool row_valid;
@@ -111,10 +115,11 @@ __device__ __forceinline__ void finish_columns(const Finish& f, int c_in_slice, 
 #pragma unroll
     for (int j = 0; j < kCols; ++j) v[j] = 0.0f;
     for (int sender = 0; sender < f.split; ++sender) {  // CTA order: the sum does not depend on timing
-      const uint32_t src = f.exchange_base + exchange_offset(sender, f.slice_cols, c_in_slice, f.tile_row);
+      const uint32_t src =
+          f.exchange_base + exchange_offset(sender, f.slice_cols, c_in_slice, f.tile_row, f.exchange_rows);
 #pragma unroll
       for (int j = 0; j < kCols / 4; ++j) {
-        const float4 t = ld_shared_v4(src + j * Geo::kBlockM * 16);
+        const float4 t = ld_shared_v4(src + j * f.exchange_rows * 16);
         v[4 * j + 0] += t.x;
         v[4 * j + 1] += t.y;
         v[4 * j + 2] += t.z;
@@ -166,7 +171,7 @@ __device__ __forceinline__ void finish_columns(const Finish& f, int c_in_slice, 
   }
 }
 
-__global__ void __launch_bounds__(Geo::kThreads, 1)
+__global__ void __launch_bounds__(Geo::kThreads, 2)  // two CTAs of small problems share an SM
 gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    const __grid_constant__ CUtensorMap tm_y, const TcParams p, const SplitPlan plan) {
   constexpr int kMaxStages = SplitGeometry::kMaxStages;
@@ -185,8 +190,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
   const uint32_t smem_a = base;
   const uint32_t smem_b = smem_a + stages * bytes_a;  // the MMA's 128-row reads of a short X stage end in here
-  const uint32_t smem_epi = base + C::kRingBytes;
-  const uint32_t smem_scales = smem_epi + C::kEpiBytes;
+  const uint32_t smem_epi = base + plan.ring_bytes;
+  const uint32_t smem_scales = smem_epi + (plan.staged_stores ? C::kEpiBytes : 0);
   const uint32_t bars = smem_scales + C::kScaleBytes;
   const uint32_t bar_full = bars;                     // [stages]
   const uint32_t bar_empty = bars + 8 * kMaxStages;   // [stages]
@@ -231,7 +236,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     fence_mbar_init();
     prefetch_tensormap(&tm_x);
     prefetch_tensormap(&tm_w);
-    if (p.use_tma_store) prefetch_tensormap(&tm_y);
+    if (p.use_tma_store && plan.staged_stores) prefetch_tensormap(&tm_y);
     // the first pass over the ring needs no waiting: start it before the set-up barrier.  W (weights) may
     // be read while the previous kernel still runs; X only after it has completed.
     for (int i = 0; i < kb_len && i < stages; ++i) {
@@ -338,12 +343,12 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll
           for (int j = 0; j < kCols; ++j) acc[j] = 0u;  // K shorter than the split: an empty slice adds nothing
         }
-        const uint32_t local = smem_a + exchange_offset(rank, slice_cols, c_in_slice, tile_row);
+        const uint32_t local = smem_a + exchange_offset(rank, slice_cols, c_in_slice, tile_row, plan.rows_a);
         const uint32_t remote = mapa_cluster(local, static_cast<uint32_t>(dest));
         if (row < p.M) {
 #pragma unroll
           for (int j = 0; j < kCols / 4; ++j) {
-            st_cluster_v4(remote + j * Geo::kBlockM * 16, acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+            st_cluster_v4(remote + j * plan.rows_a * 16, acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
           }
         }
       };
@@ -372,12 +377,13 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     f.slice_cols = slice_cols;
     f.tile_row = tile_row;
     f.lane = lane;
+    f.exchange_rows = plan.rows_a;
     f.cols_valid = p.N - col_first < slice_cols ? p.N - col_first : slice_cols;
     f.xs = row < p.M ? __ldg(p.x_scale + row) : 0.0f;
     f.row_valid = row < p.M;
     f.bias = p.bias != nullptr ? p.bias + col_first : nullptr;
     f.out_fp16 = p.out_fp16 != 0;
-    f.boxed = p.use_tma_store != 0 && slice_cols % Geo::kStoreCols == 0;
+    f.boxed = p.use_tma_store != 0 && plan.staged_stores && slice_cols % Geo::kStoreCols == 0;
     f.vector_ok = p.use_tma_store != 0;  // same condition: 16-byte aligned rows of Y
     const uint32_t stage_buf = smem_epi + quarter * (2 * Geo::kStoreRows * Geo::kStoreCols * 2);
     const bool use_tma = f.boxed;
@@ -450,7 +456,8 @@ int splitk_resident_clusters(int split, cudaError_t* err) {
 
 cudaError_t launch_gemm_splitk(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
                                const TcParams& p, const SplitPlan& plan, cudaStream_t stream) {
-  if (plan.block_n < 16 || plan.block_n > 256 || plan.split < 1 || plan.block_n % (16 * plan.split) != 0) {
+  if (plan.block_n < 16 || plan.block_n > 256 || plan.split < 1 || plan.block_n % (16 * plan.split) != 0 ||
+      plan.smem_bytes > C::kSmemBytes) {
     return cudaErrorInvalidValue;
   }
   int dev = 0;
@@ -461,7 +468,7 @@ cudaError_t launch_gemm_splitk(const CUtensorMap& tm_x, const CUtensorMap& tm_w,
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(plan.tiles * plan.split), 1, 1);
   cfg.blockDim = dim3(Geo::kThreads, 1, 1);
-  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.dynamicSmemBytes = static_cast<size_t>(plan.smem_bytes);
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   unsigned num_attrs = 0;

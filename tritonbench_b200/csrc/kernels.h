@@ -64,7 +64,10 @@ struct SplitPlan {
   int block_n;
   int split;
   int rows_a;                    // rows of X per stage: M rounded up to 8, at most 128
-  int stages;                    // operand stages in the 192 KiB ring
+  int stages;                    // operand stages in the ring
+  int ring_bytes;                // ring (operands, then the split-K exchange), a multiple of 1024, at most 192 KiB
+  int staged_stores;             // 1: Y leaves through TMA boxes staged in shared memory (tall outputs)
+  int smem_bytes;                // dynamic shared memory of a CTA
   int tiles;                     // clusters
   int waves;                     // tiles / clusters resident at once, rounded up
   bool overlap_previous_kernel;  // programmatic stream serialization: W is prefetched under the previous kernel
