@@ -169,6 +169,25 @@ int b200fp8_row_quantize(const void* x, int x_dtype, int recipe, int64_t rows, i
                          int64_t ldq, float* scale, void* cuda_stream);
 
 /*
+ * Producer + rowwise quantiser in one pass: the activation that feeds the GEMM is computed from its bf16 inputs,
+ * quantised (scale = max(rowabsmax(y), 1e-12) / 448, q = e4m3(clamp(y * (1 / scale)))) and written as e4m3 bytes plus
+ * one fp32 scale per row, without the bf16 activation being stored.  fp32 arithmetic; the SiLU uses the hardware
+ * exponential and reciprocal (about 2 ulp).
+ *   B200FP8_PRODUCER_RMS_NORM  y[k] = x1[k] * rsqrt(mean_k(x1^2) + eps) * x2[k], x2 the weight vector [cols] (ld2 ignored)
+ *   B200FP8_PRODUCER_SILU_MUL  y[k] = x1[k] / (1 + exp(-x1[k])) * x2[k],         x2 [rows, cols] with row pitch ld2
+ *   round_bf16 != 0            y is rounded to bf16 before the quantisation (= producer kernel, then quantiser)
+ * Replaces: `rms_norm_fp8_rowwise_quant(x1, wd)` / `silu_mul_fp8_rowwise_quant(x1, x2)` and, with round_bf16,
+ * `rms_norm` / `silu_mul` followed by `quantize_fp8_row`
+ * (tritonbench/operators/fp8_fused_quant_gemm_rowwise/operator.py:86-131; those kernels are Meta-internal and absent
+ * from the reference tree, so eps and the fp32 arithmetic are this library's definition).
+ */
+#define B200FP8_PRODUCER_RMS_NORM 1
+#define B200FP8_PRODUCER_SILU_MUL 2
+int b200fp8_fused_row_quantize(int producer, const void* x1_bf16, const void* x2_bf16, int64_t rows, int64_t cols,
+                               int64_t ld1, int64_t ld2, float eps, int round_bf16, void* q, int64_t ldq, float* scale,
+                               void* cuda_stream);
+
+/*
  * Read the device status word of a workspace.  Call after the stream has been synchronised.
  * Returns B200FP8_OK or B200FP8_DEVICE_TIMEOUT; *device_status receives the raw word
  * (code << 24 | site).  Replaces: the reference's exit-on-error helper macros

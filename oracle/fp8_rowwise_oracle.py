@@ -83,6 +83,25 @@ def row_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return xq, scale
 
 
+def rms_norm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, round_bf16: bool = False) -> torch.Tensor:
+    """y = x * rsqrt(mean(x^2) + eps) * weight in fp32 on bf16 inputs: the producer of `rms_norm_fused` /
+    `rms_norm_quant` (tritonbench/operators/fp8_fused_quant_gemm_rowwise/operator.py:86-107).  The producer
+    kernels themselves are Meta-internal and absent from the reference tree: eps and the fp32 arithmetic are
+    this build's definition, and parity for them is unpinned."""
+    xf = x.to(torch.float32)
+    inv = 1.0 / torch.sqrt(xf.pow(2).mean(dim=1, keepdim=True) + eps)
+    y = (xf * inv) * weight.to(torch.float32)[None, :]
+    return y.to(torch.bfloat16).to(torch.float32) if round_bf16 else y
+
+
+def silu_mul_rows(x1: torch.Tensor, x2: torch.Tensor, round_bf16: bool = False) -> torch.Tensor:
+    """y = x1 / (1 + exp(-x1)) * x2 in fp32 on bf16 inputs (`silu_mul_fused` / `silu_mul_quant`,
+    tritonbench/operators/fp8_fused_quant_gemm_rowwise/operator.py:109-131); parity unpinned, as above."""
+    a = x1.to(torch.float32)
+    y = a / (1.0 + torch.exp(-a)) * x2.to(torch.float32)
+    return y.to(torch.bfloat16).to(torch.float32) if round_bf16 else y
+
+
 def gemm_rowwise(
     xq: torch.Tensor,
     wq: torch.Tensor,

@@ -88,3 +88,78 @@ def test_bad_arguments(cuda_device):
         ops.fp8_row_quantize(torch.zeros((4, 4), dtype=torch.bfloat16))
     with pytest.raises(Exception):
         ops.fp8_row_quantize(torch.zeros((4, 16), device="cuda", dtype=torch.bfloat16), recipe="fp32")
+
+
+# ------------------------------------------------------------------ producer + quantiser in one kernel
+def _check_fused(q, scale, y_ref):
+    """q, scale from the kernel against the oracle's fp32 activation y_ref: the scale is rowabsmax / 448 up to
+    the last bits of y, and every code is the oracle's code for y / scale or its neighbour (a last-bit
+    difference in y or in the scale may move a value across a rounding boundary)."""
+    from oracle import fp8_rowwise_oracle as orc
+
+    q_ref, s_ref = orc.row_quantize(y_ref)
+    scale = scale.cpu()
+    assert torch.allclose(scale, s_ref, rtol=2e-6, atol=0), (scale - s_ref).abs().max()
+    got = orc.decode_e4m3(q.cpu().view(torch.uint8))
+    want = orc.decode_e4m3(q_ref.view(torch.uint8))
+    differ = got != want
+    assert differ.float().mean().item() < 2e-3, differ.float().mean().item()
+    # a differing code is the neighbouring e4m3 value: at most one step of 2^-3 relative (or the subnormal step)
+    step = torch.maximum(want.abs() * 0.125, torch.full_like(want, 2.0 ** -9))
+    assert bool(((got - want).abs() <= step * 1.001).all())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(16, 8192), (128, 2304), (3, 1000), (5, 20000), (64, 4104), (7, 33)])
+@pytest.mark.parametrize("round_bf16", [False, True])
+def test_rms_norm_quantiser(cuda_device, shape, round_bf16):
+    from oracle import fp8_rowwise_oracle as orc
+    from tritonbench_b200 import ops
+
+    rows, cols = shape
+    gen = torch.Generator().manual_seed(rows + cols)
+    x = (torch.randn(rows, cols, generator=gen) * 3).to(torch.bfloat16)
+    w = torch.randn(cols, generator=gen).to(torch.bfloat16)
+    q, scale = ops.rms_norm_fp8_rowwise_quant(x.cuda(), w.cuda(), eps=1e-5, round_bf16=round_bf16)
+    _check_fused(q, scale, orc.rms_norm_rows(x, w, 1e-5, round_bf16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(16, 8192), (128, 2304), (3, 1000), (5, 20000), (64, 4104), (7, 33)])
+@pytest.mark.parametrize("round_bf16", [False, True])
+def test_silu_mul_quantiser(cuda_device, shape, round_bf16):
+    from oracle import fp8_rowwise_oracle as orc
+    from tritonbench_b200 import ops
+
+    rows, cols = shape
+    gen = torch.Generator().manual_seed(2 * rows + cols)
+    x1 = (torch.randn(rows, cols, generator=gen) * 4).to(torch.bfloat16)
+    x2 = torch.randn(rows, cols, generator=gen).to(torch.bfloat16)
+    q, scale = ops.silu_mul_fp8_rowwise_quant(x1.cuda(), x2.cuda(), round_bf16=round_bf16)
+    _check_fused(q, scale, orc.silu_mul_rows(x1, x2, round_bf16))
+
+
+@pytest.mark.gpu
+def test_fused_quantiser_feeds_the_gemm_and_handles_strided_and_zero_rows(cuda_device):
+    """End to end: rms_norm -> quantise -> GEMM against the oracle's fp32 pipeline; a row view with a
+    pitch larger than its width; an all-zero row (scale = 1e-12 / 448, codes 0)."""
+    from oracle import fp8_rowwise_oracle as orc
+    from tritonbench_b200 import ops, quantize
+
+    gen = torch.Generator().manual_seed(5)
+    m, n, k = 48, 512, 1024
+    big = (torch.randn(m, k + 64, generator=gen) * 2).to(torch.bfloat16)
+    big[3] = 0
+    x = big[:, :k]
+    wd = torch.randn(k, generator=gen).to(torch.bfloat16)
+    wq, ws = quantize.fp8_row_quantize_fp32(torch.randn(n, k, generator=gen))
+    xq, xs = ops.rms_norm_fp8_rowwise_quant(big.cuda()[:, :k], wd.cuda())
+    assert float(xs[3]) == pytest.approx(1e-12 / 448, rel=1e-6, abs=0)
+    assert int((xq[3].view(torch.uint8) & 0x7F).max()) == 0  # +0 or -0 (zero times a negative weight)
+    y = ops.fp8_gemm_rowwise(xq, wq.cuda(), xs, ws.cuda())
+    xq_ref, xs_ref = orc.row_quantize(orc.rms_norm_rows(x, wd))
+    ref = orc.gemm_rowwise(xq_ref, wq, xs_ref, ws)
+    # a handful of activation codes may differ by one step from the oracle's: compare with the e4m3 step in the budget
+    err = (y.cpu().float() - ref.float()).abs()
+    assert float(err.max()) <= float(orc.tolerance(ref.float()).max()) + 0.05 * float(ref.float().abs().max())
+    ops.check_device_status()

@@ -598,6 +598,33 @@ int b200fp8_row_quantize(const void* x, int x_dtype, int recipe, int64_t rows, i
   return note_cuda(launch_row_quantize(p, static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int b200fp8_fused_row_quantize(int producer, const void* x1, const void* x2, int64_t rows, int64_t cols, int64_t ld1,
+                               int64_t ld2, float eps, int round_bf16, void* q, int64_t ldq, float* scale,
+                               void* cuda_stream) {
+  if (x1 == nullptr || x2 == nullptr || q == nullptr || scale == nullptr) return B200FP8_BAD_ARG;
+  if (producer != kProducerRmsNorm && producer != kProducerSiluMul) return B200FP8_BAD_ARG;
+  if (rows <= 0 || cols <= 0 || ld1 < cols || ldq < cols) return B200FP8_BAD_ARG;
+  if (producer == kProducerSiluMul && ld2 < cols) return B200FP8_BAD_ARG;
+  if (producer == kProducerRmsNorm && !(eps >= 0.0f)) return B200FP8_BAD_ARG;
+  if (rows > 0x7FFFFFFFll || cols > 0x7FFFFF00ll) return B200FP8_TOO_LARGE;
+  FusedQuantParams p = {};
+  p.x1 = x1;
+  p.x2 = x2;
+  p.q = static_cast<uint8_t*>(q);
+  p.scale = scale;
+  p.rows = rows;
+  p.cols = static_cast<int>(cols);
+  p.ld1 = ld1;
+  p.ld2 = producer == kProducerSiluMul ? ld2 : 0;
+  p.ldq = ldq;
+  p.producer = producer;
+  p.round_bf16 = round_bf16 ? 1 : 0;
+  p.eps = eps;
+  p.vector_ok = aligned16(x1) && aligned16(x2) && (ld1 * 2) % 16 == 0 && (p.ld2 * 2) % 16 == 0 &&
+                (reinterpret_cast<uintptr_t>(q) & 7u) == 0 && ldq % 8 == 0;
+  return note_cuda(launch_fused_row_quantize(p, static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int b200fp8_selftest_wait_timeout(void* workspace, uint32_t limit_us, void* cuda_stream) {
   if (workspace == nullptr || limit_us == 0 || limit_us > 1000000u) return B200FP8_BAD_ARG;
   return note_cuda(launch_wait_timeout_selftest(static_cast<uint32_t*>(workspace),

@@ -200,4 +200,23 @@ struct QuantParams {
 
 cudaError_t launch_row_quantize(const QuantParams& p, cudaStream_t stream);
 
+// ------------------------ producer + quantiser in one pass (fused_quantize.cu) ------------------------
+constexpr int kProducerRmsNorm = 1;  // y = x1 * rsqrt(mean(x1^2) + eps) * x2[k]   (x2: weight vector [cols])
+constexpr int kProducerSiluMul = 2;  // y = silu(x1) * x2                          (x2: [rows, cols])
+struct FusedQuantParams {
+  const void* x1;  // bf16 [rows, cols]
+  const void* x2;  // bf16: weight [cols] or second operand [rows, cols]
+  uint8_t* q;
+  float* scale;
+  long long rows;
+  int cols;
+  long long ld1, ld2;  // elements
+  long long ldq;       // bytes
+  int producer;
+  int round_bf16;  // round y to bf16 before quantising (what a producer kernel followed by a quantiser computes)
+  float eps;       // RMS norm only
+  int vector_ok;   // rows of x1, x2 start on 16-byte boundaries, rows of q on 8-byte boundaries
+};
+cudaError_t launch_fused_row_quantize(const FusedQuantParams& p, cudaStream_t stream);
+
 }  // namespace b200fp8

@@ -37,6 +37,7 @@ def flag_splitk_config(block_n: int, split: int) -> int:
 
 DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2
 QUANT_OPERATOR, QUANT_FP32 = 0, 1
+PRODUCER_RMS_NORM, PRODUCER_SILU_MUL = 1, 2
 VARIANTS = {
     "auto": VARIANT_AUTO,
     "tc_1cta": VARIANT_TC_1CTA,
@@ -63,6 +64,7 @@ EXPORTED_SYMBOLS = (
     "b200fp8_gemm_rowwise_noalloc",
     "b200fp8_noalloc_status",
     "b200fp8_row_quantize",
+    "b200fp8_fused_row_quantize",
     "b200fp8_gemm_rowwise_grouped",
     "b200fp8_selftest_wait_timeout",
     "b200fp8_gemm_blockwise",
@@ -127,6 +129,9 @@ def load() -> ctypes.CDLL:
     lib.b200fp8_selftest_wait_timeout.argtypes = [c_void_p, c_uint32, c_void_p]
     lib.b200fp8_gemm_blockwise.restype = ctypes.c_int
     lib.b200fp8_gemm_blockwise.argtypes = [c_void_p] * 5 + [c_int64] * 8 + [c_void_p, c_size_t, c_uint32, c_void_p]
+    lib.b200fp8_fused_row_quantize.restype = ctypes.c_int
+    lib.b200fp8_fused_row_quantize.argtypes = [ctypes.c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                               ctypes.c_float, ctypes.c_int, c_void_p, c_int64, c_void_p, c_void_p]
     lib.b200fp8_row_quantize.restype = ctypes.c_int
     lib.b200fp8_row_quantize.argtypes = [c_void_p, ctypes.c_int, ctypes.c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p]
     if lib.b200fp8_abi_version() != 1:

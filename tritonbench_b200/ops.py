@@ -141,6 +141,45 @@ def fp8_row_quantize(x: torch.Tensor, recipe: str = "operator") -> Tuple[torch.T
     return q.view(torch.float8_e4m3fn), scale
 
 
+def _fused_row_quantize(producer: int, x1: torch.Tensor, x2: torch.Tensor, eps: float, round_bf16: bool, what: str):
+    _require_cuda(x1, "x1")
+    _require_cuda(x2, "x2")
+    if x1.dtype != torch.bfloat16 or x2.dtype != torch.bfloat16:
+        raise ValueError("inputs must be bfloat16")
+    if x1.dim() != 2 or x1.stride(1) != 1:
+        raise ValueError("x1 must be [rows, cols] with cols contiguous")
+    rows, cols = x1.shape
+    q = torch.empty((rows, cols), dtype=torch.uint8, device=x1.device)
+    scale = torch.empty((rows,), dtype=torch.float32, device=x1.device)
+    status = _lib.load().b200fp8_fused_row_quantize(
+        producer, x1.data_ptr(), x2.data_ptr(), rows, cols, x1.stride(0), x2.stride(0) if x2.dim() == 2 else 0,
+        float(eps), 1 if round_bf16 else 0, q.data_ptr(), q.stride(0), scale.data_ptr(),
+        torch.cuda.current_stream(x1.device).cuda_stream,
+    )
+    _lib.check(status, f"b200fp8_fused_row_quantize({what}, {rows}x{cols})")
+    return q.view(torch.float8_e4m3fn), scale
+
+
+def rms_norm_fp8_rowwise_quant(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5,
+                               round_bf16: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """RMS norm + rowwise e4m3 quantisation in one kernel, in the argument order of the call
+    `rms_norm_fp8_rowwise_quant(x1, wd)` (tritonbench/operators/fp8_fused_quant_gemm_rowwise/operator.py:88):
+    y = x * rsqrt(mean(x^2) + eps) * weight in fp32, then scale = max(rowabsmax, 1e-12) / 448.
+    round_bf16=True rounds y to bf16 first (the unfused `rms_norm` then `quantize_fp8_row`, operator.py:98-103)."""
+    if weight.dim() != 1 or weight.numel() != x.shape[1] or not weight.is_contiguous():
+        raise ValueError("weight must be a contiguous vector with one element per column of x")
+    return _fused_row_quantize(_lib.PRODUCER_RMS_NORM, x, weight, eps, round_bf16, "rms_norm")
+
+
+def silu_mul_fp8_rowwise_quant(x1: torch.Tensor, x2: torch.Tensor, round_bf16: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """SiLU(x1) * x2 + rowwise e4m3 quantisation in one kernel (`silu_mul_fp8_rowwise_quant(x1, x2)`,
+    tritonbench/operators/fp8_fused_quant_gemm_rowwise/operator.py:112); fp32 arithmetic;
+    round_bf16=True rounds the product to bf16 first (`silu_mul` then `quantize_fp8_row`, operator.py:122-127)."""
+    if x2.dim() != 2 or tuple(x2.shape) != tuple(x1.shape) or x2.stride(1) != 1:
+        raise ValueError("x2 must have the shape of x1, cols contiguous")
+    return _fused_row_quantize(_lib.PRODUCER_SILU_MUL, x1, x2, 0.0, round_bf16, "silu_mul")
+
+
 def fp8_gemm_rowwise_grouped(
     xq: torch.Tensor, wq: torch.Tensor, m_sizes: torch.Tensor, x_scale: torch.Tensor, w_scale: torch.Tensor,
     out: Optional[torch.Tensor] = None,

@@ -224,6 +224,110 @@ def register_blockwise():
     return cls
 
 
+def _fused_backend(producer: str, round_bf16: bool) -> Callable:
+    """Backend factory for `fp8_fused_quant_gemm_rowwise`: producer + quantiser in one kernel, then the GEMM.  The
+    closure runs both kernels, as the stock backends do (operator.py:86-131 time the quantiser with the GEMM)."""
+
+    def backend(self, x1, x2, wq, w_scale, wd) -> Callable:
+        if not x1.is_cuda:
+            raise NotImplementedError("b200 backend runs on CUDA devices only; there is no CPU path")
+        from . import ops
+
+        m, k = x1.shape
+        n = wq.shape[0]
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=x1.device)
+        workspace = ops.get_workspace(x1.device, ops.workspace_bytes(m, n, k))
+        w_scale = w_scale.contiguous()
+
+        def fn():
+            if producer == "rms_norm":
+                xq, xs = ops.rms_norm_fp8_rowwise_quant(x1, wd, round_bf16=round_bf16)
+            else:
+                xq, xs = ops.silu_mul_fp8_rowwise_quant(x1, x2, round_bf16=round_bf16)
+            return ops.fp8_gemm_rowwise(xq, wq, xs, w_scale, out=out, workspace=workspace)
+
+        return fn
+
+    return backend
+
+
+def _torch_fused_ref(producer: str) -> Callable:
+    """fp32 torch pipeline of the same definition (producer, rowwise quantiser, dequantised fp32 GEMM)."""
+
+    def backend(self, x1, x2, wq, w_scale, wd) -> Callable:
+        def fn():
+            a = x1.to(torch.float32)
+            if producer == "rms_norm":
+                y = (a * torch.rsqrt(a.pow(2).mean(dim=1, keepdim=True) + 1e-5)) * wd.to(torch.float32)[None, :]
+            else:
+                y = a * torch.sigmoid(a) * x2.to(torch.float32)
+            scale = y.abs().amax(dim=1).clamp(min=1e-12) / 448.0
+            yq = (y / scale[:, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+            out = (yq.to(torch.float32) @ wq.to(torch.float32).T) * (scale[:, None] * w_scale[None, :])
+            return out.to(torch.bfloat16)
+
+        return fn
+
+    return backend
+
+
+def _standin_quantize_fp8_row(a, scale_ub=None, zero_start_index_M=None, use_triton=True, output_device=None):
+    """Stand-in for FBGEMM's `quantize_fp8_row` used by input generators when FBGEMM is absent:
+    fp32 arithmetic, scale = max(rowabsmax, 1e-12) / 448, returns (a_fp8, scale)."""
+    from . import quantize
+
+    return quantize.fp8_row_quantize_fp32(a.reshape(-1, a.shape[-1]))
+
+
+def register_fused_quant():
+    """Add backends to `fp8_fused_quant_gemm_rowwise` (RMS norm or SiLU-mul producer, rowwise quantiser, GEMM).
+    Its module needs `fbgemm_gpu.experimental.gen_ai`, `quantize_fp8_row` and `matmul_fp8_row` to import and its own
+    producers come from a Meta-internal package, so every stock backend is disabled here; the stand-ins only let the
+    module load and its input generator run.  The rms_norm torch pipeline is the baseline: `accuracy` is meaningful for
+    the rms_norm backends only (the operator compares every backend with one baseline although it holds two functions)."""
+    standin = _install_fbgemm_standin() or getattr(sys.modules.get("fbgemm_gpu"), "__b200_standin__", False)
+    if standin:
+        name = "fbgemm_gpu.experimental.gen_ai"
+        if name not in sys.modules:
+            mod = types.ModuleType(name)
+            mod.__b200_standin__ = True
+            sys.modules[name] = mod
+            sys.modules["fbgemm_gpu.experimental"].gen_ai = mod
+        fp8_gemm_mod = sys.modules["fbgemm_gpu.experimental.gemm.triton_gemm.fp8_gemm"]
+        fp8_gemm_mod.quantize_fp8_row = _standin_quantize_fp8_row
+
+        def _absent(*args, **kwargs):
+            raise NotImplementedError("FBGEMM is not installed")
+
+        fp8_gemm_mod.matmul_fp8_row = _absent
+    from tritonbench.utils.triton_op import REGISTERED_BENCHMARKS, register_benchmark
+
+    op = "fp8_fused_quant_gemm_rowwise"
+    module = importlib.import_module(f"tritonbench.operators.{op}.operator")
+    cls = module.Operator
+    if "b200_rms_norm_fused" not in REGISTERED_BENCHMARKS.get(op, {}):
+        cuda = torch.cuda.is_available()
+        for name, producer, rounded in (
+            ("b200_rms_norm_fused", "rms_norm", False),
+            ("b200_rms_norm_quant", "rms_norm", True),
+            ("b200_silu_mul_fused", "silu_mul", False),
+            ("b200_silu_mul_quant", "silu_mul", True),
+        ):
+            fn = _fused_backend(producer, rounded)
+            fn.__name__ = name
+            register_benchmark(operator_name=op, func_name=name, enabled=cuda)(fn)
+            setattr(cls, name, fn)
+        ref_silu = _torch_fused_ref("silu_mul")
+        ref_silu.__name__ = "torch_silu_mul_ref"
+        register_benchmark(operator_name=op, func_name="torch_silu_mul_ref")(ref_silu)
+        setattr(cls, "torch_silu_mul_ref", ref_silu)
+        ref_rms = _torch_fused_ref("rms_norm")
+        ref_rms.__name__ = "torch_rms_norm_ref"
+        register_benchmark(operator_name=op, func_name="torch_rms_norm_ref", baseline=True)(ref_rms)
+        setattr(cls, "torch_rms_norm_ref", ref_rms)
+    return cls
+
+
 def _wrap_init(cls) -> None:
     stock_init = cls.__init__
     if getattr(stock_init, "__b200_wrapped__", False):
@@ -292,8 +396,17 @@ def run(argv: List[str]):
         register_blockwise()
         if args.atol is None and args.rtol is None:
             args.atol, args.rtol = 1e-3, 1.6e-2
+    elif args.op == "fp8_fused_quant_gemm_rowwise":
+        register_fused_quant()
+        if args.atol is None and args.rtol is None:
+            # a last-bit difference in an activation moves its e4m3 code by a step (12.5 % of that element); a few
+            # such steps per row shift every output of the row by a fraction of a unit, outputs having sigma ~ sqrt(K)
+            args.atol, args.rtol = 1.0, 1.5e-1
     elif args.op != OP_NAME:
-        raise SystemExit(f"this plugin serves --op {OP_NAME}, fp8_gemm, fp8_gemm_rowwise_grouped and fp8_gemm_blockwise only")
+        raise SystemExit(
+            f"this plugin serves --op {OP_NAME}, fp8_gemm, fp8_gemm_rowwise_grouped, fp8_gemm_blockwise and "
+            "fp8_fused_quant_gemm_rowwise only"
+        )
     opbench = load_opbench_by_name(args.op)(tb_args=args, extra_args=extra)
     try:
         opbench.run(args.warmup, args.iter)
