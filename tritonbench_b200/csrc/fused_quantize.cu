@@ -57,6 +57,28 @@ __device__ __forceinline__ float block_reduce(float v, float* smem) {
   return r;
 }
 
+// sum of `s` and max of `m` over the block in one round of barriers
+__device__ __forceinline__ void block_reduce_sum_max(float& s, float& m, float* smem) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  }
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) {
+    smem[threadIdx.x >> 5] = s;
+    smem[kThreads / 32 + (threadIdx.x >> 5)] = m;
+  }
+  __syncthreads();
+  s = smem[0];
+  m = smem[kThreads / 32];
+#pragma unroll
+  for (int w = 1; w < kThreads / 32; ++w) {
+    s += smem[w];
+    m = fmaxf(m, smem[kThreads / 32 + w]);
+  }
+}
+
 __device__ __forceinline__ uint2 codes8(const float (&y)[8], float inv_scale) {
   uint32_t w[2];
 #pragma unroll
@@ -73,7 +95,7 @@ __device__ __forceinline__ uint2 codes8(const float (&y)[8], float inv_scale) {
 // kKeep: vectors of 8 elements a thread keeps in registers (rows up to 256 * 8 * kKeep columns stay on chip)
 template <int kProducer, int kKeep>
 __global__ void __launch_bounds__(kThreads) fused_row_quantize_kernel(const FusedQuantParams p) {
-  __shared__ float red[kThreads / 32];
+  __shared__ float red[2 * (kThreads / 32)];
   const long long row = blockIdx.x;
   const __nv_bfloat16* x1 = static_cast<const __nv_bfloat16*>(p.x1) + row * p.ld1;
   // second operand: the weight vector (RMS norm, shared by all rows) or this row of x2 (SiLU-mul)
@@ -129,9 +151,12 @@ __global__ void __launch_bounds__(kThreads) fused_row_quantize_kernel(const Fuse
       ss = fmaf(a, a, ss);
       amax_xw = fmaxf(amax_xw, fabsf(a * __bfloat162float(x2[c])));
     }
-    ss = block_reduce<false>(ss, red);
+    if (one_pass_stats) {
+      block_reduce_sum_max(ss, amax_xw, red);
+    } else {
+      ss = block_reduce<false>(ss, red);
+    }
     inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(ss, static_cast<float>(cols)) + p.eps));
-    if (one_pass_stats) amax_xw = block_reduce<true>(amax_xw, red);
   }
 
   auto produce = [&](float a, float b) {
