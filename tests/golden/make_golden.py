@@ -62,7 +62,9 @@ def bf16_bits(t):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TRITONBENCH_ROOT", "")
+    if not os.path.isdir(os.path.join(ref_root, "tritonbench")):
+        raise SystemExit("usage: make_golden.py <checkout of meta-pytorch/tritonbench>  (or set TRITONBENCH_ROOT)")
     quantize, shapes = import_reference_quantizer(ref_root)
 
     # (1) the reference's own input recipe (operator.py:280-297): bf16 randn under seed 1337

@@ -29,10 +29,10 @@ def _c_oracle_backend(self, xq, wq, x_scale, w_scale, bias):
 
 @pytest.fixture(scope="module")
 def harness():
-    """Put a copy of the reference package on sys.path: the offline install under baseline/_ref, else a
-    mounted checkout.  No copy -> these tests are skipped (the standalone-operator tests still run)."""
-    for cand in (os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
-        if os.path.isdir(os.path.join(cand, "tritonbench")):
+    """Put a copy of the reference package on sys.path: the offline install under baseline/_ref, else the
+    checkout named by TRITONBENCH_ROOT.  No copy -> these tests are skipped (the standalone-operator tests still run)."""
+    for cand in (os.path.join(ROOT, "baseline", "_ref"), os.environ.get("TRITONBENCH_ROOT", "")):
+        if cand and os.path.isdir(os.path.join(cand, "tritonbench")):
             sys.path.insert(0, cand)
             sys.dont_write_bytecode = True
             return cand
