@@ -93,3 +93,30 @@ def test_no_load_in_the_library_uses_cluster_multicast():
         for line in open(os.path.join(src_dir, name)):
             if "multicast" in line and "cp.async" in line:
                 raise AssertionError(f"{name}: {line.strip()}")
+
+
+def test_one_tile_per_cluster_plans_are_well_formed_for_any_shape(cdll):
+    """Host logic only: for random shapes and every forced cluster size the plan string must describe a tile
+    width that the cluster can split into 16-column multiples, at least one stage, a ring that fits, and a
+    CTA count equal to tiles x cluster."""
+    import random
+    import re
+
+    rng = random.Random(7)
+    pat = re.compile(r"tc_splitk tile=128x(\d+)x128 cluster=(\d+) .* x_rows=(\d+) stages=(\d+) ctas=(\d+) waves=(\d+) smem=(\d+)")
+    for _ in range(400):
+        m = rng.choice([1, 3, 8, 16, 31, 64, 100, 128, 300, 777, 2000])
+        n = rng.choice([8, 24, 100, 256, 1000, 2304, 4096, 13312, 28672, 50000])
+        k = rng.choice([16, 128, 144, 400, 1024, 2304, 8192, 16384])
+        split = rng.choice([0, 1, 2, 4, 8])
+        flags = lib.VARIANT_TC_SPLITK | lib.flag_splitk_config(0, split)
+        plan = lib.describe_plan(m, n, k, flags)
+        got = pat.match(plan)
+        assert got, plan
+        bn, s, x_rows, stages, ctas, waves, smem = (int(v) for v in got.groups())
+        assert 16 <= bn <= 256 and bn % (16 * s) == 0, plan
+        assert split in (0, s), plan
+        assert x_rows == (128 if m >= 128 else (m + 7) // 8 * 8), plan
+        assert 1 <= stages <= 14 and stages * (x_rows + bn) * 128 <= 192 * 1024, plan
+        assert ctas == ((m + 127) // 128) * ((n + bn - 1) // bn) * s and waves >= 1, plan
+        assert smem <= 227 * 1024, plan

@@ -669,9 +669,9 @@ int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char*
     case B200FP8_VARIANT_TC_SPLITK:
       snprintf(buf, n,
                "tc_splitk tile=128x%dx128 cluster=%d (K split, DSMEM reduce-scatter) x_rows=%d stages=%d ctas=%d "
-               "resident_clusters=%d/%d/%d/%d workspace=%zu",
+               "waves=%d smem=%d resident_clusters=%d/%d/%d/%d workspace=%zu",
                pl.splitk.block_n, pl.splitk.split, pl.splitk.rows_a, pl.splitk.stages,
-               pl.splitk.tiles * pl.splitk.split, dev.split_clusters[0],
+               pl.splitk.tiles * pl.splitk.split, pl.splitk.waves, pl.splitk.smem_bytes, dev.split_clusters[0],
                dev.split_clusters[1], dev.split_clusters[2], dev.split_clusters[3], pl.workspace_bytes);
       break;
     case B200FP8_VARIANT_SKINNY:
