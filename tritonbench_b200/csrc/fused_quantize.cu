@@ -15,7 +15,8 @@
 //
 // A CTA owns a row; what it read stays in registers between the reductions and the quantisation
 // (RMS norm: the packed bf16 row, y is recomputed; SiLU-mul: y in fp32), for rows up to 16384 columns;
-// longer rows recompute the overflow from the inputs.
+// longer rows recompute the overflow from the inputs.  The common RMS-norm case (aligned rows of at most
+// 8192 columns, no bf16 rounding) runs a persistent form that keeps the weight vector in registers.
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -236,6 +237,102 @@ __global__ void __launch_bounds__(kThreads) fused_row_quantize_kernel(const Fuse
   }
 }
 
+// RMS norm, persistent form: a CTA walks over rows blockIdx.x, blockIdx.x + gridDim.x, ... and keeps its
+// slice of the weight vector unpacked in registers for all of them; the next row is requested from memory
+// before the current one is reduced.  Same arithmetic as the kernel above without the bf16 rounding of y.
+// Needs 16-byte aligned rows, cols a multiple of 8 and at most 256 * 8 * kKeep (kKeep <= 4: the weight slice,
+// this row and the next one have to fit in registers).
+template <int kKeep>
+__global__ void __launch_bounds__(kThreads) rms_norm_quantize_persistent_kernel(const FusedQuantParams p) {
+  __shared__ float red[2 * (kThreads / 32)];
+  const __nv_bfloat16* wvec = static_cast<const __nv_bfloat16*>(p.x2);
+  const int nvec = p.cols / kVec;
+  float w[kKeep][8];
+#pragma unroll
+  for (int i = 0; i < kKeep; ++i) {
+    const int v = threadIdx.x + i * kThreads;
+    if (v < nvec) {
+      unpack8(*reinterpret_cast<const uint4*>(wvec + v * kVec), w[i]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[i][j] = 0.0f;
+    }
+  }
+  uint4 cur[kKeep];
+  long long row = blockIdx.x;
+  if (row < p.rows) {
+    const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.x1) + row * p.ld1;
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+      const int v = threadIdx.x + i * kThreads;
+      cur[i] = v < nvec ? *reinterpret_cast<const uint4*>(x + v * kVec) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  for (; row < p.rows; row += gridDim.x) {
+    uint4 nxt[kKeep];
+    const long long next_row = row + gridDim.x;
+    if (next_row < p.rows) {  // in flight while this row is reduced and written
+      const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.x1) + next_row * p.ld1;
+#pragma unroll
+      for (int i = 0; i < kKeep; ++i) {
+        const int v = threadIdx.x + i * kThreads;
+        nxt[i] = v < nvec ? *reinterpret_cast<const uint4*>(x + v * kVec) : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    float ss = 0.0f, amax_xw = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {  // vectors beyond the row are zeros: they add nothing
+      float a[8];
+      unpack8(cur[i], a);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        ss = fmaf(a[j], a[j], ss);
+        amax_xw = fmaxf(amax_xw, fabsf(a[j] * w[i][j]));
+      }
+    }
+    block_reduce_sum_max(ss, amax_xw, red);
+    const float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(ss, static_cast<float>(p.cols)) + p.eps));
+    const float scale = __fdiv_rn(fmaxf(amax_xw * inv_rms, 1e-12f), 448.0f);
+    const float inv_scale = __fdiv_rn(1.0f, scale);
+    if (threadIdx.x == 0) p.scale[row] = scale;
+    uint8_t* q = p.q + row * p.ldq;
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+      const int v = threadIdx.x + i * kThreads;
+      if (v < nvec) {
+        float a[8], y[8];
+        unpack8(cur[i], a);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] = (a[j] * inv_rms) * w[i][j];
+        *reinterpret_cast<uint2*>(q + v * kVec) = codes8(y, inv_scale);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) cur[i] = nxt[i];
+  }
+}
+
+template <int kKeep>
+cudaError_t launch_rms_persistent(const FusedQuantParams& p, cudaStream_t stream) {
+  static int ctas_per_device[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  int ctas = dev < 64 ? ctas_per_device[dev] : 0;
+  if (ctas == 0) {
+    int sms = 0, per_sm = 0;
+    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) return err;
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rms_norm_quantize_persistent_kernel<kKeep>, kThreads, 0);
+    if (err != cudaSuccess) return err;
+    ctas = sms * (per_sm > 0 ? per_sm : 1);
+    if (dev < 64) ctas_per_device[dev] = ctas;
+  }
+  const long long grid = p.rows < ctas ? p.rows : ctas;
+  rms_norm_quantize_persistent_kernel<kKeep><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
 template <int kProducer>
 cudaError_t launch_producer(const FusedQuantParams& p, cudaStream_t stream) {
   const dim3 grid(static_cast<unsigned>(p.rows), 1, 1);
@@ -252,6 +349,10 @@ cudaError_t launch_producer(const FusedQuantParams& p, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t launch_fused_row_quantize(const FusedQuantParams& p, cudaStream_t stream) {
+  if (p.producer == kProducerRmsNorm && !p.round_bf16 && p.vector_ok && p.cols % kVec == 0) {
+    if (p.cols <= 2 * kThreads * kVec) return launch_rms_persistent<2>(p, stream);
+    if (p.cols <= 4 * kThreads * kVec) return launch_rms_persistent<4>(p, stream);
+  }
   if (p.producer == kProducerRmsNorm) return launch_producer<kProducerRmsNorm>(p, stream);
   if (p.producer == kProducerSiluMul) return launch_producer<kProducerSiluMul>(p, stream);
   return cudaErrorInvalidValue;
