@@ -129,6 +129,7 @@ def _main() -> None:
     ap.add_argument("--cols", type=int, default=8192)
     ap.add_argument("--dtype", choices=["bf16", "fp16", "fp32"], default="bf16")
     ap.add_argument("--producer", choices=["none", "rms_norm", "silu_mul"], default="none")
+    ap.add_argument("--round-bf16", action="store_true", help="producers: round the activation to bf16 before quantising")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
@@ -141,11 +142,11 @@ def _main() -> None:
     in_bytes = x.element_size()
     if args.producer == "rms_norm":
         w = torch.randn((args.cols,), device="cuda", dtype=dt)
-        fn = lambda: ops.rms_norm_fp8_rowwise_quant(x, w)  # noqa: E731
+        fn = lambda: ops.rms_norm_fp8_rowwise_quant(x, w, round_bf16=args.round_bf16)  # noqa: E731
     elif args.producer == "silu_mul":
         x2 = torch.randn((args.rows, args.cols), device="cuda", dtype=dt)
         in_bytes *= 2
-        fn = lambda: ops.silu_mul_fp8_rowwise_quant(x, x2)  # noqa: E731
+        fn = lambda: ops.silu_mul_fp8_rowwise_quant(x, x2, round_bf16=args.round_bf16)  # noqa: E731
     else:
         fn = lambda: ops.fp8_row_quantize(x)  # noqa: E731
     for _ in range(args.warmup):
