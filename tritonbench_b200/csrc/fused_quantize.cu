@@ -312,9 +312,62 @@ __global__ void __launch_bounds__(kThreads) rms_norm_quantize_persistent_kernel(
   }
 }
 
+// SiLU-mul, persistent form: the next row of both inputs is in flight while the current one is reduced
+// and written.  Same arithmetic as the one-row-per-CTA kernel without the bf16 rounding of y.
 template <int kKeep>
-cudaError_t launch_rms_persistent(const FusedQuantParams& p, cudaStream_t stream) {
-  static int ctas_per_device[64] = {};
+__global__ void __launch_bounds__(kThreads) silu_mul_quantize_persistent_kernel(const FusedQuantParams p) {
+  __shared__ float red[kThreads / 32];
+  const int nvec = p.cols / kVec;
+  uint4 cur1[kKeep], cur2[kKeep];
+  auto load_row = [&](long long r, uint4 (&a)[kKeep], uint4 (&b)[kKeep]) {
+    const __nv_bfloat16* x1 = static_cast<const __nv_bfloat16*>(p.x1) + r * p.ld1;
+    const __nv_bfloat16* x2 = static_cast<const __nv_bfloat16*>(p.x2) + r * p.ld2;
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+      const int v = threadIdx.x + i * kThreads;
+      a[i] = v < nvec ? *reinterpret_cast<const uint4*>(x1 + v * kVec) : make_uint4(0u, 0u, 0u, 0u);
+      b[i] = v < nvec ? *reinterpret_cast<const uint4*>(x2 + v * kVec) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  long long row = blockIdx.x;
+  if (row < p.rows) load_row(row, cur1, cur2);
+  for (; row < p.rows; row += gridDim.x) {
+    uint4 nxt1[kKeep], nxt2[kKeep];
+    const long long next_row = row + gridDim.x;
+    if (next_row < p.rows) load_row(next_row, nxt1, nxt2);
+    float y[kKeep][8];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {  // vectors beyond the row are zeros: silu(0) * 0 = 0
+      float a[8], b[8];
+      unpack8(cur1[i], a);
+      unpack8(cur2[i], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        y[i][j] = silu_mul(a[j], b[j]);
+        amax = fmaxf(amax, fabsf(y[i][j]));
+      }
+    }
+    amax = block_reduce<true>(amax, red);
+    const float scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+    const float inv_scale = __fdiv_rn(1.0f, scale);
+    if (threadIdx.x == 0) p.scale[row] = scale;
+    uint8_t* q = p.q + row * p.ldq;
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+      const int v = threadIdx.x + i * kThreads;
+      if (v < nvec) *reinterpret_cast<uint2*>(q + v * kVec) = codes8(y[i], inv_scale);
+    }
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+      cur1[i] = nxt1[i];
+      cur2[i] = nxt2[i];
+    }
+  }
+}
+
+template <typename Kernel>
+cudaError_t launch_persistent(Kernel kernel, int* ctas_per_device, const FusedQuantParams& p, cudaStream_t stream) {
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
@@ -323,14 +376,26 @@ cudaError_t launch_rms_persistent(const FusedQuantParams& p, cudaStream_t stream
     int sms = 0, per_sm = 0;
     err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (err != cudaSuccess) return err;
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rms_norm_quantize_persistent_kernel<kKeep>, kThreads, 0);
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0);
     if (err != cudaSuccess) return err;
     ctas = sms * (per_sm > 0 ? per_sm : 1);
     if (dev < 64) ctas_per_device[dev] = ctas;
   }
   const long long grid = p.rows < ctas ? p.rows : ctas;
-  rms_norm_quantize_persistent_kernel<kKeep><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
+  kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
   return cudaGetLastError();
+}
+
+template <int kKeep>
+cudaError_t launch_rms_persistent(const FusedQuantParams& p, cudaStream_t stream) {
+  static int ctas_per_device[64] = {};
+  return launch_persistent(rms_norm_quantize_persistent_kernel<kKeep>, ctas_per_device, p, stream);
+}
+
+template <int kKeep>
+cudaError_t launch_silu_persistent(const FusedQuantParams& p, cudaStream_t stream) {
+  static int ctas_per_device[64] = {};
+  return launch_persistent(silu_mul_quantize_persistent_kernel<kKeep>, ctas_per_device, p, stream);
 }
 
 template <int kProducer>
@@ -352,6 +417,10 @@ cudaError_t launch_fused_row_quantize(const FusedQuantParams& p, cudaStream_t st
   if (p.producer == kProducerRmsNorm && !p.round_bf16 && p.vector_ok && p.cols % kVec == 0) {
     if (p.cols <= 2 * kThreads * kVec) return launch_rms_persistent<2>(p, stream);
     if (p.cols <= 4 * kThreads * kVec) return launch_rms_persistent<4>(p, stream);
+  }
+  if (p.producer == kProducerSiluMul && !p.round_bf16 && p.vector_ok && p.cols % kVec == 0) {
+    if (p.cols <= 2 * kThreads * kVec) return launch_silu_persistent<2>(p, stream);
+    if (p.cols <= 4 * kThreads * kVec) return launch_silu_persistent<4>(p, stream);
   }
   if (p.producer == kProducerRmsNorm) return launch_producer<kProducerRmsNorm>(p, stream);
   if (p.producer == kProducerSiluMul) return launch_producer<kProducerSiluMul>(p, stream);
