@@ -418,7 +418,8 @@ cudaError_t launch_fused_row_quantize(const FusedQuantParams& p, cudaStream_t st
     if (p.cols <= 2 * kThreads * kVec) return launch_rms_persistent<2>(p, stream);
     if (p.cols <= 4 * kThreads * kVec) return launch_rms_persistent<4>(p, stream);
   }
-  if (p.producer == kProducerSiluMul && !p.round_bf16 && p.vector_ok && p.cols % kVec == 0) {
+  // (rows of up to 2560 columns give a thread too little to do between two block reductions: measured slower)
+  if (p.producer == kProducerSiluMul && !p.round_bf16 && p.vector_ok && p.cols % kVec == 0 && p.cols > 2560) {
     if (p.cols <= 2 * kThreads * kVec) return launch_silu_persistent<2>(p, stream);
     if (p.cols <= 4 * kThreads * kVec) return launch_silu_persistent<4>(p, stream);
   }
