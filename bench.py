@@ -327,40 +327,6 @@ def run_own(args, workload):
             "gathered_bytes_per_rank": (world - 1) * 2 * m * n,
             "note": "GEMM into this rank's slice of the [M,N] buffer, then in-place NCCL all-gather, same stream",
         }
-        # the same result with the exchange overlapped: the GEMM runs in row panels and each panel is sent to the
-        # peers (NCCL point-to-point, in place) while the next one is multiplied
-        panels = 4 if m % 4 == 0 and m >= 1024 else 1
-        rows_p = m // panels
-
-        def overlapped_step(i):
-            xq, xs = xs_list[i % n_buf]
-            works = []
-            for pnl in range(panels):
-                r0 = pnl * rows_p
-                ops.fp8_gemm_rowwise(xq[r0 : r0 + rows_p], wq, xs[r0 : r0 + rows_p], ws, out=mine[r0 : r0 + rows_p],
-                                     workspace=workspace)
-                works += shard.exchange_panel(full, world, rank, r0, rows_p)
-            for w in works:
-                w.wait()
-
-        for i in range(2):
-            overlapped_step(i)
-        barrier()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for i in range(steps):
-            overlapped_step(i)
-        g1.record()
-        barrier()
-        t = torch.tensor([g0.elapsed_time(g1)], dtype=torch.float64, device=device)
-        td.all_reduce(t, op=td.ReduceOp.MAX)
-        o_ms = float(t.item()) / steps
-        gather["overlapped"] = {
-            "ms_per_step": o_ms,
-            "value": world * flops_step_rank / (o_ms * 1e-3) / 1e12,
-            "panels": panels,
-            "note": "GEMM in row panels; each panel exchanged with all peers (NCCL send/recv, in place) while the next is multiplied",
-        }
 
     if rank == 0:
         fp8_peak, hbm_peak, peak_note = measured_peaks()

@@ -51,17 +51,6 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str):
     full.zero_()
     mine.copy_(orc.gemm_rowwise(xq, wq, xs, ws))  # CPU stand-in for the rank's GEMM, written in place
     shard.all_gather_rows(full, world)
-    # the same result assembled panel by panel (the form that overlaps with the GEMM of the next panel)
-    full2, mine2 = shard.gathered_output(M_TOTAL, N, world, rank, "cpu")
-    full2.zero_()
-    per = M_TOTAL // world
-    works = []
-    for row0 in range(0, per, per // 4):
-        mine2[row0 : row0 + per // 4].copy_(mine[row0 : row0 + per // 4])
-        works += shard.exchange_panel(full2, world, rank, row0, per // 4)
-    for w in works:
-        w.wait()
-    assert torch.equal(full2, full)
     # device-time style reduction: the slowest rank's time is what gets reported
     t = torch.tensor([float(rank + 1)], dtype=torch.float64)
     td.all_reduce(t, op=td.ReduceOp.MAX)

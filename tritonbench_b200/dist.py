@@ -78,28 +78,6 @@ def all_gather_rows(full: torch.Tensor, world_size: int) -> None:
     td.all_gather_into_tensor(full, full[shard_slice(full.shape[0], world_size, td.get_rank())])
 
 
-def exchange_panel(full: torch.Tensor, world_size: int, rank: int, row0: int, rows: int):
-    """Start the exchange of rows [row0, row0 + rows) of every rank's slice of `full` with all peers, in place and in
-    the natural row order (batched point-to-point sends and receives: an all-gather of one row panel whose pieces are
-    not contiguous in `full`).  Returns the work handles; the caller waits on them.  Issued right after the GEMM of that
-    panel, the transfer runs while the next panel is being multiplied."""
-    import torch.distributed as td
-
-    if world_size == 1:
-        return []
-    per = full.shape[0] // world_size
-    if not (0 <= row0 and rows > 0 and row0 + rows <= per):
-        raise ValueError(f"panel [{row0}, {row0 + rows}) outside a slice of {per} rows")
-    mine = full[rank * per + row0 : rank * per + row0 + rows]
-    p2p = []
-    for step in range(1, world_size):  # staggered peers: rank r talks to r+step and r-step in the same round
-        dst = (rank + step) % world_size
-        src = (rank - step) % world_size
-        p2p.append(td.P2POp(td.isend, mine, dst))
-        p2p.append(td.P2POp(td.irecv, full[src * per + row0 : src * per + row0 + rows], src))
-    return td.batch_isend_irecv(p2p)
-
-
 def shard_slice(m_total: int, world_size: int, rank: int) -> slice:
     r0, r1 = shard_rows(m_total, world_size, rank)
     return slice(r0, r1)
