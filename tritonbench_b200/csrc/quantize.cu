@@ -206,15 +206,100 @@ __global__ void __launch_bounds__(kThreads) row_quantize_kernel(const QuantParam
   }
 }
 
+// Persistent form for aligned rows of at most 256 * 8 * kKeep elements: a CTA walks over rows blockIdx.x,
+// blockIdx.x + gridDim.x, ... and requests the next row before it reduces and writes the current one, so that
+// memory latency is paid once per CTA instead of once per row.  Same arithmetic, same bits.
+template <typename T, int kRecipe, int kKeep>
+__global__ void __launch_bounds__(kThreads) row_quantize_persistent_kernel(const QuantParams p) {
+  __shared__ float red[kThreads / 32];
+  using O = Ops<T, kRecipe>;
+  const int nvec = p.cols / kVec;
+  Raw<T> cur[kKeep];
+  auto load_row = [&](long long r, Raw<T> (&dst)[kKeep]) {
+    const T* x = static_cast<const T*>(p.x) + r * p.ldx;
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+      const int v = threadIdx.x + i * kThreads;
+      if (v < nvec) {
+        dst[i] = load_raw<T>(x + v * kVec);
+      } else {
+        dst[i].lo = make_uint4(0u, 0u, 0u, 0u);  // zeros: no effect on the absmax, never written
+        dst[i].hi = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+  long long row = blockIdx.x;
+  if (row < p.rows) load_row(row, cur);
+  for (; row < p.rows; row += gridDim.x) {
+    Raw<T> nxt[kKeep];
+    const long long next_row = row + gridDim.x;
+    if (next_row < p.rows) load_row(next_row, nxt);
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) amax = fmaxf(amax, O::absmax(cur[i]));
+    __syncthreads();  // the previous row's readers are done with `red`
+    amax = block_max(amax, red);
+    float mult, scale;
+    if constexpr (kRecipe == kRecipeOperator) {
+      const float c = fmaxf(amax, Conv<T>::rnd(1e-12f));
+      mult = Conv<T>::rnd(__fmul_rn(Conv<T>::rnd(__fdiv_rn(1.0f, c)), 448.0f));
+      if constexpr (std::is_same<T, __half>::value) mult = fminf(mult, 65504.0f);
+      scale = Conv<T>::rnd(__fdiv_rn(1.0f, mult));
+    } else {
+      scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+      mult = scale;  // used as the divisor
+    }
+    if (threadIdx.x == 0) p.scale[row] = scale;
+    uint8_t* q = p.q + row * p.ldq;
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+      const int v = threadIdx.x + i * kThreads;
+      if (v < nvec) *reinterpret_cast<uint2*>(q + v * kVec) = O::codes(cur[i], mult);
+    }
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) cur[i] = nxt[i];
+  }
+}
+
+template <typename T, int kRecipe, int kKeep>
+cudaError_t launch_persistent(const QuantParams& p, cudaStream_t stream) {
+  static int ctas_per_device[64] = {};
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  int ctas = dev < 64 ? ctas_per_device[dev] : 0;
+  if (ctas == 0) {
+    int sms = 0, per_sm = 0;
+    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) return err;
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, row_quantize_persistent_kernel<T, kRecipe, kKeep>,
+                                                        kThreads, 0);
+    if (err != cudaSuccess) return err;
+    ctas = sms * (per_sm > 0 ? per_sm : 1);
+    if (dev < 64) ctas_per_device[dev] = ctas;
+  }
+  const long long grid = p.rows < ctas ? p.rows : ctas;
+  row_quantize_persistent_kernel<T, kRecipe, kKeep><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+template <typename T, int kRecipe>
+cudaError_t launch_recipe(const QuantParams& p, cudaStream_t stream) {
+  // rows of 2561..8192 elements, aligned, a multiple of 8 long: the persistent kernel (shorter rows leave a
+  // thread too little to do between two block reductions)
+  if (p.vector_ok && p.cols % kVec == 0 && p.cols > 2560 && p.cols <= 4 * kThreads * kVec) {
+    if (p.cols <= 2 * kThreads * kVec) return launch_persistent<T, kRecipe, 2>(p, stream);
+    return launch_persistent<T, kRecipe, 4>(p, stream);
+  }
+  const dim3 grid(static_cast<unsigned>(p.rows), 1, 1);
+  row_quantize_kernel<T, kRecipe><<<grid, kThreads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
 template <typename T>
 cudaError_t launch_t(const QuantParams& p, cudaStream_t stream) {
-  const dim3 grid(static_cast<unsigned>(p.rows), 1, 1);
-  if (p.recipe == kRecipeOperator) {
-    row_quantize_kernel<T, kRecipeOperator><<<grid, kThreads, 0, stream>>>(p);
-  } else {
-    row_quantize_kernel<T, kRecipeFp32><<<grid, kThreads, 0, stream>>>(p);
-  }
-  return cudaGetLastError();
+  if (p.recipe == kRecipeOperator) return launch_recipe<T, kRecipeOperator>(p, stream);
+  return launch_recipe<T, kRecipeFp32>(p, stream);
 }
 
 }  // namespace
