@@ -261,6 +261,50 @@ __global__ void __launch_bounds__(kThreads) row_quantize_persistent_kernel(const
   }
 }
 
+// Short rows (at most 2560 elements, aligned, a multiple of 8 long): one warp per row, eight rows per CTA.
+// The absmax is a warp reduction, so no thread ever waits at a block barrier.  Same arithmetic, same bits.
+constexpr int kShortRowVecs = 10;  // vectors of 8 elements per lane: 32 * 8 * 10 = 2560 elements
+template <typename T, int kRecipe>
+__global__ void __launch_bounds__(kThreads) row_quantize_short_rows_kernel(const QuantParams p) {
+  using O = Ops<T, kRecipe>;
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+  if (row >= p.rows) return;  // whole warps leave together: no barrier follows
+  const T* x = static_cast<const T*>(p.x) + row * p.ldx;
+  uint8_t* q = p.q + row * p.ldq;
+  const int nvec = p.cols / kVec;
+  Raw<T> keep[kShortRowVecs];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kShortRowVecs; ++i) {
+    const int v = lane + i * 32;
+    if (v < nvec) keep[i] = load_raw<T>(x + v * kVec);
+  }
+#pragma unroll
+  for (int i = 0; i < kShortRowVecs; ++i) {
+    const int v = lane + i * 32;
+    if (v < nvec) amax = fmaxf(amax, O::absmax(keep[i]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  float mult, scale;
+  if constexpr (kRecipe == kRecipeOperator) {
+    const float c = fmaxf(amax, Conv<T>::rnd(1e-12f));
+    mult = Conv<T>::rnd(__fmul_rn(Conv<T>::rnd(__fdiv_rn(1.0f, c)), 448.0f));
+    if constexpr (std::is_same<T, __half>::value) mult = fminf(mult, 65504.0f);
+    scale = Conv<T>::rnd(__fdiv_rn(1.0f, mult));
+  } else {
+    scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+    mult = scale;  // used as the divisor
+  }
+  if (lane == 0) p.scale[row] = scale;
+#pragma unroll
+  for (int i = 0; i < kShortRowVecs; ++i) {
+    const int v = lane + i * 32;
+    if (v < nvec) *reinterpret_cast<uint2*>(q + v * kVec) = O::codes(keep[i], mult);
+  }
+}
+
 template <typename T, int kRecipe, int kKeep>
 cudaError_t launch_persistent(const QuantParams& p, cudaStream_t stream) {
   static int ctas_per_device[64] = {};
@@ -290,6 +334,11 @@ cudaError_t launch_recipe(const QuantParams& p, cudaStream_t stream) {
   if (p.vector_ok && p.cols % kVec == 0 && p.cols > 2560 && p.cols <= 4 * kThreads * kVec) {
     if (p.cols <= 2 * kThreads * kVec) return launch_persistent<T, kRecipe, 2>(p, stream);
     return launch_persistent<T, kRecipe, 4>(p, stream);
+  }
+  if (p.vector_ok && p.cols % kVec == 0 && p.cols <= 32 * kVec * kShortRowVecs && p.rows >= 64) {
+    const long long ctas = (p.rows + kThreads / 32 - 1) / (kThreads / 32);
+    row_quantize_short_rows_kernel<T, kRecipe><<<static_cast<unsigned>(ctas), kThreads, 0, stream>>>(p);
+    return cudaGetLastError();
   }
   const dim3 grid(static_cast<unsigned>(p.rows), 1, 1);
   row_quantize_kernel<T, kRecipe><<<grid, kThreads, 0, stream>>>(p);
