@@ -68,7 +68,10 @@ __device__ __forceinline__ float4 ld_shared_v4(uint32_t addr) {
 
 template <int kCols>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[kCols]) {
-  if constexpr (kCols == 32) {
+  if constexpr (kCols == 64) {  // two reads in flight, one wait
+    tmem_ld_32x32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+    tmem_ld_32x32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+  } else if constexpr (kCols == 32) {
     tmem_ld_32x32(taddr, r);
   } else {
     tmem_ld_32x16(taddr, r);
@@ -392,21 +395,25 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       uint32_t store_count = 0;
       int c = 0;
 #pragma unroll 1
-      for (; c + 32 <= slice_cols; c += 32) {
+      for (; c + 64 <= slice_cols; c += 64) {  // 64 columns = one box of the TMA store, when Y leaves in boxes
         const uint32_t sbuf = stage_buf + (store_count & 1u) * (Geo::kStoreRows * Geo::kStoreCols * 2);
-        if (f.boxed && c % Geo::kStoreCols == 0) {
+        if (f.boxed) {
           if (lane == 0) tma_store_wait_read<1>();  // the box used two stores ago has been read
           __syncwarp();
         }
-        finish_columns<32>(f, c, sbuf);
-        if (f.boxed && c % Geo::kStoreCols == Geo::kStoreCols - 32) {
-          const int box_col = col_first + c - (Geo::kStoreCols - 32);
+        finish_columns<64>(f, c, sbuf);
+        if (f.boxed) {
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0 && box_col < p.N) tma_store_2d(&tm_y, sbuf, box_col, row0);
+          if (lane == 0 && col_first + c < p.N) tma_store_2d(&tm_y, sbuf, col_first + c, row0);
           if (lane == 0) tma_store_commit();
           ++store_count;
         }
+      }
+      // what is left of a slice that is not a multiple of 64 columns (never boxed)
+      if (c + 32 <= slice_cols) {
+        finish_columns<32>(f, c, 0u);
+        c += 32;
       }
       if (c < slice_cols) finish_columns<16>(f, c, 0u);  // never boxed: a boxed slice is a multiple of 64 columns
       // the CTA may end once the boxes have been read out of shared memory; the writes complete with the kernel
