@@ -2,10 +2,10 @@
 // persistent kernels: narrower tiles, and split-K inside a thread-block cluster, reduced over
 // distributed shared memory.
 //
-// A cluster of S CTAs (S = 1, 2, 4 or 8) owns one 128 x BN tile of Y (BN a multiple of 16 S, at most 256: the
-// host picks the width that gives every SM a tile where it can).  CTA r
-// multiplies the r-th slice of K with the usual pipeline (TMA -> 128B-swizzled ring -> tcgen05.mma ->
-// TMEM); the ring is deep enough that a short slice is requested from memory all at once.  Then, S > 1:
+// A cluster of S CTAs (S = 1, 2, 4 or 8) owns one 128 x BN tile of Y (BN a multiple of 16 S, at most 256:
+// the host picks the width that gives every SM a tile where it can).  CTA r multiplies the r-th slice of K
+// with the usual pipeline (TMA -> 128B-swizzled ring -> tcgen05.mma -> TMEM); the ring is deep enough that
+// a short slice is requested from memory all at once.  Then, S > 1:
 //   (A) cluster barrier: every CTA's MMAs have finished, so every operand ring is free;
 //   exchange: each CTA writes its fp32 partial tile, column slice j (BN/S columns) to CTA j,
 //   into CTA j's (now idle) operand ring through shared::cluster stores - a reduce-scatter;
