@@ -127,7 +127,9 @@ int b200fp8_noalloc_status(uint32_t* device_status);
  * groups of group_rows[g] rows (an int32 array in DEVICE memory, read by the kernel: no host round trip when
  * the sizes come from a router kernel); group g is multiplied with rows [g*N, (g+1)*N) of the stacked
  * wq [num_groups*N, K]; x_scale [M_total], w_scale [num_groups*N]; y [M_total, N].  Rows beyond the sum of the
- * group sizes are left untouched.  Needs only the workspace header (256 bytes).
+ * group sizes are left untouched.  Needs only the workspace header (256 bytes).  `flags`: variant AUTO, TC_1CTA
+ * (128-row tiles per group) or TC_2CTA (a CTA pair per 256-row tile of a group; AUTO picks it when M_total x N has
+ * enough such tiles for the pairs the device runs at once), NO_TMA_STORE, OUT_FP16.
  * Replaces: `grouped_gemm_fp8_rowwise(group_A, group_B, m_sizes, a_scale, b_scale)` and
  * `torch.ops.fbgemm.f8f8bf16_rowwise_grouped_stacked` in
  * tritonbench/operators/fp8_gemm_rowwise_grouped/operator.py:412-470.

@@ -433,8 +433,9 @@ GROUPED_CASES = [
 ]
 
 
+@pytest.mark.parametrize("variant", ["auto", "tc_1cta", "tc_2cta"])
 @pytest.mark.parametrize("case", GROUPED_CASES)
-def test_grouped_gemm(cuda_device, case):
+def test_grouped_gemm(cuda_device, case, variant):
     ops = _ops()
     sizes, n, k = case
     groups, m_total = len(sizes), sum(sizes)
@@ -444,9 +445,9 @@ def test_grouped_gemm(cuda_device, case):
     wq, ws = quantize.make_quantized(groups * n, k, seed=32, std=0.05)
     m_sizes = torch.tensor(sizes, dtype=torch.int32)
     ref = orc.gemm_rowwise_grouped(xq, wq, m_sizes, xs, ws)
-    y = ops.fp8_gemm_rowwise_grouped(*_gpu(xq, wq, m_sizes, xs, ws))
+    y = ops.fp8_gemm_rowwise_grouped(*_gpu(xq, wq, m_sizes, xs, ws), variant=variant)
     ops.check_device_status()
-    _assert_close(y, ref, f"grouped {case}")
+    _assert_close(y, ref, f"grouped {case} {variant}")
     # no group may write into its neighbour's rows: equal to the per-group plain GEMMs bit for bit
     r0 = 0
     for g, rows in enumerate(sizes):

@@ -484,7 +484,9 @@ int b200fp8_gemm_rowwise_grouped(const void* xq, const void* wq, const float* x_
     return B200FP8_BAD_ARG;
   }
   const uint32_t variant = flags & B200FP8_VARIANT_MASK;
-  if (variant != B200FP8_VARIANT_AUTO && variant != B200FP8_VARIANT_TC_1CTA) return B200FP8_BAD_ARG;
+  if (variant != B200FP8_VARIANT_AUTO && variant != B200FP8_VARIANT_TC_1CTA && variant != B200FP8_VARIANT_TC_2CTA) {
+    return B200FP8_BAD_ARG;
+  }
   DeviceInfo dev;
   st = device_info(&dev);
   if (st != B200FP8_OK) return st;
@@ -495,8 +497,13 @@ int b200fp8_gemm_rowwise_grouped(const void* xq, const void* wq, const float* x_
   memset(&tm_y, 0, sizeof(tm_y));
   st = encode_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, M_total, K, ldx, TcGeometry::kBlockK, TcGeometry::kBlockM);
   if (st != B200FP8_OK) return st;
+  // a CTA pair per 256-row tile of a group when the problem has enough such tiles for the pairs the device runs at once
+  // (the group sizes live on the device: the estimate uses M_total as if it were one group)
+  const int64_t tiles_n = (N + 255) / 256;
+  int cta_group = variant == B200FP8_VARIANT_TC_2CTA ? 2 : 1;
+  if (variant == B200FP8_VARIANT_AUTO && (M_total / 256) * tiles_n >= dev.sm_count / 2) cta_group = 2;
   st = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, num_groups * N, K, ldw, TcGeometry::kBlockK,
-                 TcGeometry::kBlockN);
+                 TcGeometry::kBlockN / cta_group);
   if (st != B200FP8_OK) return st;
   const bool tma_store = (ldy % 8 == 0) && aligned16(y_bf16) && (flags & B200FP8_FLAG_NO_TMA_STORE) == 0;
   if (tma_store) {
@@ -519,9 +526,14 @@ int b200fp8_gemm_rowwise_grouped(const void* xq, const void* wq, const float* x_
   tp.num_groups = static_cast<int>(num_groups);
   tp.group_rows = group_rows;
   tp.status = static_cast<uint32_t*>(workspace);
-  // the group sizes live on the device, so the tile count is not known here: one CTA per SM, each
+  // the group sizes live on the device, so the tile count is not known here: one CTA (pair) per SM (pair), each
   // walks the tile list it derives from the sizes
-  const int64_t max_tiles = ((M_total + 127) / 128 + num_groups) * ((N + 255) / 256);
+  if (cta_group == 2) {
+    const int64_t max_tiles = ((M_total + 255) / 256 + num_groups) * tiles_n;
+    const int clusters = static_cast<int>(max_tiles < dev.max_pair_clusters ? max_tiles : dev.max_pair_clusters);
+    return note_cuda(launch_gemm_tc<2>(tm_x, tm_w, tm_y, tp, 2 * clusters, static_cast<cudaStream_t>(cuda_stream)));
+  }
+  const int64_t max_tiles = ((M_total + 127) / 128 + num_groups) * tiles_n;
   const int ctas = static_cast<int>(max_tiles < dev.sm_count ? max_tiles : dev.sm_count);
   return note_cuda(launch_gemm_tc<1>(tm_x, tm_w, tm_y, tp, ctas, static_cast<cudaStream_t>(cuda_stream)));
 }

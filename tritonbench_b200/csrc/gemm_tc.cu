@@ -146,7 +146,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
   ts.N = p.N;
   ts.tiles_n = (p.N + Cfg::kBlockN - 1) / Cfg::kBlockN;
   ts.group_m = p.group_m;
-  ts.num_groups = kPair ? 0 : p.num_groups;
+  ts.num_groups = p.num_groups;
   ts.group_rows = p.group_rows;
   ts.plain_tiles_m = (p.M + Cfg::kTileM - 1) / Cfg::kTileM;
   const int num_tiles = count_tiles(ts, Cfg::kTileM);

@@ -183,6 +183,7 @@ def silu_mul_fp8_rowwise_quant(x1: torch.Tensor, x2: torch.Tensor, round_bf16: b
 def fp8_gemm_rowwise_grouped(
     xq: torch.Tensor, wq: torch.Tensor, m_sizes: torch.Tensor, x_scale: torch.Tensor, w_scale: torch.Tensor,
     out: Optional[torch.Tensor] = None,
+    variant: str = "auto",
 ) -> torch.Tensor:
     """Grouped GEMM in the argument order of the reference's
     `grouped_gemm_fp8_rowwise(group_A, group_B, m_sizes, a_scale, b_scale)`
@@ -205,7 +206,7 @@ def fp8_gemm_rowwise_grouped(
     status = _lib.load().b200fp8_gemm_rowwise_grouped(
         xq.data_ptr(), wq.data_ptr(), x_scale.contiguous().data_ptr(), w_scale.contiguous().data_ptr(), m_sizes.data_ptr(),
         groups, out.data_ptr(), m_total, n, k, xq.stride(0), wq.stride(0), out.stride(0),
-        workspace.data_ptr(), workspace.numel(), 0, torch.cuda.current_stream(xq.device).cuda_stream,
+        workspace.data_ptr(), workspace.numel(), _lib.VARIANTS[variant], torch.cuda.current_stream(xq.device).cuda_stream,
     )
     _lib.check(status, f"b200fp8_gemm_rowwise_grouped(M={m_total}, G={groups}, N={n}, K={k})")
     return out
