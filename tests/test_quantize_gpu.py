@@ -40,7 +40,10 @@ def test_edge_rows_match_reference_fixture(cuda_device, golden_dir, name, dtype)
     assert np.array_equal(s.cpu().numpy(), d[f"s_{name}"], equal_nan=True)
 
 
-@pytest.mark.parametrize("shape", [(1, 16), (3, 7), (17, 130), (64, 8192), (5, 16384), (2, 40000), (300, 1000), (1024, 4096)])
+# the last eight sit on either side of the boundaries between the three kernels (one warp per row up to 2560 elements and
+# from 64 rows, persistent up to 8192, one CTA per row beyond) and make a persistent CTA walk over many rows
+@pytest.mark.parametrize("shape", [(1, 16), (3, 7), (17, 130), (64, 8192), (5, 16384), (2, 40000), (300, 1000), (1024, 4096),
+                                   (63, 2048), (64, 2048), (200, 2560), (200, 2568), (3000, 2816), (200, 8200), (77, 512), (5000, 8192)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 def test_operator_recipe_matches_oracle_on_random_and_ragged_rows(cuda_device, shape, dtype):
     from tritonbench_b200 import ops
@@ -110,7 +113,7 @@ def _check_fused(q, scale, y_ref):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("shape", [(16, 8192), (128, 2304), (3, 1000), (5, 20000), (64, 4104), (7, 33)])
+@pytest.mark.parametrize("shape", [(16, 8192), (128, 2304), (3, 1000), (5, 20000), (64, 4104), (7, 33), (1500, 4096), (3000, 2816)])
 @pytest.mark.parametrize("round_bf16", [False, True])
 def test_rms_norm_quantiser(cuda_device, shape, round_bf16):
     from oracle import fp8_rowwise_oracle as orc
@@ -125,7 +128,7 @@ def test_rms_norm_quantiser(cuda_device, shape, round_bf16):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("shape", [(16, 8192), (128, 2304), (3, 1000), (5, 20000), (64, 4104), (7, 33)])
+@pytest.mark.parametrize("shape", [(16, 8192), (128, 2304), (3, 1000), (5, 20000), (64, 4104), (7, 33), (1500, 4096), (3000, 2816)])
 @pytest.mark.parametrize("round_bf16", [False, True])
 def test_silu_mul_quantiser(cuda_device, shape, round_bf16):
     from oracle import fp8_rowwise_oracle as orc
