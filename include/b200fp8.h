@@ -171,6 +171,17 @@ int b200fp8_row_quantize(const void* x, int x_dtype, int recipe, int64_t rows, i
                          int64_t ldq, float* scale, void* cuda_stream);
 
 /*
+ * 128x128 block quantiser, the operand format of b200fp8_gemm_blockwise: per block the multiplier 448 / blockmax
+ * (blockmax clamped below at 1e-12 in x's dtype, the division in fp32, 1 where it is infinite), q = e4m3(x * mult)
+ * without a clamp, scale[block row][block column] = 1 / mult.  Rows and columns beyond the matrix count as zeros.
+ * scale is [ceil(rows/128)][ld_scale] fp32 with ld_scale >= ceil(cols/128).  Bit-exact with the reference's
+ * `fp8_block_quantize` (tritonbench/operators/fp8_gemm_blockwise/operator.py:87-120), which it replaces: eight eager torch
+ * kernels and a padded copy of x.
+ */
+int b200fp8_block_quantize(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ldx, void* q, int64_t ldq,
+                           float* scale, int64_t ld_scale, void* cuda_stream);
+
+/*
  * Producer + rowwise quantiser in one pass: the activation that feeds the GEMM is computed from its bf16 inputs,
  * quantised (scale = max(rowabsmax(y), 1e-12) / 448, q = e4m3(clamp(y * (1 / scale)))) and written as e4m3 bytes plus
  * one fp32 scale per row, without the bf16 activation being stored.  fp32 arithmetic; the SiLU uses the hardware

@@ -166,3 +166,33 @@ def test_fused_quantiser_feeds_the_gemm_and_handles_strided_and_zero_rows(cuda_d
     err = (y.cpu().float() - ref.float()).abs()
     assert float(err.max()) <= float(orc.tolerance(ref.float()).max()) + 0.05 * float(ref.float().abs().max())
     ops.check_device_status()
+
+
+# ------------------------------------------------------------------ 128x128 block quantiser
+def test_block_quantiser_matches_reference_fixture_bit_for_bit(cuda_device, golden_dir):
+    from tritonbench_b200 import ops
+
+    d = np.load(os.path.join(golden_dir, "ref_block_quantizer_200x300.npz"))
+    q, s = ops.fp8_block_quantize(_bf16(d["x_bf16"]).cuda())
+    assert np.array_equal(q.view(torch.uint8).cpu().numpy(), d["q"])
+    assert np.array_equal(s.cpu().numpy(), d["scale"])
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (256, 384), (1, 1), (130, 129), (1000, 520), (513, 2048), (4096, 4096)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_block_quantiser_matches_oracle(cuda_device, shape, dtype):
+    from tritonbench_b200 import ops
+
+    g = torch.Generator().manual_seed(shape[0] + 3 * shape[1])
+    x = (torch.randn(shape, generator=g) * 20).to(dtype)
+    x[0, 0] = 0.0
+    if shape[0] > 128:
+        x[128:, :128] = 0.0  # a block of zeros: multiplier 448 / 1e-12
+    q_want, s_want = orc.block_quantize_reference(x)
+    q, s = ops.fp8_block_quantize(x.cuda())
+    _same(q, s, q_want, s_want, f"{shape} {dtype}")
+    # a view with a row pitch that breaks the 16-byte alignment takes the element path
+    wide = torch.zeros((shape[0], shape[1] + 3), dtype=dtype)
+    wide[:, : shape[1]] = x
+    q2, s2 = ops.fp8_block_quantize(wide.cuda()[:, : shape[1]])
+    _same(q2, s2, q_want, s_want, f"{shape} {dtype} strided")

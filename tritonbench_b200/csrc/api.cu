@@ -610,6 +610,27 @@ int b200fp8_row_quantize(const void* x, int x_dtype, int recipe, int64_t rows, i
   return note_cuda(launch_row_quantize(p, static_cast<cudaStream_t>(cuda_stream)));
 }
 
+int b200fp8_block_quantize(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ldx, void* q, int64_t ldq,
+                           float* scale, int64_t ld_scale, void* cuda_stream) {
+  if (x == nullptr || q == nullptr || scale == nullptr) return B200FP8_BAD_ARG;
+  if (rows <= 0 || cols <= 0 || ldx < cols || ldq < cols || ld_scale < (cols + 127) / 128) return B200FP8_BAD_ARG;
+  if (rows > 0x7FFFFF00ll || cols > 0x7FFFFF00ll || (rows + 127) / 128 > 65535) return B200FP8_TOO_LARGE;
+  if (x_dtype < kQuantBf16 || x_dtype > kQuantFp32) return B200FP8_BAD_ARG;
+  const int64_t elem = x_dtype == kQuantFp32 ? 4 : 2;
+  BlockQuantParams p = {};
+  p.x = x;
+  p.q = static_cast<uint8_t*>(q);
+  p.scale = scale;
+  p.rows = rows;
+  p.cols = cols;
+  p.ldx = ldx;
+  p.ldq = ldq;
+  p.ld_scale = ld_scale;
+  p.dtype = x_dtype;
+  p.vector_ok = aligned16(x) && (ldx * elem) % 16 == 0 && (reinterpret_cast<uintptr_t>(q) & 7u) == 0 && ldq % 8 == 0;
+  return note_cuda(launch_block_quantize(p, static_cast<cudaStream_t>(cuda_stream)));
+}
+
 int b200fp8_fused_row_quantize(int producer, const void* x1, const void* x2, int64_t rows, int64_t cols, int64_t ld1,
                                int64_t ld2, float eps, int round_bf16, void* q, int64_t ldq, float* scale,
                                void* cuda_stream) {

@@ -200,6 +200,20 @@ struct QuantParams {
 
 cudaError_t launch_row_quantize(const QuantParams& p, cudaStream_t stream);
 
+// 128x128 block quantiser (quantize.cu): q [rows, cols] e4m3, scale [ceil(rows/128)][ld_scale >= ceil(cols/128)] fp32
+struct BlockQuantParams {
+  const void* x;
+  uint8_t* q;
+  float* scale;
+  long long rows, cols;
+  long long ldx;       // elements
+  long long ldq;       // bytes
+  long long ld_scale;  // elements
+  int dtype;
+  int vector_ok;  // rows of x start on 16-byte boundaries and rows of q on 8-byte boundaries
+};
+cudaError_t launch_block_quantize(const BlockQuantParams& p, cudaStream_t stream);
+
 // ------------------------ producer + quantiser in one pass (fused_quantize.cu) ------------------------
 constexpr int kProducerRmsNorm = 1;  // y = x1 * rsqrt(mean(x1^2) + eps) * x2[k]   (x2: weight vector [cols])
 constexpr int kProducerSiluMul = 2;  // y = silu(x1) * x2                          (x2: [rows, cols])

@@ -345,6 +345,96 @@ cudaError_t launch_recipe(const QuantParams& p, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+// 128x128 block quantiser (the operand format of the block-scaled GEMM): one CTA per block, one pass.
+//   blockmax = max |x| over the block (rows / columns beyond the matrix count as zeros), clamped below at T(1e-12);
+//   mult = (1 / float(blockmax)) * 448 in fp32 (1 where that is infinite);  q = e4m3(float(x) * mult): no clamp is
+//   needed, |x * mult| <= 448 (1 + 2^-23) by construction, so the saturating hardware conversion never saturates;
+//   the scale handed to the GEMM is 1 / mult.
+// Thread t owns the 8 columns [8 (t % 16), +8) of the rows t / 16 + 16 i, i = 0..7, so that a warp reads two
+// whole rows of the block (2 x 256 contiguous bytes of a 16-bit type) per instruction; interior, 16-byte aligned
+// blocks use vector accesses, edge blocks element accesses.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) block_quantize_kernel(const BlockQuantParams p) {
+  __shared__ float red[kThreads / 32];
+  const int bk = blockIdx.x, bm = blockIdx.y;
+  const int r0 = threadIdx.x >> 4;
+  const int c0 = (threadIdx.x & 15) * kVec;
+  const long long row0 = static_cast<long long>(bm) * 128 + r0;
+  const long long col = static_cast<long long>(bk) * 128 + c0;
+  const bool interior = p.vector_ok && (bm + 1) * 128ll <= p.rows && (bk + 1) * 128ll <= p.cols;
+  const T* x = static_cast<const T*>(p.x) + row0 * p.ldx + col;
+  uint8_t* q = p.q + row0 * p.ldq + col;
+
+  float v[8][8];
+  if (interior) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const Raw<T> raw = load_raw<T>(x + 16ll * i * p.ldx);
+      if constexpr (sizeof(T) == 4) {
+        const float* a = reinterpret_cast<const float*>(&raw.lo);
+        const float* b = reinterpret_cast<const float*>(&raw.hi);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[i][j] = a[j];
+          v[i][4 + j] = b[j];
+        }
+      } else {
+        const T* h = reinterpret_cast<const T*>(&raw.lo);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = Conv<T>::up(h[j]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[i][j] = (row0 + 16 * i < p.rows && col + j < p.cols) ? Conv<T>::up(x[16ll * i * p.ldx + j]) : 0.0f;
+      }
+    }
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+  }
+  amax = block_max(amax, red);
+  // torch evaluates `448 / blockmax` as reciprocal(blockmax) * 448: two roundings
+  float mult = __fmul_rn(__fdiv_rn(1.0f, fmaxf(amax, Conv<T>::rnd(1e-12f))), 448.0f);
+  if (isinf(mult)) mult = 1.0f;
+  if (threadIdx.x == 0) p.scale[static_cast<long long>(bm) * p.ld_scale + bk] = __fdiv_rn(1.0f, mult);
+
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (interior) {
+      uint32_t w[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float* a = v[i] + 4 * h;
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(a[0], mult), __fmul_rn(a[1], mult)), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(a[2], mult), __fmul_rn(a[3], mult)), __NV_SATFINITE, __NV_E4M3);
+        w[h] = lo | (hi << 16);
+      }
+      *reinterpret_cast<uint2*>(q + 16ll * i * p.ldq) = make_uint2(w[0], w[1]);
+    } else if (row0 + 16 * i < p.rows) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (col + j < p.cols) {
+          q[16ll * i * p.ldq + j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(__fmul_rn(v[i][j], mult), __NV_SATFINITE, __NV_E4M3));
+        }
+      }
+    }
+  }
+}
+
+template <typename T>
+cudaError_t launch_block_t(const BlockQuantParams& p, cudaStream_t stream) {
+  const dim3 grid(static_cast<unsigned>((p.cols + 127) / 128), static_cast<unsigned>((p.rows + 127) / 128), 1);
+  block_quantize_kernel<T><<<grid, kThreads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
 template <typename T>
 cudaError_t launch_t(const QuantParams& p, cudaStream_t stream) {
   if (p.recipe == kRecipeOperator) return launch_recipe<T, kRecipeOperator>(p, stream);
@@ -358,6 +448,15 @@ cudaError_t launch_row_quantize(const QuantParams& p, cudaStream_t stream) {
     case kQuantBf16: return launch_t<__nv_bfloat16>(p, stream);
     case kQuantFp16: return launch_t<__half>(p, stream);
     case kQuantFp32: return launch_t<float>(p, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t launch_block_quantize(const BlockQuantParams& p, cudaStream_t stream) {
+  switch (p.dtype) {
+    case kQuantBf16: return launch_block_t<__nv_bfloat16>(p, stream);
+    case kQuantFp16: return launch_block_t<__half>(p, stream);
+    case kQuantFp32: return launch_block_t<float>(p, stream);
     default: return cudaErrorInvalidValue;
   }
 }

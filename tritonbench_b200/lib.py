@@ -65,6 +65,7 @@ EXPORTED_SYMBOLS = (
     "b200fp8_noalloc_status",
     "b200fp8_row_quantize",
     "b200fp8_fused_row_quantize",
+    "b200fp8_block_quantize",
     "b200fp8_gemm_rowwise_grouped",
     "b200fp8_selftest_wait_timeout",
     "b200fp8_gemm_blockwise",
@@ -132,6 +133,9 @@ def load() -> ctypes.CDLL:
     lib.b200fp8_fused_row_quantize.restype = ctypes.c_int
     lib.b200fp8_fused_row_quantize.argtypes = [ctypes.c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                                ctypes.c_float, ctypes.c_int, c_void_p, c_int64, c_void_p, c_void_p]
+    lib.b200fp8_block_quantize.restype = ctypes.c_int
+    lib.b200fp8_block_quantize.argtypes = [c_void_p, ctypes.c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p,
+                                           c_int64, c_void_p]
     lib.b200fp8_row_quantize.restype = ctypes.c_int
     lib.b200fp8_row_quantize.argtypes = [c_void_p, ctypes.c_int, ctypes.c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p]
     if lib.b200fp8_abi_version() != 1:

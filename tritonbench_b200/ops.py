@@ -141,6 +141,27 @@ def fp8_row_quantize(x: torch.Tensor, recipe: str = "operator") -> Tuple[torch.T
     return q.view(torch.float8_e4m3fn), scale
 
 
+def fp8_block_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """CUDA 128x128 block quantiser, bit for bit the reference's `fp8_block_quantize`
+    (tritonbench/operators/fp8_gemm_blockwise/operator.py:87-120): (xq float8_e4m3fn [M, K],
+    scale float32 [ceil(M/128), ceil(K/128)] = 1 / multiplier)."""
+    _require_cuda(x, "x")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be [rows, cols] with cols contiguous")
+    dtypes = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16, torch.float32: _lib.DTYPE_FP32}
+    if x.dtype not in dtypes:
+        raise ValueError(f"unsupported dtype {x.dtype}")
+    rows, cols = x.shape
+    q = torch.empty((rows, cols), dtype=torch.uint8, device=x.device)
+    scale = torch.empty(((rows + 127) // 128, (cols + 127) // 128), dtype=torch.float32, device=x.device)
+    status = _lib.load().b200fp8_block_quantize(
+        x.data_ptr(), dtypes[x.dtype], rows, cols, x.stride(0), q.data_ptr(), q.stride(0), scale.data_ptr(),
+        scale.stride(0), torch.cuda.current_stream(x.device).cuda_stream,
+    )
+    _lib.check(status, f"b200fp8_block_quantize({rows}x{cols}, {x.dtype})")
+    return q.view(torch.float8_e4m3fn), scale
+
+
 def _fused_row_quantize(producer: int, x1: torch.Tensor, x2: torch.Tensor, eps: float, round_bf16: bool, what: str):
     _require_cuda(x1, "x1")
     _require_cuda(x2, "x2")

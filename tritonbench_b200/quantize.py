@@ -44,6 +44,10 @@ def fp8_block_quantize(x: torch.Tensor, block_m: int = 128, block_k: int = 128) 
     """Same contract as the reference's `fp8_block_quantize` (tritonbench/operators/fp8_gemm_blockwise/operator.py:87-120):
     one multiplier 448 / blockmax per block_m x block_k block (1.0 where that is infinite), no clamp before the
     e4m3 cast, returns (xq, 1 / multiplier as float32 [ceil(M/block_m), ceil(K/block_k)])."""
+    if x.is_cuda and block_m == 128 and block_k == 128:
+        from . import ops
+
+        return ops.fp8_block_quantize(x)
     m, k = x.shape
     grid_m, grid_k = -(-m // block_m), -(-k // block_k)
     padded = torch.zeros(grid_m * block_m, grid_k * block_k, dtype=x.dtype, device=x.device)
@@ -129,6 +133,7 @@ def _main() -> None:
     ap.add_argument("--cols", type=int, default=8192)
     ap.add_argument("--dtype", choices=["bf16", "fp16", "fp32"], default="bf16")
     ap.add_argument("--producer", choices=["none", "rms_norm", "silu_mul"], default="none")
+    ap.add_argument("--block", action="store_true", help="time the 128x128 block quantiser instead of the rowwise one")
     ap.add_argument("--round-bf16", action="store_true", help="producers: round the activation to bf16 before quantising")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -147,6 +152,8 @@ def _main() -> None:
         x2 = torch.randn((args.rows, args.cols), device="cuda", dtype=dt)
         in_bytes *= 2
         fn = lambda: ops.silu_mul_fp8_rowwise_quant(x, x2, round_bf16=args.round_bf16)  # noqa: E731
+    elif args.block:
+        fn = lambda: ops.fp8_block_quantize(x)  # noqa: E731
     else:
         fn = lambda: ops.fp8_row_quantize(x)  # noqa: E731
     for _ in range(args.warmup):
@@ -160,7 +167,7 @@ def _main() -> None:
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) / args.iters * 1e3
     nbytes = args.rows * args.cols * (in_bytes + 1) + 4 * args.rows
-    what = "row_quantize" if args.producer == "none" else f"{args.producer} + row_quantize"
+    what = ("block_quantize" if args.block else "row_quantize") if args.producer == "none" else f"{args.producer} + row_quantize"
     print(f"{what} {args.rows}x{args.cols} {args.dtype if args.producer == 'none' else 'bf16'}: "
           f"{us:.1f} us per call, {nbytes / us / 1e3:.0f} GB/s")
 
