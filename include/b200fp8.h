@@ -227,8 +227,11 @@ int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char*
 /*
  * Host-buffer form, the call a host program without its own device memory makes:
  * inputs and output live in host memory (pinned for full PCIe speed), device staging
- * buffers belong to the context.  One call = copy in, GEMM, copy out, synchronise.  Problems of 2048 rows or
- * more are pipelined in 1024-row panels over three streams, so both PCIe directions and the GPU work at once.
+ * buffers belong to the context.  One call = copy in, GEMM, copy out, synchronise; the context's device is
+ * made current for the duration of the call.  Larger problems are cut into panels of 1024 rows of X and 2048
+ * rows of W that go up alternately; each block of Y is multiplied and sent down (a pitched copy into the host
+ * array) as soon as its two panels are on the device, so both PCIe directions and the GPU work at once.
+ * Whatever the call returns, no copy is in flight on the caller's buffers when it returns.
  * Replaces: `input_cast(.to(device))` + backend call + result read in
  * tritonbench/utils/triton_op.py:846-850,1221-1232.
  */
@@ -237,6 +240,21 @@ int b200fp8_host_ctx_create(int64_t M, int64_t N, int64_t K, uint32_t flags, b20
 int b200fp8_host_ctx_destroy(b200fp8_host_ctx* ctx);
 int b200fp8_gemm_rowwise_host(b200fp8_host_ctx* ctx, const void* xq, const void* wq, const float* x_scale,
                               const float* w_scale, const void* bias_bf16, void* y_bf16);
+/*
+ * Serving form.  The context keeps the W, w_scale and bias of the last upload on the device: an upload is this
+ * call, or any b200fp8_gemm_rowwise_host call that passed wq.  A b200fp8_gemm_rowwise_host call with wq == NULL
+ * reuses them (its w_scale and bias_bf16 arguments are ignored; BAD_ARG if nothing was uploaded yet): only X and
+ * x_scale go up, and Y comes down in whole row panels.  set_weights(ctx, NULL, NULL, NULL) forgets the weights.
+ * Synchronous.  Replaces: the reference keeps `wq` on the device across the timed calls of one input
+ * (tritonbench/utils/triton_op.py:846-850 casts the inputs once, 1221-1232 times the call).
+ */
+int b200fp8_host_ctx_set_weights(b200fp8_host_ctx* ctx, const void* wq, const float* w_scale, const void* bias_bf16);
+/*
+ * Tuning knob: panel sizes of the pipeline above (rows of X per panel, rows of W = columns of Y per panel).
+ * A panel smaller than its dimension must be a multiple of 128 rows / 256 columns; at most 64 panels per
+ * dimension and 1024 blocks.  Any setting gives the same Y.  Replaces: nothing in the reference.
+ */
+int b200fp8_host_ctx_set_panels(b200fp8_host_ctx* ctx, int64_t panel_rows, int64_t panel_cols);
 
 #ifdef __cplusplus
 }

@@ -12,6 +12,7 @@ What it pins
     FBGEMM is faked, and the stock backends stay disabled.
   * block quantiser: the sibling operator's `fp8_block_quantize`
     (tritonbench/operators/fp8_gemm_blockwise/operator.py:87-120), imported and run the same way.
+  * non-finite inputs: both quantisers on rows / blocks that hold a NaN or an infinity.
   * GEMM: the reference has no runnable implementation and no test vectors for the GEMM itself
     (its kernels live in FBGEMM), so the stored Y is the fp32 dequantise-then-matmul result computed
     with plain torch CPU ops here, written out independently of oracle/ (no import of it).
@@ -132,6 +133,27 @@ def main():
     xb[3, 5] = 1000.0
     qb, sb = blockwise.fp8_block_quantize(xb)
     np.savez_compressed(os.path.join(HERE, "ref_block_quantizer_200x300.npz"), x_bf16=bf16_bits(xb), q=u8(qb), scale=sb.numpy())
+
+    # (7) rows (and blocks) that hold a NaN or an infinity, through the same two reference functions: torch's max,
+    #     amax and clamp propagate NaN, so one NaN turns the whole row's (block's) scale and codes into NaN;
+    #     an infinity gives a zero multiplier, zero codes for the finite elements and NaN for the infinite one
+    nf = torch.randn((6, 64), generator=torch.Generator().manual_seed(11))
+    nf[1, 5] = float("nan")
+    nf[2, 7] = float("inf")
+    nf[3, 1] = float("-inf")
+    nf[3, 2] = float("nan")
+    nf[5] = 0.0
+    nonfinite = {}
+    for name, dt in (("bf16", torch.bfloat16), ("fp16", torch.float16), ("fp32", torch.float32)):
+        q, s = quantize(nf.to(dt))
+        nonfinite[f"q_{name}"] = u8(q)
+        nonfinite[f"s_{name}"] = s.numpy()
+    xb = torch.randn((130, 260), generator=torch.Generator().manual_seed(12)).to(torch.bfloat16)
+    xb[5, 7] = float("nan")       # block (0, 0)
+    xb[129, 200] = float("inf")   # block (1, 1)
+    qb, sb = blockwise.fp8_block_quantize(xb)
+    np.savez_compressed(os.path.join(HERE, "ref_quantizer_nonfinite.npz"), rows=nf.numpy(), **nonfinite,
+                        block_x_bf16=bf16_bits(xb), block_q=u8(qb), block_scale=sb.numpy())
 
     # (5) all 256 e4m3 byte patterns as torch decodes them
     allb = torch.arange(256, dtype=torch.uint8)

@@ -120,3 +120,6 @@ def test_one_tile_per_cluster_plans_are_well_formed_for_any_shape(cdll):
         assert 1 <= stages <= 14 and stages * (x_rows + bn) * 128 <= 192 * 1024, plan
         assert ctas == ((m + 127) // 128) * ((n + bn - 1) // bn) * s and waves >= 1, plan
         assert smem <= 227 * 1024, plan
+        # tensor memory: the CTAs one SM can hold by shared memory never need more than its 512 columns
+        tmem_cols = 32 if bn <= 32 else 64 if bn <= 64 else 128 if bn <= 128 else 256
+        assert (227 * 1024 // smem) * tmem_cols <= 512, plan

@@ -72,6 +72,30 @@ def test_quantizer_restatement_matches_reference_on_edge_rows(golden_dir, name, 
     assert np.array_equal(s.numpy(), d[f"s_{name}"], equal_nan=True)
 
 
+def _canon_nan_codes(q):
+    """e4m3 codes with both NaN patterns (0x7F, 0xFF) mapped to 0x7F: the sign of a NaN is not part of the contract."""
+    q = np.asarray(q, dtype=np.uint8)
+    return np.where((q & 0x7F) == 0x7F, np.uint8(0x7F), q)
+
+
+@pytest.mark.parametrize("name,dtype", [("bf16", torch.bfloat16), ("fp16", torch.float16), ("fp32", torch.float32)])
+def test_quantizer_restatement_matches_reference_on_rows_with_nan_and_infinity(golden_dir, name, dtype):
+    """A NaN makes its whole row NaN (scale and codes); an infinity gives scale inf, zero codes and one NaN."""
+    d = _load(golden_dir, "ref_quantizer_nonfinite.npz")
+    q, s = orc.row_quantize_reference(torch.from_numpy(d["rows"]).to(dtype))
+    assert np.array_equal(_canon_nan_codes(q.view(torch.uint8).numpy()), _canon_nan_codes(d[f"q_{name}"]))
+    assert np.array_equal(s.numpy(), d[f"s_{name}"], equal_nan=True)
+    assert np.isnan(d[f"s_{name}"][[1, 3]]).all() and np.isinf(d[f"s_{name}"][2])
+    assert (_canon_nan_codes(d[f"q_{name}"][1]) == 0x7F).all()
+
+
+def test_block_quantizer_restatement_matches_reference_on_blocks_with_nan_and_infinity(golden_dir):
+    d = _load(golden_dir, "ref_quantizer_nonfinite.npz")
+    q, s = orc.block_quantize_reference(_bf16(d["block_x_bf16"]))
+    assert np.array_equal(_canon_nan_codes(q.view(torch.uint8).numpy()), _canon_nan_codes(d["block_q"]))
+    assert np.array_equal(s.numpy(), d["block_scale"], equal_nan=True)
+
+
 def test_gemm_oracle_matches_golden_outputs_bit_for_bit(golden_dir):
     for f in ("config1_seed0_128x256x512.npz", "ref_quantizer_bf16_128x256x512.npz"):
         d = _load(golden_dir, f)

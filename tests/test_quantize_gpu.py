@@ -40,6 +40,44 @@ def test_edge_rows_match_reference_fixture(cuda_device, golden_dir, name, dtype)
     assert np.array_equal(s.cpu().numpy(), d[f"s_{name}"], equal_nan=True)
 
 
+def _canon_nan_codes(q):
+    """e4m3 codes with both NaN patterns (0x7F, 0xFF) mapped to 0x7F: the sign of a NaN is not part of the contract."""
+    q = np.asarray(q, dtype=np.uint8)
+    return np.where((q & 0x7F) == 0x7F, np.uint8(0x7F), q)
+
+
+@pytest.mark.parametrize("name,dtype", [("bf16", torch.bfloat16), ("fp16", torch.float16), ("fp32", torch.float32)])
+def test_rows_with_nan_and_infinity_match_reference_fixture(cuda_device, golden_dir, name, dtype):
+    """torch's max / clamp propagate NaN: one NaN makes the row's scale and all of its codes NaN; an infinity gives an
+    infinite scale, zero codes and a NaN where the infinity was.  Fixture made by the reference's own function."""
+    from tritonbench_b200 import ops
+
+    d = np.load(os.path.join(golden_dir, "ref_quantizer_nonfinite.npz"))
+    q, s = ops.fp8_row_quantize(torch.from_numpy(d["rows"]).to(dtype).cuda())
+    assert np.array_equal(_canon_nan_codes(q.view(torch.uint8).cpu().numpy()), _canon_nan_codes(d[f"q_{name}"]))
+    assert np.array_equal(s.cpu().numpy(), d[f"s_{name}"], equal_nan=True)
+    qb, sb = ops.fp8_block_quantize(_bf16(d["block_x_bf16"]).cuda())
+    assert np.array_equal(_canon_nan_codes(qb.view(torch.uint8).cpu().numpy()), _canon_nan_codes(d["block_q"]))
+    assert np.array_equal(sb.cpu().numpy(), d["block_scale"], equal_nan=True)
+
+
+@pytest.mark.parametrize("shape", [(200, 2048), (300, 4096), (5, 16384), (3, 40000), (9, 1001)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_nan_and_infinity_in_every_kernel_form(cuda_device, shape, dtype):
+    """The same rule in the warp-per-row, persistent and CTA-per-row kernels (and their tails), against the oracle."""
+    from tritonbench_b200 import ops
+
+    g = torch.Generator().manual_seed(shape[1])
+    x = torch.randn(shape, generator=g).to(dtype)
+    x[0, shape[1] - 1] = float("nan")
+    x[1, shape[1] // 2] = float("inf")
+    x[2, 0] = float("-inf")
+    q_want, s_want = orc.row_quantize_reference(x)
+    q, s = ops.fp8_row_quantize(x.cuda())
+    assert np.array_equal(_canon_nan_codes(q.view(torch.uint8).cpu().numpy()), _canon_nan_codes(q_want.view(torch.uint8).numpy()))
+    assert np.array_equal(s.cpu().numpy(), s_want.numpy(), equal_nan=True)
+
+
 # the last eight sit on either side of the boundaries between the three kernels (one warp per row up to 2560 elements and
 # from 64 rows, persistent up to 8192, one CTA per row beyond) and make a persistent CTA walk over many rows
 @pytest.mark.parametrize("shape", [(1, 16), (3, 7), (17, 130), (64, 8192), (5, 16384), (2, 40000), (300, 1000), (1024, 4096),

@@ -204,6 +204,13 @@ SplitPlan make_split_plan(long long M, long long N, long long K, const int* resi
   best.ring_bytes = (ring + 1023) / 1024 * 1024;
   best.staged_stores = M > 64 ? 1 : 0;  // short outputs leave in 16-byte stores straight from registers
   best.smem_bytes = best.ring_bytes + (best.staged_stores ? 32 * 1024 : 0) + 1024 + 256 + 1024;
+  // Tensor memory: an SM has 512 columns and this kernel's CTAs take tmem_cols each with a tcgen05.alloc that
+  // blocks until the columns are free.  CTAs that block there while their cluster peers wait at a cluster
+  // barrier would never be released, so no more CTAs may be resident on an SM than its tensor memory holds.
+  // Shared memory is the limit the launch controls: ask for enough of it that floor(227 KiB / smem_bytes)
+  // CTAs need at most 512 columns (76 KiB for 256 columns: two CTAs; 46 KiB for 128: four; ...).
+  const int min_smem = SplitGeometry::min_smem_bytes_for_tmem(split_tmem_cols(best.block_n));
+  if (best.smem_bytes < min_smem) best.smem_bytes = min_smem;
   best.tiles = static_cast<int>(tiles_m * ((N + best.block_n - 1) / best.block_n));
   return best;
 }
@@ -722,36 +729,116 @@ int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char*
 }
 
 // ------------------------------------ host-buffer context ------------------------------------
-// One call = copy in, GEMM, copy out.  The copies are what the call costs (PCIe), so large problems are
-// cut into row panels that flow through three streams: panel i+1 of X goes up while panel i is multiplied
-// and panel i-1 of Y comes down; both PCIe directions are busy at once.  W and the scales go first.
+// One call = copy in, GEMM, copy out.  The copies are what the call costs (PCIe), so the problem is cut into
+// panels that flow through three streams - uploads, GEMMs, downloads - with both PCIe directions busy at once.
+//
+// A block Y[i][j] (panel i of the rows, panel j of the columns) needs panel i of X and panel j of W.  When W comes
+// from the host with every call, sending all of W before the first X panel would keep the download direction idle
+// for the first third of the call; instead X panels and W panels go up alternately and every block is multiplied
+// and sent down as soon as both of its panels are there, so the blocks ready for download grow with the square of
+// the bytes uploaded.  Blocks of Y are then sub-matrices of the host array (a pitched copy).  When W stays on the
+// device (b200fp8_host_ctx_set_weights) only X goes up and Y comes down in whole row panels (contiguous copies).
 namespace {
-constexpr int kMaxPanels = 64;
+constexpr int kMaxPanels = 64;       // per dimension
+constexpr int kMaxBlocks = 1024;     // blocks of Y per call
 constexpr int64_t kPanelRows = 1024;
+constexpr int64_t kPanelCols = 2048;
+
+struct HostStep {
+  int kind;  // 0: upload X panel a; 1: upload W panel a; 2: multiply and download block (a, b)
+  int a, b;
+};
 }  // namespace
 
 struct b200fp8_host_ctx {
+  int device;
   int64_t M, N, K;
   uint32_t flags;
-  int panels;
-  int64_t panel_rows;
+  int64_t panel_rows, panel_cols;  // as configured; W resident: whole rows of Y (one column panel)
   cudaStream_t s_in, s_compute, s_out;
-  cudaEvent_t ev_w, ev_start;
   cudaEvent_t ev_x[kMaxPanels];
-  cudaEvent_t ev_y[kMaxPanels];
+  cudaEvent_t ev_w[kMaxPanels];
+  cudaEvent_t ev_y[kMaxBlocks];
+  cudaEvent_t ev_done;
   uint8_t* d_x;
   uint8_t* d_w;
   float* d_xs;
   float* d_ws;
   __nv_bfloat16* d_bias;
   __nv_bfloat16* d_y;
-  uint8_t* d_workspace;       // one workspace per panel (panels in flight must not share one)
-  size_t workspace_bytes;     // per panel
-  uint32_t* h_status;         // pinned, one word per panel
+  uint8_t* d_workspace;    // one workspace per block in flight when the plan needs more than the status word
+  size_t workspace_bytes;  // per block
+  size_t workspace_total;
+  uint32_t* h_status;      // pinned, one word per block
+  bool weights_resident;
+  bool bias_resident;
 };
+
+namespace {
+
+struct DeviceGuard {  // the context's device is current inside the call, the caller's afterwards
+  int previous = -1;
+  cudaError_t enter(int device) {
+    cudaError_t e = cudaGetDevice(&previous);
+    if (e != cudaSuccess) return e;
+    return previous == device ? cudaSuccess : cudaSetDevice(device);
+  }
+  ~DeviceGuard() {
+    int now = -1;
+    if (previous >= 0 && cudaGetDevice(&now) == cudaSuccess && now != previous) cudaSetDevice(previous);
+  }
+};
+
+int panels_of(int64_t extent, int64_t panel) { return static_cast<int>((extent + panel - 1) / panel); }
+
+// Largest workspace any block of the context's panel grid needs (interior, last row, last column, corner).
+size_t block_workspace_bytes(const b200fp8_host_ctx* c, int64_t panel_rows, int64_t panel_cols) {
+  const int64_t last_rows = c->M - (panels_of(c->M, panel_rows) - 1) * panel_rows;
+  const int64_t last_cols = c->N - (panels_of(c->N, panel_cols) - 1) * panel_cols;
+  size_t need = 0;
+  const int64_t rows[2] = {panel_rows < c->M ? panel_rows : c->M, last_rows};
+  const int64_t cols[2] = {panel_cols < c->N ? panel_cols : c->N, last_cols};
+  for (int i = 0; i < 2; ++i) {
+    for (int j = 0; j < 2; ++j) {
+      const size_t b = b200fp8_workspace_bytes(rows[i], cols[j], c->K, c->flags);
+      if (b == 0) return 0;
+      if (b > need) need = b;
+    }
+  }
+  return (need + 255) / 256 * 256;
+}
+
+// Upload order: always the operand of which the smaller fraction is on the device (X on a tie); after each
+// upload, every block that has just become computable.
+int build_schedule(int pm, int pn, bool weights_resident, HostStep* steps) {
+  int n = 0, up_x = 0, up_w = weights_resident ? pn : 0;
+  while (up_x < pm || up_w < pn) {
+    const bool send_x = up_w >= pn || (up_x < pm && up_x * pn <= up_w * pm);
+    if (send_x) {
+      steps[n++] = {0, up_x, 0};
+      for (int j = 0; j < up_w; ++j) steps[n++] = {2, up_x, j};
+      ++up_x;
+    } else {
+      steps[n++] = {1, up_w, 0};
+      for (int i = 0; i < up_x; ++i) steps[n++] = {2, i, up_w};
+      ++up_w;
+    }
+  }
+  return n;
+}
+
+void sync_all(b200fp8_host_ctx* c) {
+  cudaStreamSynchronize(c->s_in);
+  cudaStreamSynchronize(c->s_compute);
+  cudaStreamSynchronize(c->s_out);
+}
+
+}  // namespace
 
 int b200fp8_host_ctx_destroy(b200fp8_host_ctx* c) {
   if (c == nullptr) return B200FP8_OK;
+  DeviceGuard guard;
+  guard.enter(c->device);
   if (c->s_in) cudaStreamSynchronize(c->s_in);
   if (c->s_compute) cudaStreamSynchronize(c->s_compute);
   if (c->s_out) cudaStreamSynchronize(c->s_out);
@@ -763,16 +850,54 @@ int b200fp8_host_ctx_destroy(b200fp8_host_ctx* c) {
   cudaFree(c->d_y);
   cudaFree(c->d_workspace);
   if (c->h_status) cudaFreeHost(c->h_status);
-  if (c->ev_w) cudaEventDestroy(c->ev_w);
-  if (c->ev_start) cudaEventDestroy(c->ev_start);
+  if (c->ev_done) cudaEventDestroy(c->ev_done);
   for (int i = 0; i < kMaxPanels; ++i) {
     if (c->ev_x[i]) cudaEventDestroy(c->ev_x[i]);
+    if (c->ev_w[i]) cudaEventDestroy(c->ev_w[i]);
+  }
+  for (int i = 0; i < kMaxBlocks; ++i) {
     if (c->ev_y[i]) cudaEventDestroy(c->ev_y[i]);
   }
   if (c->s_in) cudaStreamDestroy(c->s_in);
   if (c->s_compute) cudaStreamDestroy(c->s_compute);
   if (c->s_out) cudaStreamDestroy(c->s_out);
   delete c;
+  return B200FP8_OK;
+}
+
+int b200fp8_host_ctx_set_panels(b200fp8_host_ctx* c, int64_t panel_rows, int64_t panel_cols) {
+  if (c == nullptr || panel_rows <= 0 || panel_cols <= 0) return B200FP8_BAD_ARG;
+  if (panel_rows > c->M) panel_rows = c->M;
+  if (panel_cols > c->N) panel_cols = c->N;
+  // interior panels must keep every block's pointers aligned for TMA: whole 128-row / 256-column tiles
+  if (panel_rows < c->M && panel_rows % 128 != 0) return B200FP8_BAD_ARG;
+  if (panel_cols < c->N && panel_cols % 256 != 0) return B200FP8_BAD_ARG;
+  const int pm = panels_of(c->M, panel_rows), pn = panels_of(c->N, panel_cols);
+  if (pm > kMaxPanels || pn > kMaxPanels || pm * pn > kMaxBlocks) return B200FP8_TOO_LARGE;
+  DeviceGuard guard;
+  cudaError_t e = guard.enter(c->device);
+  if (e != cudaSuccess) return note_cuda(e);
+  const size_t per_block = block_workspace_bytes(c, panel_rows, panel_cols);
+  const size_t per_row_panel = block_workspace_bytes(c, panel_rows, c->N);  // the grid used while W is resident
+  if (per_block == 0 || per_row_panel == 0) return B200FP8_BAD_ARG;
+  const size_t per = per_block > per_row_panel ? per_block : per_row_panel;
+  // kernels that need only the status word share one workspace; the others get one per block
+  const size_t total = per == B200FP8_WORKSPACE_HEADER_BYTES ? per : per * static_cast<size_t>(pm) * pn;
+  if (total > c->workspace_total) {
+    sync_all(c);
+    cudaFree(c->d_workspace);
+    c->d_workspace = nullptr;
+    c->workspace_total = 0;
+    e = cudaMalloc(&c->d_workspace, total);
+    if (e != cudaSuccess) return note_cuda(e);
+    c->workspace_total = total;
+    e = cudaMemsetAsync(c->d_workspace, 0, total, c->s_compute);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->s_compute);
+    if (e != cudaSuccess) return note_cuda(e);
+  }
+  c->workspace_bytes = per;
+  c->panel_rows = panel_rows;
+  c->panel_cols = panel_cols;
   return B200FP8_OK;
 }
 
@@ -792,24 +917,14 @@ int b200fp8_host_ctx_create(int64_t M, int64_t N, int64_t K, uint32_t flags, b20
   c->N = N;
   c->K = K;
   c->flags = flags;
-  // panels of 1024 rows once there are at least two of them; at most kMaxPanels
-  c->panel_rows = M >= 2 * kPanelRows ? kPanelRows : M;
-  while ((M + c->panel_rows - 1) / c->panel_rows > kMaxPanels) c->panel_rows *= 2;
-  c->panels = static_cast<int>((M + c->panel_rows - 1) / c->panel_rows);
-  const int64_t last_rows = M - (c->panels - 1) * c->panel_rows;
-  const size_t ws_a = b200fp8_workspace_bytes(c->panel_rows, N, K, flags);
-  const size_t ws_b = b200fp8_workspace_bytes(last_rows, N, K, flags);
-  c->workspace_bytes = (((ws_a > ws_b ? ws_a : ws_b) + 255) / 256) * 256;
-  cudaError_t e = cudaSuccess;
-  if (ws_a == 0 || ws_b == 0) e = cudaErrorInvalidValue;
+  cudaError_t e = cudaGetDevice(&c->device);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_compute, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking);
-  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_w, cudaEventDisableTiming);
-  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_start, cudaEventDisableTiming);
-  for (int i = 0; i < c->panels && e == cudaSuccess; ++i) {
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_done, cudaEventDisableTiming);
+  for (int i = 0; i < kMaxPanels && e == cudaSuccess; ++i) {
     e = cudaEventCreateWithFlags(&c->ev_x[i], cudaEventDisableTiming);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_y[i], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_w[i], cudaEventDisableTiming);
   }
   if (e == cudaSuccess) e = cudaMalloc(&c->d_x, static_cast<size_t>(M) * K);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_w, static_cast<size_t>(N) * K);
@@ -817,68 +932,161 @@ int b200fp8_host_ctx_create(int64_t M, int64_t N, int64_t K, uint32_t flags, b20
   if (e == cudaSuccess) e = cudaMalloc(&c->d_ws, static_cast<size_t>(N) * sizeof(float));
   if (e == cudaSuccess) e = cudaMalloc(&c->d_bias, static_cast<size_t>(N) * sizeof(__nv_bfloat16));
   if (e == cudaSuccess) e = cudaMalloc(&c->d_y, static_cast<size_t>(M) * N * sizeof(__nv_bfloat16));
-  if (e == cudaSuccess) e = cudaMalloc(&c->d_workspace, c->workspace_bytes * c->panels);
-  if (e == cudaSuccess) e = cudaMallocHost(&c->h_status, sizeof(uint32_t) * kMaxPanels);
-  if (e == cudaSuccess) e = cudaMemsetAsync(c->d_workspace, 0, c->workspace_bytes * c->panels, c->s_compute);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(c->s_compute);
+  if (e == cudaSuccess) e = cudaMallocHost(&c->h_status, sizeof(uint32_t) * kMaxBlocks);
   if (e != cudaSuccess) {
     b200fp8_host_ctx_destroy(c);
     return note_cuda(e);
+  }
+  // Panels once a dimension holds at least two of them; one panel otherwise.  Small problems (a few MB in
+  // all) are not worth cutting: a panel's copy should last much longer than the ~10 us a copy costs to start.
+  int64_t rows = M >= 2 * kPanelRows ? kPanelRows : M;
+  int64_t cols = N >= 2 * kPanelCols ? kPanelCols : N;
+  if (static_cast<double>(M + N) * static_cast<double>(K) < 8.0e6) {
+    rows = M;
+    cols = N;
+  }
+  while (panels_of(M, rows) > 16) rows *= 2;
+  while (panels_of(N, cols) > 16) cols *= 2;
+  st = b200fp8_host_ctx_set_panels(c, rows, cols);
+  if (st != B200FP8_OK) {
+    b200fp8_host_ctx_destroy(c);
+    return st;
   }
   *out = c;
   return B200FP8_OK;
 }
 
-int b200fp8_gemm_rowwise_host(b200fp8_host_ctx* c, const void* xq, const void* wq, const float* x_scale,
-                              const float* w_scale, const void* bias_bf16, void* y_bf16) {
-  if (c == nullptr || xq == nullptr || wq == nullptr || x_scale == nullptr || w_scale == nullptr ||
-      y_bf16 == nullptr) {
-    return B200FP8_BAD_ARG;
+int b200fp8_host_ctx_set_weights(b200fp8_host_ctx* c, const void* wq, const float* w_scale, const void* bias_bf16) {
+  if (c == nullptr) return B200FP8_BAD_ARG;
+  DeviceGuard guard;
+  cudaError_t e = guard.enter(c->device);
+  if (e != cudaSuccess) return note_cuda(e);
+  if (wq == nullptr) {  // forget the resident copy: later calls take W from the host again
+    c->weights_resident = false;
+    c->bias_resident = false;
+    return B200FP8_OK;
   }
-  const size_t M = static_cast<size_t>(c->M), N = static_cast<size_t>(c->N), K = static_cast<size_t>(c->K);
-  // weights, scales and bias first
-  cudaError_t e = cudaMemcpyAsync(c->d_w, wq, N * K, cudaMemcpyHostToDevice, c->s_in);
+  if (w_scale == nullptr) return B200FP8_BAD_ARG;
+  const size_t N = static_cast<size_t>(c->N), K = static_cast<size_t>(c->K);
+  e = cudaMemcpyAsync(c->d_w, wq, N * K, cudaMemcpyHostToDevice, c->s_in);
   if (e == cudaSuccess) e = cudaMemcpyAsync(c->d_ws, w_scale, N * sizeof(float), cudaMemcpyHostToDevice, c->s_in);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(c->d_xs, x_scale, M * sizeof(float), cudaMemcpyHostToDevice, c->s_in);
   if (e == cudaSuccess && bias_bf16 != nullptr) {
     e = cudaMemcpyAsync(c->d_bias, bias_bf16, N * sizeof(__nv_bfloat16), cudaMemcpyHostToDevice, c->s_in);
   }
-  if (e == cudaSuccess) e = cudaEventRecord(c->ev_w, c->s_in);
-  if (e == cudaSuccess) e = cudaStreamWaitEvent(c->s_compute, c->ev_w, 0);
+  const cudaError_t e2 = cudaStreamSynchronize(c->s_in);
+  if (e == cudaSuccess) e = e2;
+  if (e != cudaSuccess) return note_cuda(e);
+  c->weights_resident = true;
+  c->bias_resident = bias_bf16 != nullptr;
+  return B200FP8_OK;
+}
+
+int b200fp8_gemm_rowwise_host(b200fp8_host_ctx* c, const void* xq, const void* wq, const float* x_scale,
+                              const float* w_scale, const void* bias_bf16, void* y_bf16) {
+  if (c == nullptr || xq == nullptr || x_scale == nullptr || y_bf16 == nullptr) return B200FP8_BAD_ARG;
+  const bool resident = wq == nullptr;  // reuse the W, w_scale and bias of the last upload
+  if (resident ? !c->weights_resident : w_scale == nullptr) return B200FP8_BAD_ARG;
+  DeviceGuard guard;
+  cudaError_t e = guard.enter(c->device);
   if (e != cudaSuccess) return note_cuda(e);
 
-  const uint8_t* x_host = static_cast<const uint8_t*>(xq);
-  __nv_bfloat16* y_host = static_cast<__nv_bfloat16*>(y_bf16);
-  for (int i = 0; i < c->panels; ++i) {
-    const size_t r0 = static_cast<size_t>(i) * c->panel_rows;
-    const size_t rows = (r0 + c->panel_rows <= M) ? static_cast<size_t>(c->panel_rows) : M - r0;
-    e = cudaMemcpyAsync(c->d_x + r0 * K, x_host + r0 * K, rows * K, cudaMemcpyHostToDevice, c->s_in);
-    if (e == cudaSuccess) e = cudaEventRecord(c->ev_x[i], c->s_in);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->s_compute, c->ev_x[i], 0);
-    if (e != cudaSuccess) return note_cuda(e);
-    uint8_t* ws = c->d_workspace + static_cast<size_t>(i) * c->workspace_bytes;
-    const int st = b200fp8_gemm_rowwise(c->d_x + r0 * K, c->d_w, c->d_xs + r0, c->d_ws,
-                                        bias_bf16 != nullptr ? c->d_bias : nullptr, c->d_y + r0 * N,
-                                        static_cast<int64_t>(rows), c->N, c->K, c->K, c->K, c->N, ws,
-                                        c->workspace_bytes, c->flags, c->s_compute);
-    if (st != B200FP8_OK) return st;
-    e = cudaEventRecord(c->ev_y[i], c->s_compute);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->s_out, c->ev_y[i], 0);
-    if (e == cudaSuccess) {
-      e = cudaMemcpyAsync(y_host + r0 * N, c->d_y + r0 * N, rows * N * sizeof(__nv_bfloat16), cudaMemcpyDeviceToHost,
-                          c->s_out);
+  const size_t M = static_cast<size_t>(c->M), N = static_cast<size_t>(c->N), K = static_cast<size_t>(c->K);
+  const int64_t panel_rows = c->panel_rows;
+  const int64_t panel_cols = resident ? c->N : c->panel_cols;
+  const int pm = panels_of(c->M, panel_rows), pn = panels_of(c->N, panel_cols);
+  const bool shared_workspace = c->workspace_bytes == B200FP8_WORKSPACE_HEADER_BYTES;
+  const bool use_bias = resident ? c->bias_resident : bias_bf16 != nullptr;
+  HostStep steps[2 * kMaxPanels + kMaxBlocks];
+  const int num_steps = build_schedule(pm, pn, resident, steps);
+
+  // the scales and the bias are a few KB: all of them first
+  e = cudaMemcpyAsync(c->d_xs, x_scale, M * sizeof(float), cudaMemcpyHostToDevice, c->s_in);
+  if (!resident) {
+    if (e == cudaSuccess) e = cudaMemcpyAsync(c->d_ws, w_scale, N * sizeof(float), cudaMemcpyHostToDevice, c->s_in);
+    if (e == cudaSuccess && bias_bf16 != nullptr) {
+      e = cudaMemcpyAsync(c->d_bias, bias_bf16, N * sizeof(__nv_bfloat16), cudaMemcpyHostToDevice, c->s_in);
     }
-    if (e == cudaSuccess) {
-      e = cudaMemcpyAsync(c->h_status + i, ws, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->s_out);
-    }
-    if (e != cudaSuccess) return note_cuda(e);
   }
-  e = cudaStreamSynchronize(c->s_out);
-  // the next call must not overwrite d_w / d_x while this call's kernels could still read them: they cannot,
-  // every kernel has completed before its panel's copy-out, and the last copy-out has completed here
+  if (!resident) c->weights_resident = false;  // until this call's upload has completed
+  const uint8_t* x_host = static_cast<const uint8_t*>(xq);
+  const uint8_t* w_host = static_cast<const uint8_t*>(wq);
+  __nv_bfloat16* y_host = static_cast<__nv_bfloat16*>(y_bf16);
+  int status = B200FP8_OK;
+  int blocks = 0;
+  for (int s = 0; s < num_steps && e == cudaSuccess && status == B200FP8_OK; ++s) {
+    const HostStep& step = steps[s];
+    if (step.kind == 0) {
+      const size_t r0 = static_cast<size_t>(step.a) * panel_rows;
+      const size_t rows = r0 + panel_rows <= M ? static_cast<size_t>(panel_rows) : M - r0;
+      e = cudaMemcpyAsync(c->d_x + r0 * K, x_host + r0 * K, rows * K, cudaMemcpyHostToDevice, c->s_in);
+      if (e == cudaSuccess) e = cudaEventRecord(c->ev_x[step.a], c->s_in);
+      continue;
+    }
+    if (step.kind == 1) {
+      const size_t c0 = static_cast<size_t>(step.a) * panel_cols;
+      const size_t cols = c0 + panel_cols <= N ? static_cast<size_t>(panel_cols) : N - c0;
+      e = cudaMemcpyAsync(c->d_w + c0 * K, w_host + c0 * K, cols * K, cudaMemcpyHostToDevice, c->s_in);
+      if (e == cudaSuccess) e = cudaEventRecord(c->ev_w[step.a], c->s_in);
+      continue;
+    }
+    const size_t r0 = static_cast<size_t>(step.a) * panel_rows, c0 = static_cast<size_t>(step.b) * panel_cols;
+    const size_t rows = r0 + panel_rows <= M ? static_cast<size_t>(panel_rows) : M - r0;
+    const size_t cols = c0 + panel_cols <= N ? static_cast<size_t>(panel_cols) : N - c0;
+    // the GEMM stream waits for the block's two panels (the scales went up before either)
+    e = cudaStreamWaitEvent(c->s_compute, c->ev_x[step.a], 0);
+    if (e == cudaSuccess && !resident) e = cudaStreamWaitEvent(c->s_compute, c->ev_w[step.b], 0);
+    if (e != cudaSuccess) break;
+    uint8_t* ws = c->d_workspace + (shared_workspace ? 0 : static_cast<size_t>(blocks) * c->workspace_bytes);
+    status = b200fp8_gemm_rowwise(c->d_x + r0 * K, c->d_w + c0 * K, c->d_xs + r0, c->d_ws + c0,
+                                  use_bias ? c->d_bias + c0 : nullptr, c->d_y + r0 * N + c0,
+                                  static_cast<int64_t>(rows), static_cast<int64_t>(cols), c->K, c->K, c->K, c->N, ws,
+                                  c->workspace_bytes, c->flags, c->s_compute);
+    if (status != B200FP8_OK) break;
+    if (c->ev_y[blocks] == nullptr) e = cudaEventCreateWithFlags(&c->ev_y[blocks], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventRecord(c->ev_y[blocks], c->s_compute);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->s_out, c->ev_y[blocks], 0);
+    if (e == cudaSuccess) {
+      if (cols == N) {
+        e = cudaMemcpyAsync(y_host + r0 * N, c->d_y + r0 * N, rows * N * sizeof(__nv_bfloat16), cudaMemcpyDeviceToHost,
+                            c->s_out);
+      } else {
+        e = cudaMemcpy2DAsync(y_host + r0 * N + c0, N * sizeof(__nv_bfloat16), c->d_y + r0 * N + c0,
+                              N * sizeof(__nv_bfloat16), cols * sizeof(__nv_bfloat16), rows, cudaMemcpyDeviceToHost,
+                              c->s_out);
+      }
+    }
+    if (e == cudaSuccess && !shared_workspace) {
+      e = cudaMemcpyAsync(c->h_status + blocks, ws, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->s_out);
+    }
+    ++blocks;
+  }
+  if (e == cudaSuccess && status == B200FP8_OK && shared_workspace) {
+    e = cudaMemcpyAsync(c->h_status, c->d_workspace, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->s_out);
+  }
+  // Whatever happened, the caller gets its host buffers back only when no copy is in flight on them.  On
+  // success the download stream finishing last implies the other two have finished (every block's download
+  // waits for its GEMM, which waits for its uploads), but uploads of panels no block needed would not be
+  // covered, so all three are waited for.
+  const cudaError_t e_in = cudaStreamSynchronize(c->s_in);
+  const cudaError_t e_compute = cudaStreamSynchronize(c->s_compute);
+  const cudaError_t e_out = cudaStreamSynchronize(c->s_out);
+  if (status != B200FP8_OK) return status;
+  if (e == cudaSuccess) e = e_in;
+  if (e == cudaSuccess) e = e_compute;
+  if (e == cudaSuccess) e = e_out;
   if (e != cudaSuccess) return note_cuda(e);
-  for (int i = 0; i < c->panels; ++i) {
-    if ((c->h_status[i] >> 24) == kDevTimeout) return B200FP8_DEVICE_TIMEOUT;
+  if (!resident) {
+    c->weights_resident = true;
+    c->bias_resident = bias_bf16 != nullptr;
+  }
+  const int words = shared_workspace ? 1 : blocks;
+  for (int i = 0; i < words; ++i) {
+    if ((c->h_status[i] >> 24) == kDevTimeout) {
+      // leave the workspace clean for the next call
+      cudaMemsetAsync(c->d_workspace, 0, c->workspace_total, c->s_compute);
+      cudaStreamSynchronize(c->s_compute);
+      return B200FP8_DEVICE_TIMEOUT;
+    }
   }
   return B200FP8_OK;
 }

@@ -20,7 +20,10 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
+#include <atomic>
+
 #include "kernels.h"
+#include "nanmax.cuh"
 
 namespace b200fp8 {
 namespace {
@@ -47,14 +50,14 @@ __device__ __forceinline__ float block_reduce(float v, float* smem) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float other = __shfl_xor_sync(0xffffffffu, v, o);
-    v = kMax ? fmaxf(v, other) : v + other;
+    v = kMax ? max_nan(v, other) : v + other;
   }
   __syncthreads();  // the previous reduction's readers are done with smem
   if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
   __syncthreads();
   float r = smem[0];
 #pragma unroll
-  for (int w = 1; w < kThreads / 32; ++w) r = kMax ? fmaxf(r, smem[w]) : r + smem[w];
+  for (int w = 1; w < kThreads / 32; ++w) r = kMax ? max_nan(r, smem[w]) : r + smem[w];
   return r;
 }
 
@@ -63,7 +66,7 @@ __device__ __forceinline__ void block_reduce_sum_max(float& s, float& m, float* 
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     s += __shfl_xor_sync(0xffffffffu, s, o);
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, o));
   }
   __syncthreads();
   if ((threadIdx.x & 31) == 0) {
@@ -76,7 +79,7 @@ __device__ __forceinline__ void block_reduce_sum_max(float& s, float& m, float* 
 #pragma unroll
   for (int w = 1; w < kThreads / 32; ++w) {
     s += smem[w];
-    m = fmaxf(m, smem[kThreads / 32 + w]);
+    m = max_nan(m, smem[kThreads / 32 + w]);
   }
 }
 
@@ -133,7 +136,7 @@ __global__ void __launch_bounds__(kThreads) fused_row_quantize_kernel(const Fuse
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           ss = fmaf(a[j], a[j], ss);
-          amax_xw = fmaxf(amax_xw, fabsf(a[j] * b[j]));
+          amax_xw = max_nan(amax_xw, fabsf(a[j] * b[j]));
         }
       }
     }
@@ -144,13 +147,13 @@ __global__ void __launch_bounds__(kThreads) fused_row_quantize_kernel(const Fuse
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         ss = fmaf(a[j], a[j], ss);
-        amax_xw = fmaxf(amax_xw, fabsf(a[j] * b[j]));
+        amax_xw = max_nan(amax_xw, fabsf(a[j] * b[j]));
       }
     }
     for (int c = vec_cols + threadIdx.x; c < cols; c += kThreads) {
       const float a = __bfloat162float(x1[c]);
       ss = fmaf(a, a, ss);
-      amax_xw = fmaxf(amax_xw, fabsf(a * __bfloat162float(x2[c])));
+      amax_xw = max_nan(amax_xw, fabsf(a * __bfloat162float(x2[c])));
     }
     if (one_pass_stats) {
       block_reduce_sum_max(ss, amax_xw, red);
@@ -173,7 +176,7 @@ __global__ void __launch_bounds__(kThreads) fused_row_quantize_kernel(const Fuse
   };
   auto absmax8 = [](const float (&y)[8], float m) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(y[j]));
+    for (int j = 0; j < 8; ++j) m = max_nan(m, fabsf(y[j]));
     return m;
   };
 
@@ -203,12 +206,12 @@ __global__ void __launch_bounds__(kThreads) fused_row_quantize_kernel(const Fuse
       amax = absmax8(y, amax);
     }
     for (int c = vec_cols + threadIdx.x; c < cols; c += kThreads) {
-      amax = fmaxf(amax, fabsf(produce(__bfloat162float(x1[c]), __bfloat162float(x2[c]))));
+      amax = max_nan(amax, fabsf(produce(__bfloat162float(x1[c]), __bfloat162float(x2[c]))));
     }
     amax = block_reduce<true>(amax, red);
   }
 
-  const float scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+  const float scale = __fdiv_rn(max_nan(amax, 1e-12f), 448.0f);
   const float inv_scale = __fdiv_rn(1.0f, scale);
   if (threadIdx.x == 0) p.scale[row] = scale;
 
@@ -287,12 +290,12 @@ __global__ void __launch_bounds__(kThreads) rms_norm_quantize_persistent_kernel(
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         ss = fmaf(a[j], a[j], ss);
-        amax_xw = fmaxf(amax_xw, fabsf(a[j] * w[i][j]));
+        amax_xw = max_nan(amax_xw, fabsf(a[j] * w[i][j]));
       }
     }
     block_reduce_sum_max(ss, amax_xw, red);
     const float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(ss, static_cast<float>(p.cols)) + p.eps));
-    const float scale = __fdiv_rn(fmaxf(amax_xw * inv_rms, 1e-12f), 448.0f);
+    const float scale = __fdiv_rn(max_nan(amax_xw * inv_rms, 1e-12f), 448.0f);
     const float inv_scale = __fdiv_rn(1.0f, scale);
     if (threadIdx.x == 0) p.scale[row] = scale;
     uint8_t* q = p.q + row * p.ldq;
@@ -345,11 +348,11 @@ __global__ void __launch_bounds__(kThreads) silu_mul_quantize_persistent_kernel(
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         y[i][j] = silu_mul(a[j], b[j]);
-        amax = fmaxf(amax, fabsf(y[i][j]));
+        amax = max_nan(amax, fabsf(y[i][j]));
       }
     }
     amax = block_reduce<true>(amax, red);
-    const float scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+    const float scale = __fdiv_rn(max_nan(amax, 1e-12f), 448.0f);
     const float inv_scale = __fdiv_rn(1.0f, scale);
     if (threadIdx.x == 0) p.scale[row] = scale;
     uint8_t* q = p.q + row * p.ldq;
@@ -367,11 +370,11 @@ __global__ void __launch_bounds__(kThreads) silu_mul_quantize_persistent_kernel(
 }
 
 template <typename Kernel>
-cudaError_t launch_persistent(Kernel kernel, int* ctas_per_device, const FusedQuantParams& p, cudaStream_t stream) {
+cudaError_t launch_persistent(Kernel kernel, std::atomic<int>* ctas_per_device, const FusedQuantParams& p, cudaStream_t stream) {
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
-  int ctas = dev < 64 ? ctas_per_device[dev] : 0;
+  int ctas = dev < 64 ? ctas_per_device[dev].load() : 0;
   if (ctas == 0) {
     int sms = 0, per_sm = 0;
     err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -388,13 +391,13 @@ cudaError_t launch_persistent(Kernel kernel, int* ctas_per_device, const FusedQu
 
 template <int kKeep>
 cudaError_t launch_rms_persistent(const FusedQuantParams& p, cudaStream_t stream) {
-  static int ctas_per_device[64] = {};
+  static std::atomic<int> ctas_per_device[64] = {};
   return launch_persistent(rms_norm_quantize_persistent_kernel<kKeep>, ctas_per_device, p, stream);
 }
 
 template <int kKeep>
 cudaError_t launch_silu_persistent(const FusedQuantParams& p, cudaStream_t stream) {
-  static int ctas_per_device[64] = {};
+  static std::atomic<int> ctas_per_device[64] = {};
   return launch_persistent(silu_mul_quantize_persistent_kernel<kKeep>, ctas_per_device, p, stream);
 }
 

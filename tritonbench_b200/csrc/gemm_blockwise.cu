@@ -20,6 +20,8 @@
 // to the two promotion warpgroups (232 each) with setmaxnreg.
 //
 // Persistent over a static tile list; every mbarrier wait is bounded.
+#include <mutex>
+
 #include "kernels.h"
 #include "ptx.cuh"
 
@@ -281,13 +283,17 @@ gemm_blockwise_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
 cudaError_t launch_gemm_blockwise(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
                                   const BlockwiseParams& p, int num_ctas, cudaStream_t stream) {
   static bool configured[64] = {};
+  static std::mutex mutex;
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
-  if (dev < 64 && !configured[dev]) {
-    err = cudaFuncSetAttribute(gemm_blockwise_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesBw);
-    if (err != cudaSuccess) return err;
-    configured[dev] = true;
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    if (dev < 64 && !configured[dev]) {
+      err = cudaFuncSetAttribute(gemm_blockwise_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesBw);
+      if (err != cudaSuccess) return err;
+      configured[dev] = true;
+    }
   }
   gemm_blockwise_kernel<<<num_ctas, kThreadsBw, kSmemBytesBw, stream>>>(tm_x, tm_w, tm_y, p);
   return cudaGetLastError();

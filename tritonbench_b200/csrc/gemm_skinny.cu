@@ -25,6 +25,8 @@
 // else (X, scales, bias, Y, workspace) only after griddepcontrol.wait, i.e. after the previous kernel
 // has completed.  Back-to-back decode GEMMs thus overlap one kernel's tail, where SMs finish at
 // different times, with the next kernel's prologue and first 192 KiB of weights per SM.
+#include <mutex>
+
 #include "kernels.h"
 #include "ptx.cuh"
 #include "streamk.cuh"
@@ -391,10 +393,12 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 
 cudaError_t skinny_static_scratch(void** device_ptr, size_t* bytes) {
   static void* address_on_device[64] = {};
+  static std::mutex mutex;
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mutex);
   if (address_on_device[dev] == nullptr) {
     void* ptr = nullptr;
     err = cudaGetSymbolAddress(&ptr, g_static_scratch);
@@ -409,14 +413,18 @@ cudaError_t skinny_static_scratch(void** device_ptr, size_t* bytes) {
 cudaError_t launch_gemm_skinny(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const SkinnyParams& p,
                                const SkinnyPlan& plan, cudaStream_t stream) {
   static size_t configured_bytes[64] = {};
+  static std::mutex mutex;
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
-  if (dev < 64 && configured_bytes[dev] < plan.smem_bytes) {
-    err = cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               SkinnyGeometry::kSmemBudget);
-    if (err != cudaSuccess) return err;
-    configured_bytes[dev] = SkinnyGeometry::kSmemBudget;
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    if (dev < 64 && configured_bytes[dev] < plan.smem_bytes) {
+      err = cudaFuncSetAttribute(gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 SkinnyGeometry::kSmemBudget);
+      if (err != cudaSuccess) return err;
+      configured_bytes[dev] = SkinnyGeometry::kSmemBudget;
+    }
   }
   SkinnyShape sh = {};
   sh.tokens_pad = plan.tokens_pad;

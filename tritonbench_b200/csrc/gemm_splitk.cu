@@ -22,6 +22,7 @@
 //
 // Every mbarrier wait is bounded; a CTA that gives up still arrives at both cluster barriers so
 // that its peers are never left waiting.
+#include <mutex>
 #include <type_traits>
 
 #include "kernels.h"
@@ -174,7 +175,12 @@ __device__ __forceinline__ void finish_columns(const Finish& f, int c_in_slice, 
   }
 }
 
-__global__ void __launch_bounds__(Geo::kThreads, 2)  // two CTAs of small problems share an SM
+// Two or more CTAs of small problems share an SM.  How many is bounded on the host: the plan asks for at least
+// SplitGeometry::min_smem_bytes_for_tmem(columns) of shared memory, so that the CTAs resident on one SM never
+// need more than its 512 tensor-memory columns (a tcgen05.alloc that had to wait for a peer stuck at a cluster
+// barrier would never return).  With the 168 registers per thread ptxas reports, 192 threads x 168 registers
+// already hold an SM to two CTAs; the shared-memory floor keeps the rule true whatever the compiler does.
+__global__ void __launch_bounds__(Geo::kThreads, 2)
 gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    const __grid_constant__ CUtensorMap tm_y, const TcParams p, const SplitPlan plan) {
   constexpr int kMaxStages = SplitGeometry::kMaxStages;
@@ -185,7 +191,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const int bytes_a = plan.rows_a * Geo::kBlockK;  // multiples of 1024: whole 8-row swizzle atoms
   const int bytes_b = block_n * Geo::kBlockK;
   const uint32_t stage_tx = static_cast<uint32_t>(bytes_a + bytes_b);
-  const uint32_t tmem_cols = block_n <= 32 ? 32u : (block_n <= 64 ? 64u : (block_n <= 128 ? 128u : 256u));
+  const uint32_t tmem_cols = static_cast<uint32_t>(split_tmem_cols(block_n));
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -430,6 +436,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
 cudaError_t configure(int dev) {
   static bool configured[64] = {};
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
   if (dev >= 0 && dev < 64 && configured[dev]) return cudaSuccess;
   const cudaError_t err =
       cudaFuncSetAttribute(gemm_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
@@ -464,7 +472,8 @@ int splitk_resident_clusters(int split, cudaError_t* err) {
 cudaError_t launch_gemm_splitk(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
                                const TcParams& p, const SplitPlan& plan, cudaStream_t stream) {
   if (plan.block_n < 16 || plan.block_n > 256 || plan.split < 1 || plan.block_n % (16 * plan.split) != 0 ||
-      plan.smem_bytes > C::kSmemBytes) {
+      plan.smem_bytes > C::kSmemBytes ||
+      plan.smem_bytes < SplitGeometry::min_smem_bytes_for_tmem(split_tmem_cols(plan.block_n))) {
     return cudaErrorInvalidValue;
   }
   int dev = 0;

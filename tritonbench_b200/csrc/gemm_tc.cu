@@ -13,7 +13,7 @@
 //   warps 2-5  epilogue: tcgen05.ld one TMEM lane quarter each, multiply by x_scale[m]*w_scale[n],
 //              add bias, round to bf16, stage 32x64 boxes in swizzled shared memory, TMA-store.
 //
-// Grouped mode (single-CTA variant; a mixture-of-experts layer): the rows of X are partitioned into
+// Grouped mode (both variants; a mixture-of-experts layer): the rows of X are partitioned into
 // groups by a device array of group sizes, group g multiplies rows g*N..(g+1)*N of the stacked W.
 // The tile list is then built on the device from the group sizes (no host round trip); a tile never
 // writes rows of the next group: boxes that straddle a group's end are stored with plain predicated
@@ -22,6 +22,8 @@
 // The accumulator is double buffered in TMEM, so the epilogue of tile i overlaps the main loop
 // of tile i+1.  Every mbarrier wait is bounded (ptx.cuh: mbar_wait); on a time-out the kernel
 // records a status word and all roles fall through to the common exit, which frees TMEM.
+#include <mutex>
+
 #include "kernels.h"
 #include "ptx.cuh"
 
@@ -418,13 +420,17 @@ cudaError_t launch_gemm_tc(const CUtensorMap& tm_x, const CUtensorMap& tm_w, con
   auto kernel = gemm_tc_kernel<kCtaGroup>;
   // Opt in to the large dynamic shared-memory size once per device.
   static bool configured[64] = {};
+  static std::mutex mutex;
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
-  if (dev < 64 && !configured[dev]) {
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (err != cudaSuccess) return err;
-    configured[dev] = true;
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    if (dev < 64 && !configured[dev]) {
+      err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+      if (err != cudaSuccess) return err;
+      configured[dev] = true;
+    }
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(num_ctas), 1, 1);

@@ -59,7 +59,17 @@ cudaError_t launch_gemm_tc(const CUtensorMap& tm_x, const CUtensorMap& tm_w, con
 struct SplitGeometry {
   static constexpr int kRingBytes = 192 * 1024;
   static constexpr int kMaxStages = 14;
+  static constexpr int kSmemPerSm = 227 * 1024;  // shared memory the CTAs of one SM can hold together
+  static constexpr int kTmemColsPerSm = 512;
+  // Smallest dynamic shared-memory request with which the CTAs that fit on one SM by shared memory
+  // (floor(kSmemPerSm / request)) hold at most the SM's 512 tensor-memory columns between them.
+  static constexpr int min_smem_bytes_for_tmem(int tmem_cols) {
+    const int max_ctas = kTmemColsPerSm / tmem_cols;
+    return (kSmemPerSm / (max_ctas + 1) / 1024 + 1) * 1024;
+  }
 };
+// tensor-memory columns a CTA of the one-tile-per-cluster kernel allocates for a tile of block_n columns
+__host__ __device__ constexpr int split_tmem_cols(int block_n) { return block_n <= 32 ? 32 : (block_n <= 64 ? 64 : (block_n <= 128 ? 128 : 256)); }
 struct SplitPlan {
   int block_n;
   int split;

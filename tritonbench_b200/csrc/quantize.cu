@@ -15,9 +15,11 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "kernels.h"
+#include "nanmax.cuh"
 
 namespace b200fp8 {
 namespace {
@@ -46,12 +48,12 @@ __device__ __forceinline__ uint8_t to_e4m3(float v) {
 
 __device__ __forceinline__ float block_max(float v, float* smem) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  for (int o = 16; o > 0; o >>= 1) v = max_nan(v, __shfl_xor_sync(0xffffffffu, v, o));
   if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
   __syncthreads();
   float r = smem[0];
 #pragma unroll
-  for (int w = 1; w < kThreads / 32; ++w) r = fmaxf(r, smem[w]);
+  for (int w = 1; w < kThreads / 32; ++w) r = max_nan(r, smem[w]);
   return r;
 }
 
@@ -81,8 +83,8 @@ template <int kRecipe>
 struct Ops<__nv_bfloat16, kRecipe> {
   static __device__ __forceinline__ float absmax(const Raw<__nv_bfloat16>& r) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r.lo);
-    __nv_bfloat162 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
-    return fmaxf(__low2float(m), __high2float(m));
+    __nv_bfloat162 m = __hmax2_nan(__hmax2_nan(__habs2(h[0]), __habs2(h[1])), __hmax2_nan(__habs2(h[2]), __habs2(h[3])));
+    return max_nan(__low2float(m), __high2float(m));
   }
   static __device__ __forceinline__ uint2 codes(const Raw<__nv_bfloat16>& r, float mult) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r.lo);
@@ -104,8 +106,8 @@ template <int kRecipe>
 struct Ops<__half, kRecipe> {
   static __device__ __forceinline__ float absmax(const Raw<__half>& r) {
     const __half2* h = reinterpret_cast<const __half2*>(&r.lo);
-    __half2 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
-    return fmaxf(__low2float(m), __high2float(m));
+    __half2 m = __hmax2_nan(__hmax2_nan(__habs2(h[0]), __habs2(h[1])), __hmax2_nan(__habs2(h[2]), __habs2(h[3])));
+    return max_nan(__low2float(m), __high2float(m));
   }
   static __device__ __forceinline__ uint2 codes(const Raw<__half>& r, float mult) {
     const __half2* h = reinterpret_cast<const __half2*>(&r.lo);
@@ -130,7 +132,7 @@ struct Ops<float, kRecipe> {
     const float* b = reinterpret_cast<const float*>(&r.hi);
     float m = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) m = fmaxf(m, fmaxf(fabsf(a[j]), fabsf(b[j])));
+    for (int j = 0; j < 4; ++j) m = max_nan(m, max_nan(fabsf(a[j]), fabsf(b[j])));
     return m;
   }
   static __device__ __forceinline__ float one(float v, float mult) {
@@ -169,23 +171,23 @@ __global__ void __launch_bounds__(kThreads) row_quantize_kernel(const QuantParam
 #pragma unroll
   for (int i = 0; i < kMaxVecs; ++i) {
     const int v = threadIdx.x + i * kThreads;
-    if (v < nvec) amax = fmaxf(amax, O::absmax(keep[i]));
+    if (v < nvec) amax = max_nan(amax, O::absmax(keep[i]));
   }
   for (int v = threadIdx.x + kMaxVecs * kThreads; v < nvec; v += kThreads) {  // rows longer than 16384
-    amax = fmaxf(amax, O::absmax(load_raw<T>(x + v * kVec)));
+    amax = max_nan(amax, O::absmax(load_raw<T>(x + v * kVec)));
   }
-  for (int c = vec_cols + threadIdx.x; c < cols; c += kThreads) amax = fmaxf(amax, fabsf(Conv<T>::up(x[c])));
+  for (int c = vec_cols + threadIdx.x; c < cols; c += kThreads) amax = max_nan(amax, fabsf(Conv<T>::up(x[c])));
   amax = block_max(amax, red);
 
   // the row's multiplier (or divisor) and the scale handed to the GEMM
   float mult, scale;
   if constexpr (kRecipe == kRecipeOperator) {
-    const float c = fmaxf(amax, Conv<T>::rnd(1e-12f));
+    const float c = max_nan(amax, Conv<T>::rnd(1e-12f));
     mult = Conv<T>::rnd(__fmul_rn(Conv<T>::rnd(__fdiv_rn(1.0f, c)), 448.0f));
-    if constexpr (std::is_same<T, __half>::value) mult = fminf(mult, 65504.0f);
+    if constexpr (std::is_same<T, __half>::value) mult = min_nan(mult, 65504.0f);
     scale = Conv<T>::rnd(__fdiv_rn(1.0f, mult));
   } else {
-    scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+    scale = __fdiv_rn(max_nan(amax, 1e-12f), 448.0f);
     mult = scale;  // used as the divisor
   }
   if (threadIdx.x == 0) p.scale[row] = scale;
@@ -236,17 +238,17 @@ __global__ void __launch_bounds__(kThreads) row_quantize_persistent_kernel(const
     if (next_row < p.rows) load_row(next_row, nxt);
     float amax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < kKeep; ++i) amax = fmaxf(amax, O::absmax(cur[i]));
+    for (int i = 0; i < kKeep; ++i) amax = max_nan(amax, O::absmax(cur[i]));
     __syncthreads();  // the previous row's readers are done with `red`
     amax = block_max(amax, red);
     float mult, scale;
     if constexpr (kRecipe == kRecipeOperator) {
-      const float c = fmaxf(amax, Conv<T>::rnd(1e-12f));
+      const float c = max_nan(amax, Conv<T>::rnd(1e-12f));
       mult = Conv<T>::rnd(__fmul_rn(Conv<T>::rnd(__fdiv_rn(1.0f, c)), 448.0f));
-      if constexpr (std::is_same<T, __half>::value) mult = fminf(mult, 65504.0f);
+      if constexpr (std::is_same<T, __half>::value) mult = min_nan(mult, 65504.0f);
       scale = Conv<T>::rnd(__fdiv_rn(1.0f, mult));
     } else {
-      scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+      scale = __fdiv_rn(max_nan(amax, 1e-12f), 448.0f);
       mult = scale;  // used as the divisor
     }
     if (threadIdx.x == 0) p.scale[row] = scale;
@@ -283,18 +285,18 @@ __global__ void __launch_bounds__(kThreads) row_quantize_short_rows_kernel(const
 #pragma unroll
   for (int i = 0; i < kShortRowVecs; ++i) {
     const int v = lane + i * 32;
-    if (v < nvec) amax = fmaxf(amax, O::absmax(keep[i]));
+    if (v < nvec) amax = max_nan(amax, O::absmax(keep[i]));
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  for (int o = 16; o > 0; o >>= 1) amax = max_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   float mult, scale;
   if constexpr (kRecipe == kRecipeOperator) {
-    const float c = fmaxf(amax, Conv<T>::rnd(1e-12f));
+    const float c = max_nan(amax, Conv<T>::rnd(1e-12f));
     mult = Conv<T>::rnd(__fmul_rn(Conv<T>::rnd(__fdiv_rn(1.0f, c)), 448.0f));
-    if constexpr (std::is_same<T, __half>::value) mult = fminf(mult, 65504.0f);
+    if constexpr (std::is_same<T, __half>::value) mult = min_nan(mult, 65504.0f);
     scale = Conv<T>::rnd(__fdiv_rn(1.0f, mult));
   } else {
-    scale = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+    scale = __fdiv_rn(max_nan(amax, 1e-12f), 448.0f);
     mult = scale;  // used as the divisor
   }
   if (lane == 0) p.scale[row] = scale;
@@ -307,11 +309,11 @@ __global__ void __launch_bounds__(kThreads) row_quantize_short_rows_kernel(const
 
 template <typename T, int kRecipe, int kKeep>
 cudaError_t launch_persistent(const QuantParams& p, cudaStream_t stream) {
-  static int ctas_per_device[64] = {};
+  static std::atomic<int> ctas_per_device[64] = {};
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
-  int ctas = dev < 64 ? ctas_per_device[dev] : 0;
+  int ctas = dev < 64 ? ctas_per_device[dev].load() : 0;
   if (ctas == 0) {
     int sms = 0, per_sm = 0;
     err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -397,11 +399,11 @@ __global__ void __launch_bounds__(kThreads) block_quantize_kernel(const BlockQua
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+    for (int j = 0; j < 8; ++j) amax = max_nan(amax, fabsf(v[i][j]));
   }
   amax = block_max(amax, red);
   // torch evaluates `448 / blockmax` as reciprocal(blockmax) * 448: two roundings
-  float mult = __fmul_rn(__fdiv_rn(1.0f, fmaxf(amax, Conv<T>::rnd(1e-12f))), 448.0f);
+  float mult = __fmul_rn(__fdiv_rn(1.0f, max_nan(amax, Conv<T>::rnd(1e-12f))), 448.0f);
   if (isinf(mult)) mult = 1.0f;
   if (threadIdx.x == 0) p.scale[static_cast<long long>(bm) * p.ld_scale + bk] = __fdiv_rn(1.0f, mult);
 

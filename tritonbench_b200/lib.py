@@ -61,6 +61,8 @@ EXPORTED_SYMBOLS = (
     "b200fp8_host_ctx_create",
     "b200fp8_host_ctx_destroy",
     "b200fp8_gemm_rowwise_host",
+    "b200fp8_host_ctx_set_weights",
+    "b200fp8_host_ctx_set_panels",
     "b200fp8_gemm_rowwise_noalloc",
     "b200fp8_noalloc_status",
     "b200fp8_row_quantize",
@@ -118,6 +120,10 @@ def load() -> ctypes.CDLL:
     lib.b200fp8_host_ctx_destroy.argtypes = [c_void_p]
     lib.b200fp8_gemm_rowwise_host.restype = ctypes.c_int
     lib.b200fp8_gemm_rowwise_host.argtypes = [c_void_p] * 7
+    lib.b200fp8_host_ctx_set_weights.restype = ctypes.c_int
+    lib.b200fp8_host_ctx_set_weights.argtypes = [c_void_p] * 4
+    lib.b200fp8_host_ctx_set_panels.restype = ctypes.c_int
+    lib.b200fp8_host_ctx_set_panels.argtypes = [c_void_p, c_int64, c_int64]
     lib.b200fp8_gemm_rowwise_noalloc.restype = ctypes.c_int
     lib.b200fp8_gemm_rowwise_noalloc.argtypes = [c_void_p] * 6 + [c_int64] * 6 + [c_void_p]
     lib.b200fp8_noalloc_status.restype = ctypes.c_int

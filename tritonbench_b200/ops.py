@@ -205,11 +205,14 @@ def fp8_gemm_rowwise_grouped(
     xq: torch.Tensor, wq: torch.Tensor, m_sizes: torch.Tensor, x_scale: torch.Tensor, w_scale: torch.Tensor,
     out: Optional[torch.Tensor] = None,
     variant: str = "auto",
+    workspace: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Grouped GEMM in the argument order of the reference's
     `grouped_gemm_fp8_rowwise(group_A, group_B, m_sizes, a_scale, b_scale)`
     (tritonbench/operators/fp8_gemm_rowwise_grouped/operator.py:412-432): xq [M_total, K], wq [G*N, K] stacked,
-    m_sizes int32 [G] on the device (never copied to the host), scales per row; returns bf16 [M_total, N]."""
+    m_sizes int32 [G] on the device (never copied to the host), scales per row; returns bf16 [M_total, N].
+    Pass `workspace` (256 zero bytes, see get_workspace) when the call is captured in a CUDA graph: the cached
+    workspace is keyed by stream, and a capture stream would otherwise allocate a new one inside the capture."""
     for t, name in ((xq, "xq"), (wq, "wq"), (m_sizes, "m_sizes"), (x_scale, "x_scale"), (w_scale, "w_scale")):
         _require_cuda(t, name)
     if m_sizes.dtype != torch.int32 or m_sizes.dim() != 1 or not m_sizes.is_contiguous():
@@ -223,7 +226,8 @@ def fp8_gemm_rowwise_grouped(
         raise ValueError("x_scale must have M_total elements and w_scale G*N elements")
     if out is None:
         out = torch.empty((m_total, n), dtype=torch.bfloat16, device=xq.device)
-    workspace = get_workspace(xq.device, _lib.WORKSPACE_HEADER_BYTES)
+    if workspace is None:
+        workspace = get_workspace(xq.device, _lib.WORKSPACE_HEADER_BYTES)
     status = _lib.load().b200fp8_gemm_rowwise_grouped(
         xq.data_ptr(), wq.data_ptr(), x_scale.contiguous().data_ptr(), w_scale.contiguous().data_ptr(), m_sizes.data_ptr(),
         groups, out.data_ptr(), m_total, n, k, xq.stride(0), wq.stride(0), out.stride(0),
@@ -234,10 +238,12 @@ def fp8_gemm_rowwise_grouped(
 
 
 def fp8_gemm_blockwise(xq: torch.Tensor, wq: torch.Tensor, x_scale: torch.Tensor, w_scale: torch.Tensor,
-                       out: Optional[torch.Tensor] = None, tma_store: bool = True) -> torch.Tensor:
+                       out: Optional[torch.Tensor] = None, tma_store: bool = True,
+                       workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """128x128 block-scaled GEMM in the argument order of the reference's `matmul_fp8_block(xq, wq, x_scale, w_scale)`
     (tritonbench/operators/fp8_gemm_blockwise/operator.py:139-149): x_scale [ceil(M/128), ceil(K/128)],
-    w_scale [ceil(N/128), ceil(K/128)] float32 (the reciprocal multipliers); returns bf16 [M, N]."""
+    w_scale [ceil(N/128), ceil(K/128)] float32 (the reciprocal multipliers); returns bf16 [M, N].
+    `workspace`: as for fp8_gemm_rowwise_grouped."""
     for t, name in ((xq, "xq"), (wq, "wq"), (x_scale, "x_scale"), (w_scale, "w_scale")):
         _require_cuda(t, name)
     m, k = xq.shape
@@ -253,7 +259,8 @@ def fp8_gemm_blockwise(xq: torch.Tensor, wq: torch.Tensor, x_scale: torch.Tensor
         w_scale = w_scale.contiguous()
     if out is None:
         out = torch.empty((m, n), dtype=torch.bfloat16, device=xq.device)
-    workspace = get_workspace(xq.device, _lib.WORKSPACE_HEADER_BYTES)
+    if workspace is None:
+        workspace = get_workspace(xq.device, _lib.WORKSPACE_HEADER_BYTES)
     status = _lib.load().b200fp8_gemm_blockwise(
         xq.data_ptr(), wq.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(), out.data_ptr(), m, n, k,
         xq.stride(0), wq.stride(0), out.stride(0), x_scale.stride(0), w_scale.stride(0),
@@ -317,9 +324,11 @@ def check_device_status(device: Optional[torch.device] = None) -> None:
 
 class HostGemm:
     """Host-buffer GEMM: inputs and output are CPU tensors (pin them for full PCIe speed);
-    every call copies in, runs the kernel, copies out and synchronises."""
+    every call copies in, runs the kernel, copies out and synchronises.
 
-    def __init__(self, m: int, n: int, k: int, variant: str = "auto"):
+    set_weights(wq, w_scale, bias) uploads the weights once; calls that then pass wq=None send only X."""
+
+    def __init__(self, m: int, n: int, k: int, variant: str = "auto", panels: Optional[Tuple[int, int]] = None):
         import ctypes
 
         self.shape = (m, n, k)
@@ -329,19 +338,43 @@ class HostGemm:
             self._lib.b200fp8_host_ctx_create(m, n, k, _flags(variant, True), ctypes.byref(self._ctx)),
             "b200fp8_host_ctx_create",
         )
+        if panels is not None:
+            _lib.check(self._lib.b200fp8_host_ctx_set_panels(self._ctx, panels[0], panels[1]), "b200fp8_host_ctx_set_panels")
+
+    @staticmethod
+    def _host(t, name):
+        if t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"{name}: HostGemm takes contiguous CPU tensors")
+        return t.data_ptr()
+
+    def set_weights(self, wq, w_scale, bias=None) -> None:
+        m, n, k = self.shape
+        if wq is None:
+            _lib.check(self._lib.b200fp8_host_ctx_set_weights(self._ctx, None, None, None), "b200fp8_host_ctx_set_weights")
+            return
+        if tuple(wq.shape) != (n, k) or w_scale.numel() != n or w_scale.dtype != torch.float32:
+            raise ValueError("wq must be [N, K] and w_scale float32 [N]")
+        _lib.check(
+            self._lib.b200fp8_host_ctx_set_weights(
+                self._ctx, self._host(wq, "wq"), self._host(w_scale, "w_scale"),
+                self._host(bias, "bias") if bias is not None else None),
+            "b200fp8_host_ctx_set_weights",
+        )
 
     def __call__(self, xq, wq, x_scale, w_scale, bias=None, out=None) -> torch.Tensor:
         m, n, k = self.shape
-        for t in (xq, wq, x_scale, w_scale):
-            if t.is_cuda or not t.is_contiguous():
-                raise ValueError("HostGemm takes contiguous CPU tensors")
-        if tuple(xq.shape) != (m, k) or tuple(wq.shape) != (n, k):
+        if tuple(xq.shape) != (m, k) or (wq is not None and tuple(wq.shape) != (n, k)):
             raise ValueError("shape differs from the context's")
+        if x_scale.numel() != m or x_scale.dtype != torch.float32:
+            raise ValueError("x_scale must be float32 [M]")
         if out is None:
             out = torch.empty((m, n), dtype=torch.bfloat16, pin_memory=True)
+        elif tuple(out.shape) != (m, n) or out.dtype != torch.bfloat16:
+            raise ValueError("out must be bfloat16 [M, N]")
         status = self._lib.b200fp8_gemm_rowwise_host(
-            self._ctx, xq.data_ptr(), wq.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(),
-            bias.data_ptr() if bias is not None else None, out.data_ptr(),
+            self._ctx, self._host(xq, "xq"), self._host(wq, "wq") if wq is not None else None,
+            self._host(x_scale, "x_scale"), self._host(w_scale, "w_scale") if w_scale is not None else None,
+            self._host(bias, "bias") if bias is not None else None, self._host(out, "out"),
         )
         _lib.check(status, "b200fp8_gemm_rowwise_host")
         return out

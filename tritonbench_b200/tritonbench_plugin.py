@@ -142,8 +142,8 @@ def b200_grouped(self, group_A, group_B, m_sizes, a_scale, b_scale) -> Callable:
     groups = m_sizes.numel()
     out = torch.empty((group_A.shape[0], group_B.shape[0] // groups), dtype=torch.bfloat16, device=group_A.device)
     sizes = m_sizes.to(torch.int32).contiguous()
-    ops.get_workspace(group_A.device, 256)  # allocated here, outside the timed / captured region
-    return lambda: ops.fp8_gemm_rowwise_grouped(group_A, group_B, sizes, a_scale, b_scale, out=out)
+    ws = ops.get_workspace(group_A.device, 256)  # allocated here, outside the timed / captured region
+    return lambda: ops.fp8_gemm_rowwise_grouped(group_A, group_B, sizes, a_scale, b_scale, out=out, workspace=ws)
 
 
 def torch_dequant_grouped_ref(self, group_A, group_B, m_sizes, a_scale, b_scale) -> Callable:
@@ -188,8 +188,8 @@ def b200_blockwise(self, xq, wq, x_scale, w_scale) -> Callable:
     x_scale = x_scale.to(xq.device).contiguous()  # the stock quantiser leaves the scales where it computed them
     w_scale = w_scale.to(xq.device).contiguous()
     out = torch.empty((xq.shape[0], wq.shape[0]), dtype=torch.bfloat16, device=xq.device)
-    ops.get_workspace(xq.device, 256)
-    return lambda: ops.fp8_gemm_blockwise(xq, wq, x_scale, w_scale, out=out)
+    ws = ops.get_workspace(xq.device, 256)
+    return lambda: ops.fp8_gemm_blockwise(xq, wq, x_scale, w_scale, out=out, workspace=ws)
 
 
 def torch_dequant_blockwise_ref(self, xq, wq, x_scale, w_scale) -> Callable:
