@@ -10,11 +10,18 @@ the job is the M = N*8192 prefill problem, i.e. M = 65536 at 8 GPUs).  Rank 0 pr
   value      whole-job TFLOP/s with inputs resident in HBM, timed with CUDA events on the launching
              stream over exactly K back-to-back steps, max over ranks
   e2e        the same metric through the host-buffer C-ABI call (b200fp8_gemm_rowwise_host): every
-             step copies X, W and the scales from pinned host memory, runs the kernel and copies Y back
+             step copies X, W and the scales from pinned host memory, runs the kernel and copies Y back;
+             with the PCIe rates measured in the same process and the fraction of that bound it reaches
   roofline   achieved vs the measured tensor peak (large M) or HBM peak (decode workload)
   cpu_baseline  the CPU oracle (torch fp32 dequantise-then-matmul) timed on a bounded row sample
+  parity     rows of the Y each timed loop produced last, sampled and compared with the CPU oracle inside
+             this run; a failure makes the process exit non-zero
+  also       (default workload only) the other benchmark configurations, each timed and checked the same
+             way: the four decode shapes with ordinary and with overlapped launches, the four irregular
+             shapes, the M = 65536 prefill problem split over the ranks (strong scaling) without and with
+             the all-gather of Y, and the square workload sustained for at least a second
 
-`--impl reference` times that CPU path alone (all host threads) and prints the same line shape.
+`--impl reference` times the CPU path alone (all host threads) and prints the same line shape.
 """
 import argparse
 import json
@@ -32,6 +39,7 @@ if ROOT not in sys.path:
 
 METRIC = "fp8_gemm_rowwise_tflops"
 UNIT = "TFLOP/s"
+L2_BYTES = 126e6
 
 WORKLOADS = {
     # name: (M per GPU, N, K, x_std, w_std, dist, bound)
@@ -45,28 +53,42 @@ WORKLOADS = {
     "irregular_4096x14336x4096": (4096, 14336, 4096, 1.0, 1.0, "student_t3", "tensor"),
     "irregular_777x1024x8192": (777, 1024, 8192, 1.0, 1.0, "student_t3", "tensor"),
 }
-
-# per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/; None where no capture of that workload exists
-NCU_TRAFFIC_BYTES = {
-    "square_8192": 462.2e6,
-    "decode_m16": 241.3e6,
-}
+PREFILL_M, PREFILL_N, PREFILL_K = 65536, 8192, 8192
+PARITY_ROWS = 64
 
 
 def measured_peaks():
-    """(fp8 tensor peak TFLOP/s, HBM GB/s, note).  The fp8 peak is twice the measured cuBLAS bf16
-    figure: kind::f8f6f4 runs on the same tensor pipe at twice the bf16 rate."""
+    """(fp8 tensor peak TFLOP/s burst, sustained, HBM GB/s, note).  The fp8 peak is twice the measured cuBLAS
+    bf16 figure: kind::f8f6f4 runs on the same tensor pipe at twice the bf16 rate."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return 2.0 * float(p["bf16_tflops"]), float(p["hbm_gbs"]), "of measured (fp8 peak = 2 x cuBLAS bf16 burst)"
-    return 2.0 * 1590.0, 6650.0, "of fallback (fp8 peak = 2 x 1.59 PFLOP/s)"
+        return (2.0 * float(p["bf16_tflops"]), 2.0 * float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                float(p["hbm_gbs"]), "of measured (fp8 peak = 2 x cuBLAS bf16)")
+    return 2.0 * 1590.0, 2.0 * 1400.0, 6650.0, "of fallback (fp8 peak = 2 x 1.59 PFLOP/s burst, 2 x 1.4 sustained)"
+
+
+def ncu_traffic(workload: str, plan: str):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the ncu capture recorded for
+    this workload in profiles/ncu_traffic.md, or (None, why) when the table has no row for the workload or the
+    row was captured with another kernel plan than the one the library picks now."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.md")
+    if not os.path.exists(path):
+        return None, "profiles/ncu_traffic.md is missing"
+    for line in open(path):
+        cells = [c.strip() for c in line.strip().strip("|").split("|")]
+        if len(cells) < 5 or cells[0] != workload:
+            continue
+        want = cells[1].strip("`")
+        if not plan.startswith(want):
+            return None, f"profiles/ncu_traffic.md holds a capture of plan '{want}', the library now picks another"
+        return float(cells[2]), f"profiles/{cells[4]} @ {cells[3]}"
+    return None, "no ncu capture of this workload in profiles/ncu_traffic.md"
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs (reading only)."""
 
     REASONS = {
         0x0000000000000004: "sw_power_cap",
@@ -76,7 +98,7 @@ class ClockSampler:
         0x0000000000000080: "hw_power_brake_slowdown",
     }
 
-    def __init__(self, index: int, period_s: float = 0.004):
+    def __init__(self, index: int, period_s: float = 0.002):
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
         self.sm_max = None
@@ -87,10 +109,8 @@ class ClockSampler:
             import pynvml
 
             pynvml.nvmlInit()
-            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-            phys = int(visible.split(",")[index]) if visible and visible.split(",")[index].isdigit() else index
             self._nv = pynvml
-            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(physical_gpu_index(index))
             self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
         except Exception:
             self._h = None
@@ -124,10 +144,62 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons), "samples": 0}
         return {
             "sm_mhz": statistics.median(self.samples),
+            "sm_min_mhz": min(self.samples),
             "sm_max_mhz": self.sm_max,
             "reasons": sorted(self.reasons),
             "samples": len(self.samples),
         }
+
+
+def physical_gpu_index(local_index: int) -> int:
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if visible:
+        parts = visible.split(",")
+        if local_index < len(parts) and parts[local_index].strip().isdigit():
+            return int(parts[local_index])
+    return local_index
+
+
+class NumaBinding:
+    """While active, the calling thread runs on the CPUs NVML lists as close to the GPU, so that pinned host
+    buffers allocated (and first touched) inside land on the GPU's own NUMA node.  The previous affinity is
+    restored on exit.  Reads NVML only; changes nothing but this process's own CPU affinity."""
+
+    def __init__(self, local_index: int):
+        self.cpus, self.note, self._saved = None, "not bound", None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(physical_gpu_index(local_index))
+            words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+            near = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+            allowed = os.sched_getaffinity(0)
+            if near & allowed:
+                self.cpus = near & allowed
+                self.note = f"{len(self.cpus)} of {len(allowed)} allowed CPUs are near the GPU"
+            else:
+                self.note = "NVML lists no allowed CPU near the GPU"
+        except Exception as e:  # no NVML, no affinity support: stay where we are
+            self.note = f"not bound ({type(e).__name__})"
+
+    def __enter__(self):
+        if self.cpus:
+            self._saved = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, self.cpus)
+        return self
+
+    def __exit__(self, *exc):
+        if self._saved is not None:
+            os.sched_setaffinity(0, self._saved)
+
+
+def host_threads(world: int = 1) -> int:
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(1, n // max(world, 1))
 
 
 def cpu_oracle_rate(xq, wq, xs, ws, target_seconds: float, steps: int = 1, warmup: int = 0):
@@ -137,8 +209,8 @@ def cpu_oracle_rate(xq, wq, xs, ws, target_seconds: float, steps: int = 1, warmu
 
     # all the host threads this process may use (torchrun exports OMP_NUM_THREADS=1 to its ranks)
     try:
-        torch.set_num_threads(len(os.sched_getaffinity(0)))
-    except (AttributeError, RuntimeError):
+        torch.set_num_threads(host_threads())
+    except RuntimeError:
         pass
     m, k = xq.shape
     n = wq.shape[0]
@@ -203,123 +275,377 @@ def run_reference(args, workload):
     print(json.dumps(line), flush=True)
 
 
-def time_e2e(ops, m, n, k, x_pair, wq, ws, e2e_steps, barrier, grouped, device, world, flops_step_rank):
-    """Wall-clock over e2e_steps synchronous host-buffer calls (each: H2D copies, kernel, D2H copy)."""
-    import torch.distributed as td
+# --------------------------------------------------------------------------------------------- own arm
+class Run:
+    """State shared by the legs of one bench process: rank, device, barrier, max-over-ranks timing."""
 
+    def __init__(self, args):
+        import torch.distributed as td
+
+        from tritonbench_b200 import dist as shard
+        from tritonbench_b200 import lib
+
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+        lib.load()  # fail loudly when the CUDA library is missing
+        self.td, self.shard = td, shard
+        self.rank, self.local_rank, self.world = shard.env_rank_world()
+        if self.world != args.gpus:
+            if self.world == 1 and args.gpus > 1:
+                raise SystemExit(f"--gpus {args.gpus} needs a torchrun launch with {args.gpus} ranks")
+            args.gpus = self.world
+        torch.cuda.set_device(self.local_rank)
+        self.device = torch.device("cuda", self.local_rank)
+        self.grouped = shard.init_process_group("nccl") if self.world > 1 else False
+        self.launches = 0
+        self.parity_failures = []
+        try:
+            torch.set_num_threads(min(16, host_threads(self.world)))  # for the in-run oracle checks
+        except RuntimeError:
+            pass
+
+    def barrier(self):
+        torch.cuda.synchronize(self.device)
+        if self.grouped:
+            self.td.barrier()
+        torch.cuda.synchronize(self.device)
+
+    def max_over_ranks(self, value: float) -> float:
+        if not self.grouped:
+            return value
+        t = torch.tensor([value], dtype=torch.float64, device=self.device)
+        self.td.all_reduce(t, op=self.td.ReduceOp.MAX)
+        return float(t.item())
+
+    def all_true(self, ok: bool) -> bool:
+        return self.max_over_ranks(0.0 if ok else 1.0) == 0.0
+
+    def time_steps(self, step, steps, warmup, sampler=None):
+        """ms per step: CUDA events on the launching stream around exactly `steps` back-to-back steps, barrier and
+        synchronise on both sides, max over ranks."""
+        from tritonbench_b200 import ops
+
+        for i in range(warmup):
+            step(i)
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if sampler is not None:
+            sampler.__enter__()
+        try:
+            self.barrier()
+            e0.record()
+            for i in range(steps):
+                step(i)
+            e1.record()
+            self.barrier()
+        finally:
+            if sampler is not None:
+                sampler.__exit__(None, None, None)
+        ops.check_device_status(self.device)
+        return self.max_over_ranks(e0.elapsed_time(e1)) / steps
+
+    def parity(self, what, y, xq, wq, xs, ws, seed=0):
+        """PARITY_ROWS rows of y (first and last among them) against the CPU oracle on the same operands."""
+        from oracle import fp8_rowwise_oracle as orc  # the checker, never the thing measured
+
+        m = xq.shape[0]
+        g = torch.Generator().manual_seed(seed)
+        rows = torch.randperm(m, generator=g)[: min(m, PARITY_ROWS)]
+        if m > 1:
+            rows[0], rows[-1] = 0, m - 1
+        rows = rows.sort().values
+        dev_rows = rows.to(xq.device)
+        ref = orc.gemm_rowwise(xq[dev_rows].cpu(), wq.cpu(), xs[dev_rows].cpu(), ws.cpu(), decode="cast")
+        res = orc.compare(y[rows.to(y.device)], ref)
+        out = {"checked_rows": int(rows.numel()), "checked_elements": int(ref.numel()), "max_ratio": round(res["max_ratio"], 4),
+               "ok": bool(res["ok"]), "bound": "1 bf16 ulp + 1e-2 RMS(ref)"}
+        if not out["ok"]:
+            self.parity_failures.append(f"rank {self.rank}: {what}: {res}")
+        return out
+
+
+def make_sets(quantize, m, n, k, dist_name, x_std, w_std, device, x_seed, w_seed, min_bytes, share_w=None):
+    """Operand / output sets to rotate through so that no step finds its operands in L2 from the step before:
+    enough copies that one trip around them moves more than `min_bytes`.  W is drawn once (every set multiplies
+    the same weights); with share_w False each set has its own copy of it, so that W is cold as well."""
+    wq, ws = quantize.make_quantized(n, k, seed=w_seed, device=device, dist=dist_name, std=w_std)
+    per_set_private = m * k + 2 * m * n
+    if share_w is None:
+        share_w = n * k >= 2 * L2_BYTES  # a W this large cannot survive in L2 between steps anyway
+    per_set = per_set_private + (0 if share_w else n * k)
+    count = 3 if share_w else int(max(3, min(48, min_bytes // max(per_set, 1) + 1)))
+    sets = []
+    for b in range(count):
+        xq, xs = quantize.make_quantized(m, k, seed=x_seed + 1000 * b, device=device, dist=dist_name, std=x_std)
+        w_b = wq if (share_w or b == 0) else wq.clone()
+        sets.append((xq, xs, w_b, torch.empty((m, n), dtype=torch.bfloat16, device=device)))
+    return sets, wq, ws, count * per_set + (n * k if share_w else 0)
+
+
+def gemm_leg(run, name, shape, dist_name, x_std, w_std, bound, steps, warmup, modes=("ordinary",), x_seed=None, sampler=None,
+             min_seconds=0.0, share_w=None):
+    """Times one GEMM shape on this rank (every rank runs the same leg on its own GPU) and checks the last Y."""
+    from tritonbench_b200 import lib, ops, quantize
+
+    m, n, k = shape
+    fp8_peak, fp8_sustained, hbm_peak, peak_note = measured_peaks()
+    seed = run.shard.shard_seed(run.rank) if x_seed is None else x_seed
+    sets, wq, ws, rotation_bytes = make_sets(quantize, m, n, k, dist_name, x_std, w_std, run.device, seed, run.shard.W_SEED,
+                                             2.2 * L2_BYTES, share_w=share_w)
+    workspace = ops.get_workspace(run.device, ops.workspace_bytes(m, n, k))
+    flops = 2.0 * m * n * k
+    alg_bytes = m * k + n * k + 2 * m * n + 4 * (m + n)
+    out = {"M": m, "N": n, "K": k, "plan": lib.describe_plan(m, n, k).split(" workspace=")[0],
+           "l2": f"{len(sets)} operand sets rotated ({rotation_bytes / 1e6:.0f} MB per trip; L2 is 126 MB)", "steps": steps}
+    first_y = None
+    for mode in modes:
+        overlap = mode == "overlapped"
+
+        def step(i, overlap=overlap):
+            xq, xs, w_b, y = sets[i % len(sets)]
+            ops.fp8_gemm_rowwise(xq, w_b, xs, ws, out=y, workspace=workspace, overlap=overlap)
+
+        n_steps = steps
+        if min_seconds > 0.0:  # size the loop from a short probe so that it lasts at least min_seconds
+            probe = run.time_steps(step, 10, warmup)
+            n_steps = int(max(steps, min_seconds * 1e3 / probe + 1))
+        ms = run.time_steps(step, n_steps, warmup, sampler=sampler)
+        run.launches += n_steps
+        last = (n_steps - 1) % len(sets)
+        xq, xs, w_b, y = sets[last]
+        rec = {"us_per_step": round(ms * 1e3, 3), "tflops": round(flops / (ms * 1e-3) / 1e12, 2),
+               "gbs": round(alg_bytes / (ms * 1e-3) / 1e9, 1), "steps": n_steps}
+        if bound == "hbm":
+            rec["frac_of_hbm"] = round(rec["gbs"] / hbm_peak, 4)
+        else:
+            rec["frac_of_fp8_peak"] = round(rec["tflops"] / (fp8_sustained if min_seconds > 0 else fp8_peak), 4)
+        if first_y is None:
+            rec["parity"] = run.parity(f"{name} {mode}", y, xq, w_b, xs, ws, seed=m + n)
+            first_y = y.clone()
+        else:  # same operands, same buffer: the launch mode must not change a bit of the result
+            same = bool(torch.equal(y, first_y))
+            rec["parity"] = {"identical_to": modes[0], "ok": same}
+            if not same:
+                run.parity_failures.append(f"rank {run.rank}: {name} {mode}: differs from the {modes[0]} launches")
+        out[mode] = rec
+    out["peak"] = {"hbm_gbs": hbm_peak} if bound == "hbm" else {"fp8_tflops": fp8_sustained if min_seconds > 0 else fp8_peak}
+    out["peak_source"] = peak_note
+    return out
+
+
+def prefill_leg(run, steps, warmup):
+    """Strong scaling of the M = 65536 prefill problem: 65536 / world rows per rank, W replicated; the GEMM alone,
+    and the GEMM followed by the in-place NCCL all-gather that assembles Y on every rank."""
+    from tritonbench_b200 import lib, ops, quantize
+
+    world, rank, device = run.world, run.rank, run.device
+    m_total, n, k = PREFILL_M, PREFILL_N, PREFILL_K
+    rows = m_total // world
+    wq, ws = quantize.make_quantized(n, k, seed=run.shard.W_SEED, device=device)
+    xq, xs = quantize.make_quantized(rows, k, seed=run.shard.shard_seed(rank), device=device)
+    full, mine = run.shard.gathered_output(m_total, n, world, rank, device)
+    workspace = ops.get_workspace(device, ops.workspace_bytes(rows, n, k))
+    flops_total = 2.0 * m_total * n * k
+
+    def gemm(i):
+        ops.fp8_gemm_rowwise(xq, wq, xs, ws, out=mine, workspace=workspace)
+
+    ms = run.time_steps(gemm, steps, warmup)
+    run.launches += steps
+    out = {
+        "M_total": m_total, "N": n, "K": k, "rows_per_rank": rows, "scaling": "strong",
+        "plan": lib.describe_plan(rows, n, k).split(" workspace=")[0],
+        "l2": f"per-rank working set {(rows * k + n * k + 2 * rows * n) / 1e6:.0f} MB per step (L2 is 126 MB)",
+        "gemm_only": {"ms_per_step": round(ms, 4), "tflops_total": round(flops_total / (ms * 1e-3) / 1e12, 1),
+                      "tflops_per_gpu": round(flops_total / world / (ms * 1e-3) / 1e12, 1), "steps": steps,
+                      "parity": run.parity("prefill_65536 gemm", mine, xq, wq, xs, ws, seed=7)},
+    }
+    if run.grouped:
+        def gemm_gather(i):
+            ops.fp8_gemm_rowwise(xq, wq, xs, ws, out=mine, workspace=workspace)
+            run.shard.all_gather_rows(full, world)
+
+        ms_g = run.time_steps(gemm_gather, steps, warmup)
+        run.launches += steps
+        # the gathered buffer holds every rank's shard: check the rows of the NEXT rank's shard against the oracle
+        other = (rank + 1) % world
+        xq_o, xs_o = quantize.make_quantized(rows, k, seed=run.shard.shard_seed(other), device=device)
+        out["with_all_gather"] = {
+            "ms_per_step": round(ms_g, 4), "tflops_total": round(flops_total / (ms_g * 1e-3) / 1e12, 1), "steps": steps,
+            "gathered_bytes_per_rank": (world - 1) * 2 * rows * n,
+            "nvlink_gbs_if_serial": round((world - 1) * 2 * rows * n / max((ms_g - ms) * 1e-3, 1e-9) / 1e9, 1),
+            "how": "GEMM into this rank's slice of the [M,N] buffer, then in-place NCCL all_gather_into_tensor, same stream",
+            "parity": run.parity("prefill_65536 gathered shard of the next rank", full[other * rows:(other + 1) * rows],
+                                 xq_o, wq, xs_o, ws, seed=9),
+        }
+    return out
+
+
+def measure_pcie(device, nbytes=128 << 20, reps=3):
+    """Pinned host <-> device copy rates of this process, GB/s: each direction alone, and both at once."""
+    h_a = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    h_b = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d_a = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    d_b = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    s1, s2 = torch.cuda.Stream(device), torch.cuda.Stream(device)
+
+    def timed(fn):
+        best = float("inf")
+        for _ in range(reps + 1):
+            torch.cuda.synchronize(device)
+            t0 = time.perf_counter()
+            fn()
+            torch.cuda.synchronize(device)
+            best = min(best, time.perf_counter() - t0)
+        return best
+
+    def h2d():
+        with torch.cuda.stream(s1):
+            d_a.copy_(h_a, non_blocking=True)
+
+    def d2h():
+        with torch.cuda.stream(s2):
+            h_b.copy_(d_b, non_blocking=True)
+
+    def both():
+        h2d()
+        d2h()
+
+    t_up, t_down, t_both = timed(h2d), timed(d2h), timed(both)
+    return {"h2d_gbs": round(nbytes / t_up / 1e9, 2), "d2h_gbs": round(nbytes / t_down / 1e9, 2),
+            "duplex_gbs_per_direction": round(nbytes / t_both / 1e9, 2), "copy_bytes": nbytes}
+
+
+def e2e_leg(run, m, n, k, xq, xs, wq, ws, steps, flops_step_rank):
+    """Wall clock over `steps` synchronous host-buffer calls (each: H2D copies, kernels, D2H copies), max over ranks;
+    once with W sent by every call, once with W kept on the device; the last Y of each checked against the oracle."""
+    from tritonbench_b200 import ops
+
+    binding = NumaBinding(run.local_rank)
+    with binding:  # pinned pages are placed where the allocating thread runs
+        h_x = xq.view(torch.uint8).cpu().contiguous().pin_memory()
+        h_w = wq.view(torch.uint8).cpu().contiguous().pin_memory()
+        h_xs, h_ws = xs.cpu().pin_memory(), ws.cpu().pin_memory()
+        h_out = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+        pcie = measure_pcie(run.device)
     host = ops.HostGemm(m, n, k)
-    h_in = [t.cpu().contiguous().pin_memory() for t in (x_pair[0].view(torch.uint8), wq.view(torch.uint8), x_pair[1], ws)]
-    h_out = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
-    for _ in range(2):
-        host(*h_in, out=h_out)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        host(*h_in, out=h_out)
-    t_e2e = time.perf_counter() - t0
+
+    def loop(send_w: bool):
+        args = (h_x, h_w if send_w else None, h_xs, h_ws if send_w else None)
+        for _ in range(2):
+            host(*args, out=h_out)
+        run.barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            host(*args, out=h_out)
+        return run.max_over_ranks(time.perf_counter() - t0) / steps
+
+    t_full = loop(True)
+    parity_full = run.parity("e2e", h_out, xq, wq, xs, ws, seed=3)
+    h_out.fill_(0)
+    t_res = loop(False)  # W, w_scale of the last upload stay in the context
+    parity_res = run.parity("e2e weights resident", h_out, xq, wq, xs, ws, seed=4)
     host.close()
-    if grouped:
-        t = torch.tensor([t_e2e], dtype=torch.float64, device=device)
-        td.all_reduce(t, op=td.ReduceOp.MAX)
-        t_e2e = float(t.item())
-    return t_e2e, world * flops_step_rank * e2e_steps / t_e2e / 1e12
+    world = run.world
+    h2d = m * k + n * k + 4 * (m + n)
+    d2h = 2 * m * n
+    bound_s = max(h2d / (pcie["h2d_gbs"] * 1e9), d2h / (pcie["d2h_gbs"] * 1e9))
+    bound_res_s = max((m * k + 4 * m) / (pcie["h2d_gbs"] * 1e9), d2h / (pcie["d2h_gbs"] * 1e9))
+    return {
+        "value": world * flops_step_rank / t_full / 1e12,
+        "unit": UNIT,
+        "h2d_bytes_per_step": world * h2d,
+        "d2h_bytes_per_step": world * d2h,
+        "steps": steps,
+        "ms_per_step": t_full * 1e3,
+        "api": "b200fp8_gemm_rowwise_host (pinned host buffers in, pinned host buffer out, synchronous; X and W panels "
+               "uploaded alternately, blocks of Y downloaded as they complete)",
+        "pcie": pcie,
+        "pcie_bound_ms": bound_s * 1e3,
+        "pcie_frac": bound_s / t_full,
+        "pcie_frac_note": "max(h2d bytes / measured h2d rate, d2h bytes / measured d2h rate) / call time, rank 0's rates; "
+                          "1.0 would need uploads and downloads to overlap completely",
+        "aggregate_pcie_gbs": {"h2d": world * h2d / t_full / 1e9, "d2h": world * d2h / t_full / 1e9},
+        "numa": binding.note,
+        "parity": parity_full,
+        "weights_resident": {
+            "value": world * flops_step_rank / t_res / 1e12, "unit": UNIT, "ms_per_step": t_res * 1e3,
+            "h2d_bytes_per_step": world * (m * k + 4 * m), "d2h_bytes_per_step": world * d2h,
+            "pcie_frac": bound_res_s / t_res,
+            "api": "b200fp8_host_ctx_set_weights once, then b200fp8_gemm_rowwise_host with wq = NULL (X up, Y down)",
+            "parity": parity_res,
+        },
+    }
 
 
 def run_own(args, workload):
-    import torch.distributed as td
-
-    from tritonbench_b200 import dist as shard
     from tritonbench_b200 import lib, ops, quantize
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
-    lib.load()  # fail loudly when the CUDA library is missing
-
-    rank, local_rank, world = shard.env_rank_world()
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit(f"--gpus {args.gpus} needs a torchrun launch with {args.gpus} ranks")
-        args.gpus = world
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    grouped = shard.init_process_group("nccl") if world > 1 else False
-
+    run = Run(args)
+    rank, world, device = run.rank, run.world, run.device
     m, n, k, x_std, w_std, dist_name, bound = WORKLOADS[workload]
     steps, warmup = args.steps, max(args.warmup, 3)
+    fp8_peak, fp8_sustained, hbm_peak, peak_note = measured_peaks()
 
     # W from the common seed on every rank (replicated), this rank's X rows from its shard seed.
-    # Three X / Y buffers are rotated so that no step finds its X or Y in L2 from the step before.
-    n_buf = 3
-    wq, ws = quantize.make_quantized(n, k, seed=shard.W_SEED, device=device, dist=dist_name, std=w_std)
-    xs_list = [
-        quantize.make_quantized(m, k, seed=shard.shard_seed(rank) + 1000 * b, device=device, dist=dist_name, std=x_std)
-        for b in range(n_buf)
-    ]
-    outs = [torch.empty((m, n), dtype=torch.bfloat16, device=device) for _ in range(n_buf)]
+    # Operand sets are rotated so that no step finds its X or Y in L2 from the step before.
+    # (the headline workload keeps ONE W, as a serving job does: the 192 MB of X and Y that every step moves
+    # through the 126 MB L2 leave little of the 64 MB W behind)
+    sets, wq, ws, rotation_bytes = make_sets(quantize, m, n, k, dist_name, x_std, w_std, device, run.shard.shard_seed(rank),
+                                             run.shard.W_SEED, 2.2 * L2_BYTES, share_w=True if workload == "square_8192" else None)
     workspace = ops.get_workspace(device, ops.workspace_bytes(m, n, k))
-
     # decode shapes: successive steps may overlap (each kernel reads only W before its predecessor is done)
     overlap = m <= 128 and not args.no_overlap
 
     def step(i):
-        xq, xs = xs_list[i % n_buf]
-        ops.fp8_gemm_rowwise(xq, wq, xs, ws, out=outs[i % n_buf], workspace=workspace, overlap=overlap)
+        xq, xs, w_b, y = sets[i % len(sets)]
+        ops.fp8_gemm_rowwise(xq, w_b, xs, ws, out=y, workspace=workspace, overlap=overlap)
 
-    def barrier():
-        torch.cuda.synchronize(device)
-        if grouped:
-            td.barrier()
-        torch.cuda.synchronize(device)
-
-    for i in range(warmup):
-        step(i)
-    barrier()
-    sampler = ClockSampler(local_rank)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with sampler:
-        barrier()
-        e0.record()
-        for i in range(steps):
-            step(i)
-        e1.record()
-        barrier()
-    ops.check_device_status(device)
-    t_ms = e0.elapsed_time(e1)
-    if grouped:
-        t = torch.tensor([t_ms], dtype=torch.float64, device=device)
-        td.all_reduce(t, op=td.ReduceOp.MAX)
-        t_ms = float(t.item())
-    ms_per_step = t_ms / steps
+    sampler = ClockSampler(run.local_rank)
+    ms_per_step = run.time_steps(step, steps, warmup, sampler=sampler)
+    run.launches += steps
+    timed_launches = steps
     flops_step_rank = 2.0 * m * n * k
     value = world * flops_step_rank / (ms_per_step * 1e-3) / 1e12
+    last = sets[(steps - 1) % len(sets)]
+    parity = run.parity("main", last[3], last[0], last[2], last[1], ws, seed=1)
 
     # ---- end to end through the host-buffer C-ABI entry point ----
-    e2e_steps = 0 if args.kernel_only else min(steps, 10)
-    t_e2e, e2e_value = None, None
-    if e2e_steps:
-        t_e2e, e2e_value = time_e2e(ops, m, n, k, xs_list[0], wq, ws, e2e_steps, barrier, grouped, device, world, flops_step_rank)
-    h2d = world * (m * k + n * k + 4 * (m + n))
-    d2h = world * 2 * m * n
+    e2e = None
+    if not args.kernel_only:
+        e2e = e2e_leg(run, m, n, k, sets[0][0], sets[0][1], wq, ws, min(steps, 10), flops_step_rank)
 
-    # ---- optional: assemble Y on every rank with an in-place NCCL all-gather after each GEMM ----
+    # ---- the other benchmark configurations (default workload only) ----
+    also = None
+    if workload == "square_8192" and not args.kernel_only and not args.no_also:
+        also = {}
+        leg_steps = max(args.also_steps, 20)
+        for name in ("decode_m1", "decode_m16", "decode_m64", "decode_m128"):
+            mm, nn, kk, xs_, ws_, dn, bd = WORKLOADS[name]
+            also[name] = gemm_leg(run, name, (mm, nn, kk), dn, xs_, ws_, bd, max(leg_steps, 200), warmup,
+                                  modes=("ordinary", "overlapped"), x_seed=0)
+        for name in sorted(w for w in WORKLOADS if w.startswith("irregular_")):
+            mm, nn, kk, xs_, ws_, dn, bd = WORKLOADS[name]
+            also[name] = gemm_leg(run, name, (mm, nn, kk), dn, xs_, ws_, bd, leg_steps, warmup, x_seed=0)
+        also["prefill_65536"] = prefill_leg(run, max(10, min(steps, 20)), warmup)
+        sustained_sampler = ClockSampler(run.local_rank, period_s=0.02)
+        sus = gemm_leg(run, "sustained", (m, n, k), dist_name, x_std, w_std, bound, steps, warmup, sampler=sustained_sampler,
+                       min_seconds=args.sustained_seconds, share_w=True)
+        sus["clocks"] = sustained_sampler.summary()
+        sus["note"] = f"the headline workload back to back for at least {args.sustained_seconds} s; fraction of the sustained peak"
+        also["sustained_square_8192"] = sus
+
+    # ---- optional: the weak-scaling workload followed by an in-place NCCL all-gather of Y ----
     gather = None
-    if grouped and args.gather:
-        full, mine = shard.gathered_output(m * world, n, world, rank, device)
-        for i in range(2):
-            ops.fp8_gemm_rowwise(xs_list[0][0], wq, xs_list[0][1], ws, out=mine, workspace=workspace)
-            shard.all_gather_rows(full, world)
-        barrier()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        for i in range(steps):
-            xq, xs = xs_list[i % n_buf]
-            ops.fp8_gemm_rowwise(xq, wq, xs, ws, out=mine, workspace=workspace)
-            shard.all_gather_rows(full, world)
-        g1.record()
-        barrier()
-        t = torch.tensor([g0.elapsed_time(g1)], dtype=torch.float64, device=device)
-        td.all_reduce(t, op=td.ReduceOp.MAX)
-        g_ms = float(t.item()) / steps
+    if run.grouped and args.gather:
+        full, mine = run.shard.gathered_output(m * world, n, world, rank, device)
+
+        def gemm_gather(i):
+            xq, xs, w_b, _ = sets[i % len(sets)]
+            ops.fp8_gemm_rowwise(xq, w_b, xs, ws, out=mine, workspace=workspace)
+            run.shard.all_gather_rows(full, world)
+
+        g_ms = run.time_steps(gemm_gather, steps, 2)
         gather = {
             "ms_per_step": g_ms,
             "value": world * flops_step_rank / (g_ms * 1e-3) / 1e12,
@@ -328,25 +654,25 @@ def run_own(args, workload):
             "note": "GEMM into this rank's slice of the [M,N] buffer, then in-place NCCL all-gather, same stream",
         }
 
+    all_ok = run.all_true(not run.parity_failures)
     if rank == 0:
-        fp8_peak, hbm_peak, peak_note = measured_peaks()
         alg_bytes = m * k + n * k + 2 * m * n + 4 * (m + n)
+        plan = lib.describe_plan(m, n, k)
         if bound == "tensor":
             achieved = flops_step_rank / (ms_per_step * 1e-3) / 1e12
             roofline = {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak}
         else:
             achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9
             roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak}
-        roofline["traffic"] = NCU_TRAFFIC_BYTES.get(workload)
+        roofline["traffic"], roofline["traffic_source"] = ncu_traffic(workload, plan)
         roofline["peak_source"] = peak_note
-        roofline["kernel"] = lib.describe_plan(m, n, k).split(" ")[0]
+        roofline["kernel"] = plan.split(" ")[0]
         roofline["algorithmic_flops_per_launch"] = flops_step_rank
         roofline["algorithmic_bytes_per_launch"] = alg_bytes
 
         cpu = None
         if world == 1 and not args.kernel_only:
-            xq_h, xs_h = xs_list[0][0].cpu(), xs_list[0][1].cpu()
-            rate, threads, sample, _ = cpu_oracle_rate(xq_h, wq.cpu(), xs_h, ws.cpu(), target_seconds=12.0)
+            rate, threads, sample, _ = cpu_oracle_rate(sets[0][0].cpu(), wq.cpu(), sets[0][1].cpu(), ws.cpu(), target_seconds=12.0)
             cpu = {"value": rate, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
 
         line = {
@@ -370,32 +696,34 @@ def run_own(args, workload):
                 "K": k,
                 "sharding": f"rows of X and Y over {world} GPU(s), W replicated, no collective in the timed GEMM",
                 "inputs": f"X ~ {dist_name}(std {x_std}), W ~ {dist_name}(std {w_std}), rowwise e4m3, fp32 scales; W seed 0, X seed 1+rank",
-                "l2": f"{n_buf} X and Y buffers rotated; per-step working set {alg_bytes / 1e6:.0f} MB (L2 is 126 MB)",
-                "plan": lib.describe_plan(m, n, k),
+                "l2": f"{len(sets)} X and Y buffers rotated, {rotation_bytes / 1e6:.0f} MB per trip; per-step working set "
+                      f"{alg_bytes / 1e6:.0f} MB (L2 is 126 MB)",
+                "plan": plan,
                 "launch": "programmatic dependent launch: a step may start (prefetching W only) before the previous step has finished"
                 if overlap else "stream-ordered launches",
             },
             "roofline": roofline,
             "cpu_baseline": cpu,
-            "e2e": None if not e2e_steps else {
-                "value": e2e_value,
-                "unit": UNIT,
-                "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h,
-                "steps": e2e_steps,
-                "ms_per_step": t_e2e / e2e_steps * 1e3,
-                "api": "b200fp8_gemm_rowwise_host (pinned host buffers in, pinned host buffer out, synchronous)",
-            },
-            "gpu_launches": steps * world,
-            "gpu_launches_per_rank": steps,
+            "e2e": e2e,
+            "parity": parity,
+            "parity_all_legs_ok": all_ok,
+            "gpu_launches": timed_launches * world,
+            "gpu_launches_per_rank": timed_launches,
+            "gpu_launches_all_legs_per_rank": run.launches,
             "clocks": sampler.summary(),
         }
+        if also is not None:
+            line["also"] = also
         if gather is not None:
             line["with_all_gather"] = gather
         print(json.dumps(line), flush=True)
-    if grouped:
-        td.barrier()
-        td.destroy_process_group()
+    if run.parity_failures:
+        print("PARITY FAILURE\n" + "\n".join(run.parity_failures), file=sys.stderr, flush=True)
+    if run.grouped:
+        run.td.barrier()
+        run.td.destroy_process_group()
+    if not all_ok:
+        sys.exit(3)
 
 
 def main():
@@ -405,10 +733,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="square_8192")
-    ap.add_argument("--gather", action="store_true", help="N>1: also time GEMM + in-place NCCL all-gather of Y")
+    ap.add_argument("--gather", action="store_true", help="N>1: also time the weak-scaling GEMM + in-place NCCL all-gather of Y")
     ap.add_argument("--no-overlap", action="store_true", help="decode workloads: plain stream-ordered launches")
+    ap.add_argument("--no-also", action="store_true", help="default workload: skip the legs for the other configurations")
+    ap.add_argument("--also-steps", type=int, default=200, help="timed steps of each leg under `also`")
+    ap.add_argument("--sustained-seconds", type=float, default=1.0)
     ap.add_argument("--kernel-only", action="store_true",
-                    help="skip the end-to-end and CPU-baseline legs (for short profiler captures; not a bench run)")
+                    help="only the device-timed loop of the workload (for short profiler captures; not a bench run)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args, args.workload)
