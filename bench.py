@@ -470,14 +470,44 @@ def prefill_leg(run, steps, warmup):
         # the gathered buffer holds every rank's shard: check the rows of the NEXT rank's shard against the oracle
         other = (rank + 1) % world
         xq_o, xs_o = quantize.make_quantized(rows, k, seed=run.shard.shard_seed(other), device=device)
+        gathered = (world - 1) * 2 * rows * n
         out["with_all_gather"] = {
             "ms_per_step": round(ms_g, 4), "tflops_total": round(flops_total / (ms_g * 1e-3) / 1e12, 1), "steps": steps,
-            "gathered_bytes_per_rank": (world - 1) * 2 * rows * n,
-            "nvlink_gbs_if_serial": round((world - 1) * 2 * rows * n / max((ms_g - ms) * 1e-3, 1e-9) / 1e9, 1),
+            "gathered_bytes_per_rank": gathered,
+            "nvlink_gbs_if_serial": round(gathered / max((ms_g - ms) * 1e-3, 1e-9) / 1e9, 1),
             "how": "GEMM into this rank's slice of the [M,N] buffer, then in-place NCCL all_gather_into_tensor, same stream",
             "parity": run.parity("prefill_65536 gathered shard of the next rank", full[other * rows:(other + 1) * rows],
                                  xq_o, wq, xs_o, ws, seed=9),
         }
+        # the same result from ONE kernel per rank: the GEMM's epilogue stores every tile into all ranks' copies of Y
+        # (peer memory over NVLink); a one-element all-reduce orders the ranks after each step
+        shared = run.shard.SharedRows(m_total, n, world, rank, device)
+        copies = shared.my_rows_everywhere()
+        token = torch.zeros(1, device=device)
+
+        def fused(i):
+            ops.fp8_gemm_rowwise_gather(xq, wq, xs, ws, copies, ldy=n, workspace=workspace)
+            run.td.all_reduce(token)
+
+        ms_f = run.time_steps(fused, steps, warmup)
+        run.launches += steps
+        same = bool(torch.equal(shared.full, full))
+        if not same:
+            run.parity_failures.append(f"rank {rank}: prefill_65536 fused gather differs from GEMM + NCCL all-gather")
+        out["with_fused_all_gather"] = {
+            "ms_per_step": round(ms_f, 4), "tflops_total": round(flops_total / (ms_f * 1e-3) / 1e12, 1), "steps": steps,
+            "gathered_bytes_per_rank": gathered,
+            "nvlink_gbs_out_per_gpu": round(gathered / (ms_f * 1e-3) / 1e9, 1),
+            "nvlink_floor_ms": round(gathered / 770e9 * 1e3, 4),
+            "how": "b200fp8_gemm_rowwise_gather: each tile TMA-stored into every rank's copy of Y (CUDA IPC mappings) from the "
+                   "epilogue, then a one-element NCCL all-reduce as the barrier between ranks; nvlink_floor_ms = bytes a GPU "
+                   "must send / 770 GB/s (the measured peer-copy rate)",
+            "identical_to_nccl_path": same,
+            "parity": run.parity("prefill_65536 fused gather, shard of the next rank", shared.full[other * rows:(other + 1) * rows],
+                                 xq_o, wq, xs_o, ws, seed=10),
+        }
+        run.barrier()
+        shared.close()
     return out
 
 

@@ -97,6 +97,37 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
                          void* cuda_stream);
 
 /*
+ * The GEMM with its result written to several buffers at once: the fused form of "GEMM, then all-gather of Y" of
+ * a run that shards X by rows over the GPUs of one node.  y_copies[0..num_copies) are device pointers, valid in
+ * this process, to where THIS call's M rows of Y belong inside each copy of the gathered matrix: y_copies[0] in
+ * the caller's own buffer, the others inside the other GPUs' buffers mapped into this process (CUDA IPC, see
+ * b200fp8_shared_buffer_*).  All copies share the row pitch ldy (elements, a multiple of 8) and must be 16-byte
+ * aligned.  The epilogue TMA-stores every 32 x 64 box of a tile to all copies (peer copies travel over NVLink as
+ * plain stores; no kernel reads another GPU's memory), tile by tile while the next tile is multiplied, so the
+ * exchange overlaps the arithmetic.  At most 8 copies.  Large-M kernels only (flags: AUTO, TC_1CTA, TC_2CTA,
+ * OUT_FP16).  The call returns when the kernel is enqueued; rows written into another GPU's buffer may be read
+ * there only after that GPU's process has synchronised with this stream (a barrier between the ranks).
+ * Replaces: nothing in the reference (it has no multi-GPU code); the unfused form is b200fp8_gemm_rowwise
+ * followed by an NCCL all-gather.
+ */
+int b200fp8_gemm_rowwise_gather(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
+                                const void* bias_bf16, void* const* y_copies, int num_copies, int64_t M, int64_t N,
+                                int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, void* workspace,
+                                size_t workspace_bytes, uint32_t flags, void* cuda_stream);
+/*
+ * Device buffers another process of the same node can map, for the gathered Y above.  create: cudaMalloc on the
+ * current device plus its CUDA IPC handle (B200FP8_IPC_HANDLE_BYTES bytes, to be sent to the other processes by
+ * whatever channel the caller has); open: map a buffer created by another process, on another GPU, into this one
+ * (peer access is enabled on first use); close undoes open, destroy undoes create.  Replaces: nothing in the
+ * reference.
+ */
+#define B200FP8_IPC_HANDLE_BYTES 64u
+int b200fp8_shared_buffer_create(size_t bytes, void** device_ptr, void* handle_out, size_t handle_bytes);
+int b200fp8_shared_buffer_open(const void* handle_in, size_t handle_bytes, void** device_ptr);
+int b200fp8_shared_buffer_close(void* device_ptr);
+int b200fp8_shared_buffer_destroy(void* device_ptr);
+
+/*
  * The same GEMM for M <= 128 WITHOUT any caller-provided workspace and without a single allocation.
  * (No counterpart in the reference: FBGEMM's wrappers allocate their output and temporaries per call.)
  *

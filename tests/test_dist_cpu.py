@@ -26,6 +26,28 @@ def test_shard_rows_cover_the_problem_without_overlap():
         shard.shard_rows(8, 2, 2)
 
 
+def test_fused_gather_bookkeeping_every_rank_writes_its_rows_into_every_copy():
+    """Host logic of the gather-fused GEMM: rank r writes rows [r*M/G, (r+1)*M/G) at the same byte offset of every
+    copy, its own copy first.  Emulated on numpy buffers: after all ranks have 'stored', every copy is complete."""
+    import numpy as np
+
+    m_total, n = 64, 24
+    for world in (1, 2, 4, 8):
+        truth = np.arange(m_total * n, dtype=np.uint16).reshape(m_total, n)
+        copies = [np.zeros(m_total * n * 2, dtype=np.uint8) for _ in range(world)]
+        for rank in range(world):
+            order = shard.copy_order(world, rank)
+            assert order[0] == rank and sorted(order) == list(range(world))
+            off = shard.slice_byte_offset(m_total, n, world, rank)
+            r0, r1 = shard.shard_rows(m_total, world, rank)
+            assert off == r0 * n * 2
+            payload = truth[r0:r1].tobytes()
+            for dest in order:
+                copies[dest][off:off + len(payload)] = np.frombuffer(payload, dtype=np.uint8)
+        for c in copies:
+            assert np.array_equal(c.view(np.uint16).reshape(m_total, n), truth)
+
+
 def test_shard_inputs_use_a_common_w_and_distinct_x():
     a = shard.make_shard_inputs(M_TOTAL, N, K, 2, 0, "cpu")
     b = shard.make_shard_inputs(M_TOTAL, N, K, 2, 1, "cpu")

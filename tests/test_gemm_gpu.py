@@ -265,6 +265,50 @@ def test_config4_whole_prefill_problem_in_one_launch(cuda_device):
     ops.check_device_status()
 
 
+@pytest.mark.parametrize("variant,shape,ranks", [("tc_2cta", (1024, 2048, 1024), 4), ("tc_1cta", (300, 520, 400), 3),
+                                                 ("auto", (513, 1000, 256), 8), ("auto", (128, 256, 128), 2)])
+def test_gather_fused_gemm_writes_every_copy_of_y(cuda_device, variant, shape, ranks):
+    """The fused GEMM + all-gather on one GPU: `ranks` copies of the gathered [ranks*M, N] matrix stand in for the
+    other GPUs' buffers.  The rows of 'rank 1' must arrive in every copy, equal to the plain GEMM bit for bit, and
+    no other row of any copy may be touched."""
+    ops = _ops()
+    m, n, k = shape
+    xq, wq, xs, ws = _gpu(*_inputs(m, n, k, seed=m + ranks))
+    bias = torch.randn(n, device="cuda").to(torch.bfloat16)
+    want = ops.fp8_gemm_rowwise(xq, wq, xs, ws, bias=bias, variant=variant if variant != "auto" else "tc_1cta")
+    _assert_close(want, orc.gemm_rowwise(xq.cpu(), wq.cpu(), xs.cpu(), ws.cpu(), bias.cpu()), "plain")
+    rank = 1
+    copies = [torch.full((ranks * m, n), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(ranks)]
+    order = [rank] + [r for r in range(ranks) if r != rank]
+    ptrs = [copies[r][rank * m:].data_ptr() for r in order]
+    ops.fp8_gemm_rowwise_gather(xq, wq, xs, ws, ptrs, ldy=n, bias=bias, variant=variant)
+    ops.check_device_status()
+    for r in range(ranks):
+        got = copies[r][rank * m:(rank + 1) * m]
+        _assert_close(got, want, f"copy {r}")  # the same kernel arithmetic; the variants may differ in the last bit
+        assert bool((copies[r][: rank * m] == 7.0).all()) and bool((copies[r][(rank + 1) * m:] == 7.0).all()), f"copy {r}"
+    assert all(torch.equal(copies[r][rank * m:(rank + 1) * m], copies[0][rank * m:(rank + 1) * m]) for r in range(ranks))
+    with pytest.raises(Exception):
+        ops.fp8_gemm_rowwise_gather(xq, wq, xs, ws, ptrs + ptrs + ptrs + ptrs + ptrs, ldy=n)  # more than 8 copies
+    with pytest.raises(NotImplementedError):
+        ops.fp8_gemm_rowwise_gather(xq, wq, xs, ws, [ptrs[0] + 2], ldy=n)  # rows of Y must be 16-byte aligned
+
+
+def test_shared_rows_buffer_on_one_rank(cuda_device):
+    """The IPC-exportable buffer behaves like any tensor when there is a single rank."""
+    from tritonbench_b200 import dist
+
+    ops = _ops()
+    m, n, k = 256, 512, 256
+    xq, wq, xs, ws = _gpu(*_inputs(m, n, k, seed=5))
+    rows = dist.SharedRows(m, n, 1, 0, torch.device("cuda", 0))
+    assert tuple(rows.full.shape) == (m, n) and rows.full.dtype == torch.bfloat16 and rows.mine.data_ptr() == rows.full.data_ptr()
+    ops.fp8_gemm_rowwise_gather(xq, wq, xs, ws, rows.my_rows_everywhere(), ldy=n)
+    ops.check_device_status()
+    _assert_close(rows.full, orc.gemm_rowwise(xq.cpu(), wq.cpu(), xs.cpu(), ws.cpu()), "shared rows, one rank")
+    rows.close()
+
+
 # ------------------------------------------------------------------ against the reference's own library call
 def _scaled_mm_rowwise(xq, wq, xs, ws):
     """The torch baseline the operator itself names for this GEMM (tritonbench/operators/fp8_gemm_rowwise/

@@ -431,6 +431,118 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
   return note_cuda(launch_gemm_tc<1>(tm_x, tm_w, tm_y, tp, pl.num_ctas, stream));
 }
 
+int b200fp8_gemm_rowwise_gather(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
+                                const void* bias_bf16, void* const* y_copies, int num_copies, int64_t M, int64_t N,
+                                int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, void* workspace,
+                                size_t workspace_bytes, uint32_t flags, void* cuda_stream) {
+  if (xq == nullptr || wq == nullptr || x_scale == nullptr || w_scale == nullptr || y_copies == nullptr ||
+      workspace == nullptr) {
+    return B200FP8_BAD_ARG;
+  }
+  if (num_copies < 1 || num_copies > 1 + kMaxExtraOutputs) return B200FP8_BAD_ARG;
+  int st = check_sizes(M, N, K);
+  if (st != B200FP8_OK) return st;
+  if (ldx < K || ldw < K || ldy < N) return B200FP8_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0 || workspace_bytes < B200FP8_WORKSPACE_HEADER_BYTES) {
+    return B200FP8_BAD_ARG;
+  }
+  uint32_t variant = flags & B200FP8_VARIANT_MASK;
+  if (variant != B200FP8_VARIANT_AUTO && variant != B200FP8_VARIANT_TC_1CTA && variant != B200FP8_VARIANT_TC_2CTA) {
+    return B200FP8_BAD_ARG;
+  }
+  DeviceInfo dev;
+  st = device_info(&dev);
+  if (st != B200FP8_OK) return st;
+  if (dev.cc_major != 10) return B200FP8_UNSUPPORTED_ARCH;
+  // every copy is written with TMA stores only: all of them need 16-byte aligned rows
+  if (!tma_loadable(K, ldx, ldw, xq, wq) || ldy % 8 != 0) return B200FP8_UNSUPPORTED_ALIGNMENT;
+  for (int i = 0; i < num_copies; ++i) {
+    if (y_copies[i] == nullptr) return B200FP8_BAD_ARG;
+    if (!aligned16(y_copies[i])) return B200FP8_UNSUPPORTED_ALIGNMENT;
+  }
+  if (variant == B200FP8_VARIANT_AUTO) {
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    variant = pair_tiles >= dev.sm_count / 2 ? B200FP8_VARIANT_TC_2CTA : B200FP8_VARIANT_TC_1CTA;
+  }
+  const int cta_group = variant == B200FP8_VARIANT_TC_2CTA ? 2 : 1;
+  CUtensorMap tm_x, tm_w, tm_y;
+  st = encode_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, M, K, ldx, TcGeometry::kBlockK, TcGeometry::kBlockM);
+  if (st != B200FP8_OK) return st;
+  st = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, N, K, ldw, TcGeometry::kBlockK,
+                 TcGeometry::kBlockN / cta_group);
+  if (st != B200FP8_OK) return st;
+  st = encode_2d(&tm_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y_copies[0], M, N, ldy * 2, TcGeometry::kStoreCols,
+                 TcGeometry::kStoreRows);
+  if (st != B200FP8_OK) return st;
+  ExtraOutputs extra;
+  memset(&extra, 0, sizeof(extra));
+  for (int i = 1; i < num_copies; ++i) {
+    st = encode_2d(&extra.tm[i - 1], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, y_copies[i], M, N, ldy * 2,
+                   TcGeometry::kStoreCols, TcGeometry::kStoreRows);
+    if (st != B200FP8_OK) return st;
+  }
+  TcParams tp = {};
+  tp.x_scale = x_scale;
+  tp.w_scale = w_scale;
+  tp.bias = static_cast<const __nv_bfloat16*>(bias_bf16);
+  tp.y = static_cast<__nv_bfloat16*>(y_copies[0]);
+  tp.M = static_cast<int>(M);
+  tp.N = static_cast<int>(N);
+  tp.K = static_cast<int>(K);
+  tp.ldy = ldy;
+  tp.use_tma_store = 1;
+  tp.out_fp16 = (flags & B200FP8_FLAG_OUT_FP16) ? 1 : 0;
+  tp.group_m = 8;
+  tp.num_extra = num_copies - 1;
+  tp.status = static_cast<uint32_t*>(workspace);
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (cta_group == 2) {
+    const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    const int64_t clusters = tiles < dev.max_pair_clusters ? tiles : dev.max_pair_clusters;
+    return note_cuda(launch_gemm_tc<2>(tm_x, tm_w, tm_y, tp, static_cast<int>(2 * clusters), stream, &extra));
+  }
+  const int64_t tiles = ((M + 127) / 128) * ((N + 255) / 256);
+  const int ctas = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
+  return note_cuda(launch_gemm_tc<1>(tm_x, tm_w, tm_y, tp, ctas, stream, &extra));
+}
+
+// ---- device buffers that other processes of the node can map (CUDA IPC): where the gathered Y lives ----
+int b200fp8_shared_buffer_create(size_t bytes, void** device_ptr, void* handle_out, size_t handle_bytes) {
+  if (bytes == 0 || device_ptr == nullptr || handle_out == nullptr) return B200FP8_BAD_ARG;
+  if (handle_bytes < sizeof(cudaIpcMemHandle_t)) return B200FP8_BAD_ARG;
+  *device_ptr = nullptr;
+  void* ptr = nullptr;
+  cudaError_t e = cudaMalloc(&ptr, bytes);
+  if (e != cudaSuccess) return note_cuda(e);
+  cudaIpcMemHandle_t handle;
+  e = cudaIpcGetMemHandle(&handle, ptr);
+  if (e != cudaSuccess) {
+    cudaFree(ptr);
+    return note_cuda(e);
+  }
+  memcpy(handle_out, &handle, sizeof(handle));
+  *device_ptr = ptr;
+  return B200FP8_OK;
+}
+
+int b200fp8_shared_buffer_open(const void* handle_in, size_t handle_bytes, void** device_ptr) {
+  if (handle_in == nullptr || device_ptr == nullptr || handle_bytes < sizeof(cudaIpcMemHandle_t)) return B200FP8_BAD_ARG;
+  cudaIpcMemHandle_t handle;
+  memcpy(&handle, handle_in, sizeof(handle));
+  *device_ptr = nullptr;
+  return note_cuda(cudaIpcOpenMemHandle(device_ptr, handle, cudaIpcMemLazyEnablePeerAccess));
+}
+
+int b200fp8_shared_buffer_close(void* device_ptr) {
+  if (device_ptr == nullptr) return B200FP8_BAD_ARG;
+  return note_cuda(cudaIpcCloseMemHandle(device_ptr));
+}
+
+int b200fp8_shared_buffer_destroy(void* device_ptr) {
+  if (device_ptr == nullptr) return B200FP8_BAD_ARG;
+  return note_cuda(cudaFree(device_ptr));
+}
+
 int b200fp8_gemm_rowwise_noalloc(const void* xq, const void* wq, const float* x_scale, const float* w_scale,
                                  const void* bias_bf16, void* y_bf16, int64_t M, int64_t N, int64_t K, int64_t ldx,
                                  int64_t ldw, int64_t ldy, void* cuda_stream) {

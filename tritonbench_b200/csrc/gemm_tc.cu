@@ -19,6 +19,10 @@
 // writes rows of the next group: boxes that straddle a group's end are stored with plain predicated
 // stores instead of TMA.
 //
+// Gathered output (the sharded run): a tile's boxes are TMA-stored not only into Y but into up to seven more
+// buffers - the other GPUs' copies of the gathered matrix, reached through peer mappings - so the all-gather of
+// Y travels over NVLink from inside the epilogue, tile by tile, while the tensor cores multiply the next tile.
+//
 // The accumulator is double buffered in TMEM, so the epilogue of tile i overlaps the main loop
 // of tile i+1.  Every mbarrier wait is bounded (ptx.cuh: mbar_wait); on a time-out the kernel
 // records a status word and all roles fall through to the common exit, which frees TMEM.
@@ -114,7 +118,7 @@ __device__ __forceinline__ TileInfo tile_info(const TileSpace& ts, int t, uint32
 template <int kCtaGroup>
 __global__ void __launch_bounds__(TcGeometry::kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-               const __grid_constant__ CUtensorMap tm_y, const TcParams p) {
+               const __grid_constant__ CUtensorMap tm_y, const TcParams p, const __grid_constant__ ExtraOutputs extra) {
   using Cfg = TcConfig<kCtaGroup>;
   constexpr bool kPair = kCtaGroup == 2;
   constexpr int kStages = Cfg::kStages;
@@ -168,6 +172,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     prefetch_tensormap(&tm_x);
     prefetch_tensormap(&tm_w);
     if (p.use_tma_store) prefetch_tensormap(&tm_y);
+    for (int e = 0; e < p.num_extra; ++e) prefetch_tensormap(&extra.tm[e]);
     if constexpr (!kPair) {
       // Single CTA: the first pass over the ring needs no waiting, so it starts before the set-up barrier
       // (a CTA pair cannot: the peer's loads credit the leader's barriers, which must exist first).
@@ -388,6 +393,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
           __syncwarp();
           if (lane == 0 && row0 < row_limit && box_col < p.N) {
             tma_store_2d(&tm_y, sbuf, box_col, row0);
+            // gathered output: the same box into every other copy of Y (peer GPUs' memory over NVLink); the
+            // stores share this box's bulk group, so the staging buffer is reused only when all have read it
+            for (int e = 0; e < p.num_extra; ++e) tma_store_2d(&extra.tm[e], sbuf, box_col, row0);
           }
           if (lane == 0) tma_store_commit();
           ++store_count;
@@ -415,7 +423,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
 
 template <int kCtaGroup>
 cudaError_t launch_gemm_tc(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
-                           const TcParams& p, int num_ctas, cudaStream_t stream) {
+                           const TcParams& p, int num_ctas, cudaStream_t stream, const ExtraOutputs* extra) {
+  static const ExtraOutputs no_extra = {};
+  if (extra == nullptr) {
+    if (p.num_extra != 0) return cudaErrorInvalidValue;
+    extra = &no_extra;
+  }
   using Cfg = TcConfig<kCtaGroup>;
   auto kernel = gemm_tc_kernel<kCtaGroup>;
   // Opt in to the large dynamic shared-memory size once per device.
@@ -444,12 +457,12 @@ cudaError_t launch_gemm_tc(const CUtensorMap& tm_x, const CUtensorMap& tm_w, con
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, tm_x, tm_w, tm_y, p);
+  return cudaLaunchKernelEx(&cfg, kernel, tm_x, tm_w, tm_y, p, *extra);
 }
 
 template cudaError_t launch_gemm_tc<1>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&,
-                                       int, cudaStream_t);
+                                       int, cudaStream_t, const ExtraOutputs*);
 template cudaError_t launch_gemm_tc<2>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const TcParams&,
-                                       int, cudaStream_t);
+                                       int, cudaStream_t, const ExtraOutputs*);
 
 }  // namespace b200fp8

@@ -47,12 +47,21 @@ struct TcParams {
   int group_m;         // tile-rasterisation group height (tiles)
   int num_groups;      // 0: plain GEMM.  >0: rows of X are partitioned into groups (single-CTA variant)
   const int* group_rows;  // [num_groups] rows per group, device memory; group g uses W rows [g*N, (g+1)*N)
+  int num_extra;       // copies of Y to write besides `y` (TMA stores only; 0 for the plain GEMM)
   uint32_t* status;    // device status word
+};
+
+// Extra destinations of every tile of Y: the same rows inside other buffers - in the sharded run, the copies
+// of the gathered [M_total, N] matrix that live on the other GPUs, mapped into this process.  Each map covers
+// the [M, N] slice of its buffer where this rank's rows belong, so a box has the same coordinates in all of them.
+constexpr int kMaxExtraOutputs = 7;
+struct alignas(64) ExtraOutputs {
+  CUtensorMap tm[kMaxExtraOutputs];
 };
 
 template <int kCtaGroup>
 cudaError_t launch_gemm_tc(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
-                           const TcParams& p, int num_ctas, cudaStream_t stream);
+                           const TcParams& p, int num_ctas, cudaStream_t stream, const ExtraOutputs* extra = nullptr);
 
 // One 128 x block_n tile per cluster of `split` CTAs, K split over the cluster and reduced over distributed
 // shared memory (gemm_splitk.cu).  split is 1, 2, 4 or 8; block_n a multiple of 16 * split, at most 256.

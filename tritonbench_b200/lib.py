@@ -47,6 +47,7 @@ VARIANTS = {
     "tc_splitk": VARIANT_TC_SPLITK,
 }
 WORKSPACE_HEADER_BYTES = 256
+IPC_HANDLE_BYTES = 64
 
 # every symbol include/b200fp8.h declares
 EXPORTED_SYMBOLS = (
@@ -64,6 +65,11 @@ EXPORTED_SYMBOLS = (
     "b200fp8_host_ctx_set_weights",
     "b200fp8_host_ctx_set_panels",
     "b200fp8_gemm_rowwise_noalloc",
+    "b200fp8_gemm_rowwise_gather",
+    "b200fp8_shared_buffer_create",
+    "b200fp8_shared_buffer_open",
+    "b200fp8_shared_buffer_close",
+    "b200fp8_shared_buffer_destroy",
     "b200fp8_noalloc_status",
     "b200fp8_row_quantize",
     "b200fp8_fused_row_quantize",
@@ -126,6 +132,18 @@ def load() -> ctypes.CDLL:
     lib.b200fp8_host_ctx_set_panels.argtypes = [c_void_p, c_int64, c_int64]
     lib.b200fp8_gemm_rowwise_noalloc.restype = ctypes.c_int
     lib.b200fp8_gemm_rowwise_noalloc.argtypes = [c_void_p] * 6 + [c_int64] * 6 + [c_void_p]
+    lib.b200fp8_gemm_rowwise_gather.restype = ctypes.c_int
+    lib.b200fp8_gemm_rowwise_gather.argtypes = (
+        [c_void_p] * 5 + [ctypes.POINTER(c_void_p), ctypes.c_int] + [c_int64] * 6 + [c_void_p, c_size_t, c_uint32, c_void_p]
+    )
+    lib.b200fp8_shared_buffer_create.restype = ctypes.c_int
+    lib.b200fp8_shared_buffer_create.argtypes = [c_size_t, ctypes.POINTER(c_void_p), c_void_p, c_size_t]
+    lib.b200fp8_shared_buffer_open.restype = ctypes.c_int
+    lib.b200fp8_shared_buffer_open.argtypes = [c_void_p, c_size_t, ctypes.POINTER(c_void_p)]
+    lib.b200fp8_shared_buffer_close.restype = ctypes.c_int
+    lib.b200fp8_shared_buffer_close.argtypes = [c_void_p]
+    lib.b200fp8_shared_buffer_destroy.restype = ctypes.c_int
+    lib.b200fp8_shared_buffer_destroy.argtypes = [c_void_p]
     lib.b200fp8_noalloc_status.restype = ctypes.c_int
     lib.b200fp8_noalloc_status.argtypes = [ctypes.POINTER(c_uint32)]
     lib.b200fp8_gemm_rowwise_grouped.restype = ctypes.c_int

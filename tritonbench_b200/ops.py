@@ -6,7 +6,7 @@ Mirrors the call the reference backends make,
 (tritonbench/operators/fp8_gemm_rowwise/operator.py:187-217): same argument order and meaning,
 a fresh bf16 [M, N] tensor as the result.
 """
-from typing import Callable, Dict, Optional, Tuple
+from typing import Callable, Dict, Optional, Sequence, Tuple
 
 import torch
 
@@ -114,6 +114,48 @@ def fp8_gemm_rowwise(
     )
     _lib.check(status, f"b200fp8_gemm_rowwise(M={m}, N={n}, K={k}, variant={variant})")
     return out
+
+
+def fp8_gemm_rowwise_gather(
+    xq: torch.Tensor,
+    wq: torch.Tensor,
+    x_scale: torch.Tensor,
+    w_scale: torch.Tensor,
+    y_copies: Sequence[int],
+    ldy: int,
+    bias: Optional[torch.Tensor] = None,
+    variant: str = "auto",
+    workspace: Optional[torch.Tensor] = None,
+) -> None:
+    """The GEMM with every tile of Y stored into several buffers at once (b200fp8_gemm_rowwise_gather): the fused
+    form of GEMM + all-gather of a run sharded by rows.  y_copies are device addresses (valid in this process; the
+    first one local, the others usually peer GPUs' memory mapped through dist.SharedRows) of where this call's M
+    rows belong in each copy of the gathered matrix; ldy is their common row pitch in elements.  Asynchronous on the
+    current stream; the ranks must synchronise with each other before anyone reads rows another rank wrote."""
+    for t, name in ((xq, "xq"), (wq, "wq"), (x_scale, "x_scale"), (w_scale, "w_scale")):
+        _require_cuda(t, name)
+    if xq.dim() != 2 or wq.dim() != 2 or xq.shape[1] != wq.shape[1] or xq.stride(1) != 1 or wq.stride(1) != 1:
+        raise ValueError("xq and wq must be [M, K] and [N, K] with K contiguous")
+    m, k = xq.shape
+    n = wq.shape[0]
+    if x_scale.dtype != torch.float32 or w_scale.dtype != torch.float32 or x_scale.numel() != m or w_scale.numel() != n:
+        raise ValueError("scales must be float32 with M and N elements")
+    if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != n or not bias.is_cuda):
+        raise ValueError("bias must be a CUDA bfloat16 tensor with N elements")
+    copies = [int(p) for p in y_copies]
+    if not 1 <= len(copies) <= 8:
+        raise ValueError("between 1 and 8 copies of Y")
+    if workspace is None:
+        workspace = get_workspace(xq.device, _lib.WORKSPACE_HEADER_BYTES)
+    import ctypes
+
+    arr = (ctypes.c_void_p * len(copies))(*copies)
+    status = _lib.load().b200fp8_gemm_rowwise_gather(
+        xq.data_ptr(), wq.data_ptr(), x_scale.contiguous().data_ptr(), w_scale.contiguous().data_ptr(),
+        bias.data_ptr() if bias is not None else None, arr, len(copies), m, n, k, xq.stride(0), wq.stride(0), ldy,
+        workspace.data_ptr(), workspace.numel(), _lib.VARIANTS[variant], torch.cuda.current_stream(xq.device).cuda_stream,
+    )
+    _lib.check(status, f"b200fp8_gemm_rowwise_gather(M={m}, N={n}, K={k}, copies={len(copies)})")
 
 
 def fp8_row_quantize(x: torch.Tensor, recipe: str = "operator") -> Tuple[torch.Tensor, torch.Tensor]:
