@@ -47,7 +47,8 @@ typedef enum b200fp8_status {
 #define B200FP8_VARIANT_SKINNY 3u    /* M <= 128: swap-AB tcgen05 stream-K, persistent; for outputs too wide for TC_SPLITK */
 #define B200FP8_VARIANT_SIMT 4u      /* CUDA-core kernel, any alignment; slow, used as an on-GPU cross-check */
 #define B200FP8_VARIANT_TC_SPLITK 5u /* few tiles (decode, small M x N): one 128 x BN tile (BN <= 256) per cluster of
-                                        1/2/4/8 CTAs that split K and reduce over distributed shared memory   */
+                                        1/2/4/8 CTAs that split K and reduce over distributed shared memory, or one
+                                        128 x BN tile (BN <= 512) per CTA when that covers the output in one wave */
 #define B200FP8_VARIANT_MASK 0xFu
 #define B200FP8_FLAG_NO_TMA_STORE 0x10u /* tcgen05 variants: write Y with plain stores instead of TMA        */
 /* TC_SPLITK and SKINNY kernels only (what `auto` picks for M <= 128): launch with programmatic stream
@@ -59,8 +60,9 @@ typedef enum b200fp8_status {
  * scales, tritonbench/operators/fp8_gemm/fp8_gemm.py:88-101); same 16-bit storage, same leading dimension. */
 #define B200FP8_FLAG_OUT_FP16 0x40u
 
-/* TC_SPLITK only, bits 8-16: force the tile width (a multiple of 16 x split, at most 256) and the cluster
- * size (1, 2, 4 or 8) instead of the library's cost model; 0 in a field lets the library choose it.
+/* TC_SPLITK only, bits 8-16: force the tile width (a multiple of 16 x split, at most 256; with split 1 also a
+ * multiple of 64 from 320 to 448, a wide tile multiplied as two column halves) and the cluster size (1, 2, 4 or
+ * 8) instead of the library's cost model; 0 in a field lets the library choose it.
  * Any combination is correct; the knob exists for tuning and for tests. */
 #define B200FP8_FLAG_SPLITK_CONFIG(block_n, split) ((((uint32_t)(block_n) / 16u) << 8) | ((uint32_t)(split) << 13))
 

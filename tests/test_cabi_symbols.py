@@ -72,6 +72,8 @@ def test_workspace_sizes_and_plans_need_no_device(cdll):
     forced = lib.describe_plan(16, 4096, 4096, lib.VARIANT_TC_SPLITK | lib.flag_splitk_config(64, 4))
     assert forced.startswith("tc_splitk tile=128x64x128 cluster=4")
     assert lib.describe_plan(16, 28672, 8192, lib.VARIANT_SIMT).startswith("simt")
+    # 80 pair tiles would leave most of a second wave empty: one wave of 320-column tiles instead
+    assert lib.describe_plan(1000, 5120, 3584).startswith("tc_splitk tile=128x320x128 cluster=1")
 
 
 def test_check_maps_statuses_to_python_exceptions(cdll):
@@ -106,7 +108,7 @@ def test_one_tile_per_cluster_plans_are_well_formed_for_any_shape(cdll):
     pat = re.compile(r"tc_splitk tile=128x(\d+)x128 cluster=(\d+) .* x_rows=(\d+) stages=(\d+) ctas=(\d+) waves=(\d+) smem=(\d+)")
     for _ in range(400):
         m = rng.choice([1, 3, 8, 16, 31, 64, 100, 128, 300, 777, 2000])
-        n = rng.choice([8, 24, 100, 256, 1000, 2304, 4096, 13312, 28672, 50000])
+        n = rng.choice([8, 24, 100, 256, 1000, 2304, 4096, 5120, 9000, 13312, 28672, 50000])
         k = rng.choice([16, 128, 144, 400, 1024, 2304, 8192, 16384])
         split = rng.choice([0, 1, 2, 4, 8])
         flags = lib.VARIANT_TC_SPLITK | lib.flag_splitk_config(0, split)
@@ -114,12 +116,13 @@ def test_one_tile_per_cluster_plans_are_well_formed_for_any_shape(cdll):
         got = pat.match(plan)
         assert got, plan
         bn, s, x_rows, stages, ctas, waves, smem = (int(v) for v in got.groups())
-        assert 16 <= bn <= 256 and bn % (16 * s) == 0, plan
+        assert 16 <= bn <= 512 and bn % (16 * s) == 0, plan
+        assert bn <= 256 or (s == 1 and bn % 64 == 0), plan  # a wide tile: two halves of whole 32-column steps, no K split
         assert split in (0, s), plan
         assert x_rows == (128 if m >= 128 else (m + 7) // 8 * 8), plan
         assert 1 <= stages <= 14 and stages * (x_rows + bn) * 128 <= 192 * 1024, plan
         assert ctas == ((m + 127) // 128) * ((n + bn - 1) // bn) * s and waves >= 1, plan
         assert smem <= 227 * 1024, plan
         # tensor memory: the CTAs one SM can hold by shared memory never need more than its 512 columns
-        tmem_cols = 32 if bn <= 32 else 64 if bn <= 64 else 128 if bn <= 128 else 256
+        tmem_cols = 32 if bn <= 32 else 64 if bn <= 64 else 128 if bn <= 128 else 256 if bn <= 256 else 512
         assert (227 * 1024 // smem) * tmem_cols <= 512, plan

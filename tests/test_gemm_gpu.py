@@ -96,14 +96,18 @@ def test_cluster_split_k_kernel(cuda_device, shape):
 
 
 SPLIT_CONFIGS = [(256, 1), (256, 2), (256, 4), (256, 8), (128, 1), (128, 2), (128, 4), (128, 8), (64, 1), (64, 2), (64, 4),
-                 (208, 1), (16, 1), (48, 1), (96, 2), (192, 4), (160, 2)]
+                 (208, 1), (16, 1), (48, 1), (96, 2), (192, 4), (160, 2),
+                 (320, 1), (384, 1), (448, 1)]  # wider than 256 columns: two MMA halves, one CTA, no K split
 
 
 @pytest.mark.parametrize("config", SPLIT_CONFIGS)
 def test_every_tile_width_and_cluster_size_of_the_one_tile_per_cluster_kernel(cuda_device, config):
     """B200FP8_FLAG_SPLITK_CONFIG: each (tile width, cluster size) on a decode shape (X stage of 8 rows, deep
     ring), a ragged mid-size shape (tails in M, N and K, several row tiles) and a K shorter than the split."""
-    for m, n, k in [(5, 1000, 2320), (300, 520, 1424), (64, 256, 128)]:
+    shapes = [(5, 1000, 2320), (300, 520, 1424), (64, 256, 128)]
+    if config[0] > 256:
+        shapes.append((260, 1500, 640))  # several wide tiles in both directions, ragged everywhere
+    for m, n, k in shapes:
         xq, wq, xs, ws = _inputs(m, n, k, seed=m + n + k)
         ref = orc.gemm_rowwise(xq, wq, xs, ws)
         y = _run("tc_splitk", xq, wq, xs, ws, split_config=config)
@@ -116,7 +120,8 @@ def test_every_tile_width_and_cluster_size_of_the_one_tile_per_cluster_kernel(cu
 def test_split_config_flag_rejects_impossible_combinations(cuda_device):
     ops = _ops()
     xq, wq, xs, ws = _gpu(*_inputs(16, 256, 512))
-    for bad in [(64, 8), (128, 3), (272, 1), (48, 2)]:  # 64 / 8 < 16; 3 CTAs; wider than 256; 48 is not a multiple of 32
+    # 64 / 8 < 16; 3 CTAs; a wide tile must be a multiple of 64 columns and cannot split K; 48 is not a multiple of 32
+    for bad in [(64, 8), (128, 3), (272, 1), (288, 1), (320, 2), (48, 2)]:
         with pytest.raises(Exception):
             ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="tc_splitk", split_config=bad)
     ops.check_device_status()

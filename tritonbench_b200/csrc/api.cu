@@ -157,6 +157,43 @@ double split_plan_cost_us(long long M, long long N, long long K, int block_n, in
 // forced_block_n / forced_split: 0 = choose by the cost model.  Candidate widths: 256, 128, 64, and for
 // each cluster size the narrowest tile that still gives one wave (every SM, or as many as can hold a
 // cluster, gets exactly one tile).
+// Shared-memory layout of one (block_n, split) configuration: stages, ring, dynamic shared memory.
+static void size_split_plan(long long M, long long K, SplitPlan* p) {
+  const long long kb = (K + TcGeometry::kBlockK - 1) / TcGeometry::kBlockK;
+  p->rows_a = M >= 128 ? 128 : static_cast<int>((M + 7) / 8 * 8);
+  const int bytes_a = p->rows_a * TcGeometry::kBlockK, bytes_b = p->block_n * TcGeometry::kBlockK;
+  const long long kb_per = (kb + p->split - 1) / p->split;
+  p->stages = SplitGeometry::kRingBytes / (bytes_a + bytes_b);
+  if (p->stages > SplitGeometry::kMaxStages) p->stages = SplitGeometry::kMaxStages;
+  if (p->stages > kb_per) p->stages = static_cast<int>(kb_per > 0 ? kb_per : 1);
+  p->staged_stores = M > 64 ? 1 : 0;  // short outputs leave in 16-byte stores straight from registers
+  for (;; --p->stages) {
+    // the ring: the stages; room for the MMA's 128-row read of the last X stage; the exchange buffer
+    int ring = p->stages * (bytes_a + bytes_b);
+    const int a_overread = p->stages * bytes_a + TcGeometry::kBlockM * TcGeometry::kBlockK;
+    if (ring < a_overread) ring = a_overread;
+    const int exchange = p->split > 1 ? p->block_n * p->rows_a * 4 : 0;
+    if (ring < exchange) ring = exchange;
+    p->ring_bytes = (ring + 1023) / 1024 * 1024;
+    p->smem_bytes = p->ring_bytes + (p->staged_stores ? 32 * 1024 : 0) + split_scale_bytes(p->block_n) + 256 + 1024;
+    if (p->smem_bytes <= SplitGeometry::kMaxSmemBytes || p->stages == 1) break;  // a wide tile's third stage may not fit
+  }
+  // Tensor memory: an SM has 512 columns and this kernel's CTAs take tmem_cols each with a tcgen05.alloc that
+  // blocks until the columns are free.  CTAs that block there while their cluster peers wait at a cluster
+  // barrier would never be released, so no more CTAs may be resident on an SM than its tensor memory holds.
+  // Shared memory is the limit the launch controls: ask for enough of it that floor(227 KiB / smem_bytes)
+  // CTAs need at most 512 columns (76 KiB for 256 columns: two CTAs; 46 KiB for 128: four; ...).
+  const int min_smem = SplitGeometry::min_smem_bytes_for_tmem(split_tmem_cols(p->block_n));
+  if (p->smem_bytes < min_smem) p->smem_bytes = min_smem;
+}
+
+// CTAs of a configuration that share an SM: by shared memory, and never more than two (168 registers x 192
+// threads).  resident_clusters[] was measured with the largest shared-memory request, one CTA per SM.
+static int split_ctas_per_sm(const SplitPlan& p) {
+  const int by_smem = SplitGeometry::kSmemPerSm / (p.smem_bytes + 1024);
+  return by_smem >= 2 ? 2 : 1;
+}
+
 SplitPlan make_split_plan(long long M, long long N, long long K, const int* resident_clusters, int forced_block_n,
                           int forced_split) {
   SplitPlan best = {};
@@ -174,43 +211,30 @@ SplitPlan make_split_plan(long long M, long long N, long long K, const int* resi
     if (resident >= tiles_m) {
       const long long tiles_n = resident / tiles_m;                  // tiles along N that fit in one wave
       long long fit = ((N + tiles_n - 1) / tiles_n + step - 1) / step * step;  // narrowest width that needs no more
-      if (fit <= 256 && fit != 256 && fit != 128 && fit != 64) candidates[3] = static_cast<int>(fit);
+      // beyond 256 columns a single CTA multiplies the tile as two halves, no K split then.  Halves that are
+      // multiples of 32 columns: an MMA of 144 or 176 columns was measured at half the rate of one of 160.
+      if (fit > 256 && split == 1) fit = (fit + 63) / 64 * 64;
+      const long long widest = split == 1 ? SplitGeometry::kMaxBlockN : 256;
+      if (fit <= widest && fit != 256 && fit != 128 && fit != 64) candidates[3] = static_cast<int>(fit);
     }
     for (int i = 0; i < 4; ++i) {
       const int block_n = forced_block_n != 0 ? forced_block_n : candidates[i];
       if (block_n == 0 || block_n % step != 0) continue;
-      const double cost = split_plan_cost_us(M, N, K, block_n, split, resident);
+      SplitPlan cand = {};
+      cand.block_n = block_n;
+      cand.split = split;
+      size_split_plan(M, K, &cand);
+      const int resident_here = resident * split_ctas_per_sm(cand);  // short rings: two CTAs per SM
+      const double cost = split_plan_cost_us(M, N, K, block_n, split, resident_here);
       if (cost < best_cost) {
         best_cost = cost;
-        best.block_n = block_n;
-        best.split = split;
-        best.waves = static_cast<int>((tiles_m * ((N + block_n - 1) / block_n) + resident - 1) / resident);
+        best = cand;
+        best.waves = static_cast<int>((tiles_m * ((N + block_n - 1) / block_n) + resident_here - 1) / resident_here);
       }
       if (forced_block_n != 0) break;
     }
   }
-  best.rows_a = M >= 128 ? 128 : static_cast<int>((M + 7) / 8 * 8);
-  const int bytes_a = best.rows_a * TcGeometry::kBlockK, bytes_b = best.block_n * TcGeometry::kBlockK;
-  const long long kb_per = (kb + best.split - 1) / best.split;
-  best.stages = SplitGeometry::kRingBytes / (bytes_a + bytes_b);
-  if (best.stages > SplitGeometry::kMaxStages) best.stages = SplitGeometry::kMaxStages;
-  if (best.stages > kb_per) best.stages = static_cast<int>(kb_per > 0 ? kb_per : 1);
-  // the ring: the stages; room for the MMA's 128-row read of the last X stage; the exchange buffer
-  int ring = best.stages * (bytes_a + bytes_b);
-  const int a_overread = best.stages * bytes_a + TcGeometry::kBlockM * TcGeometry::kBlockK;
-  if (ring < a_overread) ring = a_overread;
-  const int exchange = best.split > 1 ? best.block_n * best.rows_a * 4 : 0;
-  if (ring < exchange) ring = exchange;
-  best.ring_bytes = (ring + 1023) / 1024 * 1024;
-  best.staged_stores = M > 64 ? 1 : 0;  // short outputs leave in 16-byte stores straight from registers
-  best.smem_bytes = best.ring_bytes + (best.staged_stores ? 32 * 1024 : 0) + 1024 + 256 + 1024;
-  // Tensor memory: an SM has 512 columns and this kernel's CTAs take tmem_cols each with a tcgen05.alloc that
-  // blocks until the columns are free.  CTAs that block there while their cluster peers wait at a cluster
-  // barrier would never be released, so no more CTAs may be resident on an SM than its tensor memory holds.
-  // Shared memory is the limit the launch controls: ask for enough of it that floor(227 KiB / smem_bytes)
-  // CTAs need at most 512 columns (76 KiB for 256 columns: two CTAs; 46 KiB for 128: four; ...).
-  const int min_smem = SplitGeometry::min_smem_bytes_for_tmem(split_tmem_cols(best.block_n));
-  if (best.smem_bytes < min_smem) best.smem_bytes = min_smem;
+  if (best.smem_bytes == 0) size_split_plan(M, K, &best);  // nothing was eligible: the default 256 x 1
   best.tiles = static_cast<int>(tiles_m * ((N + best.block_n - 1) / best.block_n));
   return best;
 }
@@ -240,6 +264,19 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
       if (v == B200FP8_VARIANT_TC_1CTA && ((M + 127) / 128) * ((N + 255) / 256) < dev.sm_count) {
         v = B200FP8_VARIANT_TC_SPLITK;
       }
+      // The persistent kernels run whole waves of 256-column tiles.  With one to two waves, most of the last
+      // wave's SMs idle; if tiles widened to at most 512 columns cover the output in ONE wave of single CTAs,
+      // compare that plan's modelled time with the waves of the pair kernel (a 256x256 tile takes 0.30 us per
+      // k-block at the clock these short launches see, plus 5 us of launch, pipeline fill and epilogue).
+      if (v == B200FP8_VARIANT_TC_2CTA && pair_tiles <= 2 * (dev.sm_count / 2)) {
+        const SplitPlan sp = make_split_plan(M, N, K, dev.split_clusters, 0, 1);
+        if (sp.waves == 1) {
+          const int64_t waves = (pair_tiles + dev.sm_count / 2 - 1) / (dev.sm_count / 2);
+          const double kb = static_cast<double>((K + TcGeometry::kBlockK - 1) / TcGeometry::kBlockK);
+          const double pair_us = 5.0 + static_cast<double>(waves) * kb * 0.30;
+          if (split_plan_cost_us(M, N, K, sp.block_n, 1, dev.split_clusters[0]) < pair_us) v = B200FP8_VARIANT_TC_SPLITK;
+        }
+      }
     }
   } else if (v != B200FP8_VARIANT_SIMT && !operands_tma_ok) {
     return B200FP8_UNSUPPORTED_ALIGNMENT;
@@ -263,12 +300,14 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
   } else if (v == B200FP8_VARIANT_TC_SPLITK) {
     const int forced_block_n = static_cast<int>((flags >> 8) & 0x1Fu) * 16;
     const int forced_split = static_cast<int>((flags >> 13) & 0xFu);
-    if (forced_block_n > 256 ||
+    if (forced_block_n > SplitGeometry::kMaxBlockN ||
         (forced_split != 0 && forced_split != 1 && forced_split != 2 && forced_split != 4 && forced_split != 8) ||
-        (forced_block_n != 0 && forced_block_n % (16 * (forced_split != 0 ? forced_split : 1)) != 0)) {
+        (forced_block_n != 0 && forced_block_n % (16 * (forced_split != 0 ? forced_split : 1)) != 0) ||
+        (forced_block_n > 256 && (forced_split > 1 || forced_block_n % 64 != 0))) {
       return B200FP8_BAD_ARG;
     }
-    pl.splitk = make_split_plan(M, N, K, dev.split_clusters, forced_block_n, forced_split);
+    // a forced wide tile implies no K split
+    pl.splitk = make_split_plan(M, N, K, dev.split_clusters, forced_block_n, forced_block_n > 256 ? 1 : forced_split);
     pl.splitk.overlap_previous_kernel = (flags & B200FP8_FLAG_PDL) != 0;
   } else if (v == B200FP8_VARIANT_SKINNY) {
     pl.skinny = make_skinny_plan(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), dev.sm_count);
@@ -403,7 +442,7 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
   st = encode_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, M, K, ldx, TcGeometry::kBlockK, x_box_rows);
   if (st != B200FP8_OK) return st;
   const int w_box_rows =
-      pl.variant == B200FP8_VARIANT_TC_SPLITK ? pl.splitk.block_n : TcGeometry::kBlockN / cta_group;
+      pl.variant == B200FP8_VARIANT_TC_SPLITK ? split_first_half(pl.splitk.block_n) : TcGeometry::kBlockN / cta_group;
   st = encode_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, N, K, ldw, TcGeometry::kBlockK, w_box_rows);
   if (st != B200FP8_OK) return st;
   if (pl.tma_store) {

@@ -42,12 +42,13 @@ struct C {
   static constexpr int kRingBytes = SplitGeometry::kRingBytes;  // reused for the exchange
   static constexpr int kExchangeBytes = Geo::kBlockM * 256 * 4;  // fp32 partials a CTA receives, widest tile
   static constexpr int kEpiBytes = 4 * 2 * Geo::kStoreRows * Geo::kStoreCols * 2;
-  static constexpr int kScaleBytes = 256 * 4;  // w_scale of the CTA's column slice
+  static constexpr int kScaleBytes = 256 * 4;  // w_scale of the CTA's column slice (twice that for a wide tile, whose ring is short)
   static constexpr int kBarBytes = 256;
   static constexpr int kSmemBytes = kRingBytes + kEpiBytes + kScaleBytes + kBarBytes + 1024;
   static_assert(kExchangeBytes <= kRingBytes, "the exchange buffer lives in the operand ring");
   static_assert(16 * SplitGeometry::kMaxStages + 16 <= kBarBytes, "barrier block");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
+  static_assert(kSmemBytes == SplitGeometry::kMaxSmemBytes, "the host plans against the same limit");
 };
 
 enum WaitSite : uint32_t {
@@ -191,6 +192,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const int bytes_a = plan.rows_a * Geo::kBlockK;  // multiples of 1024: whole 8-row swizzle atoms
   const int bytes_b = block_n * Geo::kBlockK;
   const uint32_t stage_tx = static_cast<uint32_t>(bytes_a + bytes_b);
+  const int n_first = split_first_half(block_n);  // a tile wider than 256 columns: two MMAs and two W boxes per step
+  const int n_second = block_n - n_first;
   const uint32_t tmem_cols = static_cast<uint32_t>(split_tmem_cols(block_n));
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -201,7 +204,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const uint32_t smem_b = smem_a + stages * bytes_a;  // the MMA's 128-row reads of a short X stage end in here
   const uint32_t smem_epi = base + plan.ring_bytes;
   const uint32_t smem_scales = smem_epi + (plan.staged_stores ? C::kEpiBytes : 0);
-  const uint32_t bars = smem_scales + C::kScaleBytes;
+  const uint32_t bars = smem_scales + split_scale_bytes(block_n);
   const uint32_t bar_full = bars;                     // [stages]
   const uint32_t bar_empty = bars + 8 * kMaxStages;   // [stages]
   const uint32_t bar_tmem_full = bars + 16 * kMaxStages;
@@ -252,6 +255,9 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       const uint32_t full = bar_full + 8 * i;
       mbar_arrive_expect_tx(full, stage_tx);
       tma_load_2d(smem_b + i * bytes_b, &tm_w, full, kb_at(i) * Geo::kBlockK, col_base);
+      if (n_second > 0) {
+        tma_load_2d(smem_b + i * bytes_b + n_first * Geo::kBlockK, &tm_w, full, kb_at(i) * Geo::kBlockK, col_base + n_first);
+      }
     }
     if (overlap) griddep_wait();
     for (int i = 0; i < kb_len && i < stages; ++i) {
@@ -283,6 +289,9 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         mbar_arrive_expect_tx(full, stage_tx);
         tma_load_2d(smem_a + stage * bytes_a, &tm_x, full, kb * Geo::kBlockK, row_base);
         tma_load_2d(smem_b + stage * bytes_b, &tm_w, full, kb * Geo::kBlockK, col_base);
+        if (n_second > 0) {
+          tma_load_2d(smem_b + stage * bytes_b + n_first * Geo::kBlockK, &tm_w, full, kb * Geo::kBlockK, col_base + n_first);
+        }
         if (++stage == static_cast<uint32_t>(stages)) {
           stage = 0;
           phase ^= 1u;
@@ -291,7 +300,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0 && has_work) {
-      const uint32_t idesc = instr_desc_e4m3(Geo::kBlockM, static_cast<uint32_t>(block_n));
+      const uint32_t idesc = instr_desc_e4m3(Geo::kBlockM, static_cast<uint32_t>(n_first));
+      const uint32_t idesc2 = instr_desc_e4m3(Geo::kBlockM, static_cast<uint32_t>(n_second > 0 ? n_second : 16));
       uint32_t stage = 0, phase = 0;
       for (int i = 0; i < kb_len; ++i) {
         ok = mbar_wait<false>(bar_full + 8 * stage, phase, abort_flag, p.status, kSiteMmaFull);
@@ -302,6 +312,13 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll
         for (int k = 0; k < Geo::kBlockK / 32; ++k) {
           tc_mma_f8<1>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        if (n_second > 0) {
+          const uint64_t b2_desc = smem_desc_k_sw128(smem_b + stage * bytes_b + n_first * Geo::kBlockK);
+#pragma unroll
+          for (int k = 0; k < Geo::kBlockK / 32; ++k) {
+            tc_mma_f8<1>(tmem_base + n_first, a_desc + 2 * k, b2_desc + 2 * k, idesc2, (i > 0 || k > 0) ? 1u : 0u);
+          }
         }
         tc_commit(bar_empty + 8 * stage);
         if (++stage == static_cast<uint32_t>(stages)) {
@@ -471,7 +488,8 @@ int splitk_resident_clusters(int split, cudaError_t* err) {
 
 cudaError_t launch_gemm_splitk(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_y,
                                const TcParams& p, const SplitPlan& plan, cudaStream_t stream) {
-  if (plan.block_n < 16 || plan.block_n > 256 || plan.split < 1 || plan.block_n % (16 * plan.split) != 0 ||
+  if (plan.block_n < 16 || plan.block_n > SplitGeometry::kMaxBlockN || plan.split < 1 ||
+      plan.block_n % (16 * plan.split) != 0 || (plan.block_n > 256 && (plan.split != 1 || plan.block_n % 64 != 0)) ||
       plan.smem_bytes > C::kSmemBytes ||
       plan.smem_bytes < SplitGeometry::min_smem_bytes_for_tmem(split_tmem_cols(plan.block_n))) {
     return cudaErrorInvalidValue;

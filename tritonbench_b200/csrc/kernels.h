@@ -64,10 +64,15 @@ cudaError_t launch_gemm_tc(const CUtensorMap& tm_x, const CUtensorMap& tm_w, con
                            const TcParams& p, int num_ctas, cudaStream_t stream, const ExtraOutputs* extra = nullptr);
 
 // One 128 x block_n tile per cluster of `split` CTAs, K split over the cluster and reduced over distributed
-// shared memory (gemm_splitk.cu).  split is 1, 2, 4 or 8; block_n a multiple of 16 * split, at most 256.
+// shared memory (gemm_splitk.cu).  split is 1, 2, 4 or 8; block_n a multiple of 16 * split, at most 256 - or, with
+// split 1 only, a multiple of 64 up to 512: a wide tile, multiplied as two column halves, for outputs whose
+// 256-column tiles would need a second, mostly empty wave of CTAs.
 struct SplitGeometry {
   static constexpr int kRingBytes = 192 * 1024;
   static constexpr int kMaxStages = 14;
+  static constexpr int kMaxBlockN = 512;     // split 1; 256 with a K split
+  // most dynamic shared memory a CTA asks for: ring, store staging (32 KiB), scales (1 KiB), barriers, alignment
+  static constexpr int kMaxSmemBytes = kRingBytes + 32 * 1024 + 1024 + 256 + 1024;
   static constexpr int kSmemPerSm = 227 * 1024;  // shared memory the CTAs of one SM can hold together
   static constexpr int kTmemColsPerSm = 512;
   // Smallest dynamic shared-memory request with which the CTAs that fit on one SM by shared memory
@@ -78,7 +83,13 @@ struct SplitGeometry {
   }
 };
 // tensor-memory columns a CTA of the one-tile-per-cluster kernel allocates for a tile of block_n columns
-__host__ __device__ constexpr int split_tmem_cols(int block_n) { return block_n <= 32 ? 32 : (block_n <= 64 ? 64 : (block_n <= 128 ? 128 : 256)); }
+__host__ __device__ constexpr int split_tmem_cols(int block_n) {
+  return block_n <= 32 ? 32 : (block_n <= 64 ? 64 : (block_n <= 128 ? 128 : (block_n <= 256 ? 256 : 512)));
+}
+// a tile wider than 256 columns is multiplied as two halves: columns [0, first) and [first, block_n)
+__host__ __device__ constexpr int split_first_half(int block_n) { return block_n <= 256 ? block_n : block_n / 2; }
+// shared memory for the W scales of a CTA's column slice
+__host__ __device__ constexpr int split_scale_bytes(int block_n) { return block_n <= 256 ? 1024 : 2048; }
 struct SplitPlan {
   int block_n;
   int split;
