@@ -756,13 +756,84 @@ def run_own(args, workload):
         sys.exit(3)
 
 
+AUX_WORKLOADS = ("row_quantize", "rms_norm_quantize", "silu_mul_quantize", "block_quantize", "blockwise_gemm", "rowwise_gemm")
+
+
+def run_aux(args):
+    """Times ONE kernel next to the hot path on one GPU - the quantisers, the block-scaled GEMM, or a single
+    rowwise GEMM shape with a chosen variant - with CUDA events over --steps back-to-back calls after --warmup
+    calls, and prints a small JSON line.  These are the commands the ncu summaries under profiles/ run; they
+    are not the driver's bench line.  Sizes: --m rows, --k columns (quantisers); --m --n --k (GEMMs)."""
+    from tritonbench_b200 import ops, quantize
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    m, n, k = args.m or 8192, args.n or 8192, args.k or 8192
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
+    what = args.workload
+    nbytes, flops = None, None
+    if what in ("row_quantize", "block_quantize", "rms_norm_quantize", "silu_mul_quantize"):
+        if what.endswith("_quantize") and what not in ("row_quantize", "block_quantize"):
+            dt = torch.bfloat16
+        x = torch.randn((m, k), device="cuda", dtype=dt)
+        nbytes = m * k * (x.element_size() + 1) + 4 * m
+        if what == "row_quantize":
+            fn = lambda: ops.fp8_row_quantize(x)  # noqa: E731
+        elif what == "block_quantize":
+            fn = lambda: ops.fp8_block_quantize(x)  # noqa: E731
+        elif what == "rms_norm_quantize":
+            w = torch.randn((k,), device="cuda", dtype=dt)
+            fn = lambda: ops.rms_norm_fp8_rowwise_quant(x, w, round_bf16=args.round_bf16)  # noqa: E731
+        else:
+            x2 = torch.randn((m, k), device="cuda", dtype=dt)
+            nbytes += m * k * 2
+            fn = lambda: ops.silu_mul_fp8_rowwise_quant(x, x2, round_bf16=args.round_bf16)  # noqa: E731
+    else:
+        x = torch.randn((m, k), device="cuda", dtype=torch.bfloat16)
+        w = torch.randn((n, k), device="cuda", dtype=torch.bfloat16)
+        out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        flops = 2.0 * m * n * k
+        if what == "blockwise_gemm":
+            xq, xs = quantize.fp8_block_quantize(x)
+            wq, ws = quantize.fp8_block_quantize(w)
+            fn = lambda: ops.fp8_gemm_blockwise(xq, wq, xs, ws, out=out)  # noqa: E731
+        else:
+            xq, xs = ops.fp8_row_quantize(x)
+            wq, ws = ops.fp8_row_quantize(w)
+            fn = lambda: ops.fp8_gemm_rowwise(xq, wq, xs, ws, out=out, variant=args.variant)  # noqa: E731
+    for _ in range(max(args.warmup, 0)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    us = e0.elapsed_time(e1) / args.steps * 1e3
+    line = {"workload": what, "M": m, "N": n if flops else None, "K": k, "dtype": args.dtype if nbytes else "fp8_e4m3",
+            "steps": args.steps, "warmup": args.warmup, "us_per_call": round(us, 2)}
+    if nbytes:
+        line["gbs"] = round(nbytes / us / 1e3, 1)
+    if flops:
+        line["tflops"] = round(flops / us / 1e6, 1)
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["own", "reference"], default="own")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="square_8192")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + list(AUX_WORKLOADS), default="square_8192")
+    ap.add_argument("--m", type=int, help="single-kernel workloads: rows")
+    ap.add_argument("--n", type=int, help="single-kernel GEMM workloads: columns of Y")
+    ap.add_argument("--k", type=int, help="single-kernel workloads: columns of X")
+    ap.add_argument("--dtype", choices=["bf16", "fp16", "fp32"], default="bf16", help="quantiser workloads: input type")
+    ap.add_argument("--round-bf16", action="store_true", help="producer + quantiser workloads: round the activation to bf16 first")
+    ap.add_argument("--variant", default="auto", help="rowwise_gemm workload: kernel variant")
     ap.add_argument("--gather", action="store_true", help="N>1: also time the weak-scaling GEMM + in-place NCCL all-gather of Y")
     ap.add_argument("--no-overlap", action="store_true", help="decode workloads: plain stream-ordered launches")
     ap.add_argument("--no-also", action="store_true", help="default workload: skip the legs for the other configurations")
@@ -771,7 +842,9 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the device-timed loop of the workload (for short profiler captures; not a bench run)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload in AUX_WORKLOADS:
+        run_aux(args)
+    elif args.impl == "reference":
         run_reference(args, args.workload)
     else:
         run_own(args, args.workload)

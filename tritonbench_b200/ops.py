@@ -431,49 +431,3 @@ class HostGemm:
             self.close()
         except Exception:
             pass
-
-
-def _main() -> None:
-    """python -m tritonbench_b200.ops --op rowwise|blockwise --m M --n N --k K [--variant V] [--iters I]
-    times one GEMM shape with CUDA events over back-to-back calls and prints microseconds and TFLOP/s."""
-    import argparse
-
-    from . import quantize
-
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=["rowwise", "blockwise"], default="rowwise")
-    ap.add_argument("--m", type=int, default=8192)
-    ap.add_argument("--n", type=int, default=8192)
-    ap.add_argument("--k", type=int, default=8192)
-    ap.add_argument("--variant", default="auto")
-    ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    args = ap.parse_args()
-    m, n, k = args.m, args.n, args.k
-    x = torch.randn((m, k), device="cuda", dtype=torch.bfloat16)
-    w = torch.randn((n, k), device="cuda", dtype=torch.bfloat16)
-    out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
-    if args.op == "blockwise":
-        xq, xs = quantize.fp8_block_quantize(x)
-        wq, ws = quantize.fp8_block_quantize(w)
-        fn = lambda: fp8_gemm_blockwise(xq, wq, xs, ws, out=out)  # noqa: E731
-    else:
-        xq, xs = fp8_row_quantize(x)
-        wq, ws = fp8_row_quantize(w)
-        fn = lambda: fp8_gemm_rowwise(xq, wq, xs, ws, out=out, variant=args.variant)  # noqa: E731
-    for _ in range(args.warmup):
-        fn()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.iters):
-        fn()
-    e1.record()
-    torch.cuda.synchronize()
-    check_device_status()
-    us = e0.elapsed_time(e1) / args.iters * 1e3
-    print(f"{args.op} {m}x{n}x{k}: {us:.1f} us per call, {2.0 * m * n * k / us / 1e6:.0f} TFLOP/s")
-
-
-if __name__ == "__main__":
-    _main()

@@ -120,57 +120,3 @@ def make_inputs(
     xq, xs = make_quantized(m, k, x_seed, device, dist, x_std)
     wq, ws = make_quantized(n, k, w_seed, device, dist, w_std)
     return xq, wq, xs, ws
-
-
-def _main() -> None:
-    """python -m tritonbench_b200.quantize --rows R --cols C [--dtype bf16|fp16|fp32] [--producer rms_norm|silu_mul]
-    [--iters N] times the CUDA quantiser kernel, or with --producer the producer + quantiser kernel (bf16 inputs),
-    with CUDA events over back-to-back calls and prints GB/s."""
-    import argparse
-
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--rows", type=int, default=28672)
-    ap.add_argument("--cols", type=int, default=8192)
-    ap.add_argument("--dtype", choices=["bf16", "fp16", "fp32"], default="bf16")
-    ap.add_argument("--producer", choices=["none", "rms_norm", "silu_mul"], default="none")
-    ap.add_argument("--block", action="store_true", help="time the 128x128 block quantiser instead of the rowwise one")
-    ap.add_argument("--round-bf16", action="store_true", help="producers: round the activation to bf16 before quantising")
-    ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    args = ap.parse_args()
-    from . import ops
-
-    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
-    if args.producer != "none":
-        dt = torch.bfloat16
-    x = torch.randn((args.rows, args.cols), device="cuda", dtype=dt)
-    in_bytes = x.element_size()
-    if args.producer == "rms_norm":
-        w = torch.randn((args.cols,), device="cuda", dtype=dt)
-        fn = lambda: ops.rms_norm_fp8_rowwise_quant(x, w, round_bf16=args.round_bf16)  # noqa: E731
-    elif args.producer == "silu_mul":
-        x2 = torch.randn((args.rows, args.cols), device="cuda", dtype=dt)
-        in_bytes *= 2
-        fn = lambda: ops.silu_mul_fp8_rowwise_quant(x, x2, round_bf16=args.round_bf16)  # noqa: E731
-    elif args.block:
-        fn = lambda: ops.fp8_block_quantize(x)  # noqa: E731
-    else:
-        fn = lambda: ops.fp8_row_quantize(x)  # noqa: E731
-    for _ in range(args.warmup):
-        fn()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.iters):
-        fn()
-    e1.record()
-    torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) / args.iters * 1e3
-    nbytes = args.rows * args.cols * (in_bytes + 1) + 4 * args.rows
-    what = ("block_quantize" if args.block else "row_quantize") if args.producer == "none" else f"{args.producer} + row_quantize"
-    print(f"{what} {args.rows}x{args.cols} {args.dtype if args.producer == 'none' else 'bf16'}: "
-          f"{us:.1f} us per call, {nbytes / us / 1e3:.0f} GB/s")
-
-
-if __name__ == "__main__":
-    _main()
