@@ -98,7 +98,7 @@ def test_blockwise_operator_backend_through_the_reference_harness(cuda_device):
 def test_fused_quant_operator_backends_through_the_reference_harness(cuda_device, backend):
     """`--op fp8_fused_quant_gemm_rowwise`: RMS norm (or SiLU-mul) + quantiser in one kernel, then the GEMM; each of
     the four backends against the torch pipeline of its own definition, at the tolerance derived from one e4m3
-    step on a small fraction of the activations (atol 0.025 sqrt(K), rtol 1.6e-2)."""
+    step on a small fraction of the activations (atol 0.1 sqrt(K), a tenth of an output's sigma; rtol 1.6e-2)."""
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "tritonbench")):
         pytest.skip("no installed copy of the tritonbench package on this machine")
@@ -115,4 +115,4 @@ def test_fused_quant_operator_backends_through_the_reference_harness(cuda_device
         assert cells[backend].accuracy is True, (backend, shape)
         assert cells[backend].latency is not None
     atol, rtol = plug.fused_quant_tolerance(2048)
-    assert abs(atol - 1.131) < 1e-3 and rtol == 1.6e-2
+    assert abs(atol - 4.525) < 1e-3 and rtol == 1.6e-2

@@ -14,8 +14,8 @@
 //   warps 4-11  promotion + epilogue: warp w owns TMEM lane quarter w%4 (32 rows) and column half
 //               (w-4)/4 (128 columns = one scale block of W): 128 fp32 accumulators per thread
 //
-// A promotion thread holds 128 accumulators plus two 32-column read buffers, so that the next TMEM
-// read is in flight while the previous one is folded in; that needs about 210 registers.  The kernel
+// A promotion thread holds 128 accumulators plus two 32-column read buffers, two TMEM reads in flight at a
+// time, and folds the products in with packed fp32 FMAs (fma.rn.f32x2); that needs about 210 registers.  The kernel
 // starts with 168 per thread (384 threads) and moves registers from the first warpgroup (40 each)
 // to the two promotion warpgroups (232 each) with setmaxnreg.
 //
@@ -209,34 +209,36 @@ gemm_blockwise_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
       for (int kb = 0; kb < num_kb; ++kb, ++block_no) {
         const uint32_t buf = block_no & 1u;
         const uint32_t use = (block_no >> 1) & 1u;
-        const float s = __ldg(xs + kb) * __ldg(ws + kb);
+        const float s = __ldg(xs + kb) * __ldg(ws + kb);  // issued before the wait below; measured: not on the critical path
         ok = mbar_wait<false>(bar_acc_full + 8 * buf, use, abort_flag, p.status, kSiteEpiAccFull);
         ok = __all_sync(0xffffffffu, ok) != 0;
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * Geo::kBlockN + half * 128;
-        // four 32-column reads through two buffers: read c+1 is in flight while read c is folded in
+        // four 32-column reads through two 32-register buffers, two reads in flight at a time; the products are
+        // folded in with packed fp32 FMAs (two per instruction), so that from "buffer full" to "buffer free" a
+        // warp spends two read latencies and 32 instructions
         uint32_t part0[32], part1[32];
         tmem_ld_32x32(t_addr, part0);
-        tmem_ld_wait_for(part0);
         tmem_ld_32x32(t_addr + 32, part1);
+        tmem_ld_wait_for(part0);
+        keep_below(part1);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(part0[j]), s, acc[j]);
-        tmem_ld_wait_for(part1);
+        for (int j = 0; j < 32; j += 2) fma2(acc[j], acc[j + 1], part0[j], part0[j + 1], s);
         tmem_ld_32x32(t_addr + 64, part0);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(__uint_as_float(part1[j]), s, acc[32 + j]);
-        tmem_ld_wait_for(part0);
+        for (int j = 0; j < 32; j += 2) fma2(acc[32 + j], acc[33 + j], part1[j], part1[j + 1], s);
         tmem_ld_32x32(t_addr + 96, part1);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[64 + j] = fmaf(__uint_as_float(part0[j]), s, acc[64 + j]);
-        tmem_ld_wait_for(part1);
-        // the whole buffer is in registers: hand it back before the last quarter of the arithmetic
+        tmem_ld_wait_for(part0);
+        keep_below(part1);
+        // the whole buffer is in registers: hand it back before the second half of the arithmetic
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[96 + j] = fmaf(__uint_as_float(part1[j]), s, acc[96 + j]);
+        for (int j = 0; j < 32; j += 2) fma2(acc[64 + j], acc[65 + j], part0[j], part0[j + 1], s);
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) fma2(acc[96 + j], acc[97 + j], part1[j], part1[j + 1], s);
       }
       if (!ok) break;
 

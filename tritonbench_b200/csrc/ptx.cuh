@@ -331,6 +331,33 @@ __device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {
                : "memory");
 }
 
+// Compiler-only fence: code that reads `r` stays below this point (and therefore below a tcgen05.wait::ld
+// issued just before it), although the load that wrote `r` was issued earlier.  Emits no instruction.
+__device__ __forceinline__ void keep_below(uint32_t (&r)[32]) {
+  asm volatile(""
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
+// Two fp32 fused multiply-adds in one instruction (sm_100 packed fp32): acc{0,1} += a{0,1} * s.
+__device__ __forceinline__ void fma2(float& acc0, float& acc1, uint32_t a0, uint32_t a1, float s) {
+  asm("{\n"
+      ".reg .b64 a, b, c;\n"
+      "mov.b64 a, {%2, %3};\n"
+      "mov.b64 b, {%4, %4};\n"
+      "mov.b64 c, {%0, %1};\n"
+      "fma.rn.f32x2 c, a, b, c;\n"
+      "mov.b64 {%0, %1}, c;\n"
+      "}\n"
+      : "+f"(acc0), "+f"(acc1)
+      : "r"(a0), "r"(a1), "f"(s));
+}
+
 // Register reallocation between warpgroups (all 128 threads of a warpgroup execute the same one):
 // a warpgroup that needs few registers gives them up, one that needs many takes them.
 template <int kRegs>

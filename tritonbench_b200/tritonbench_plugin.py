@@ -286,12 +286,15 @@ FUSED_BASELINES = {
 
 def fused_quant_tolerance(k: int):
     """(atol, rtol) for comparing a fused-quantiser backend with the torch pipeline of the same definition.
-    The two compute the activation y with different fp32 summation orders and exponentials, so a fraction of the
-    activations (0.2 % measured) lands on the other side of an e4m3 rounding boundary: one step, at most 1/8 of
-    that element.  With unit-variance inputs (the operator draws x, w and the norm weight from N(0,1)) an output
-    has sigma ~ sqrt(K), one flipped activation moves it by ~1/8, and 0.002 K flips add in quadrature to
-    sqrt(0.002 K) / 8 = 0.0056 sqrt(K).  atol is 4.5 times that; rtol is two bf16 steps, as for the plain GEMM."""
-    return 0.025 * float(k) ** 0.5, 1.6e-2
+    The two compute the activation y with different fp32 operation orders (and exponentials), so a fraction of the
+    activations (0.2 % measured; more when y is rounded to bf16 first, where a last-bit difference can move y by a
+    whole bf16 step) lands on the other side of an e4m3 rounding boundary: one step, up to 1/8 of that element.
+    With unit-variance inputs (the operator draws x, w and the norm weight from N(0,1)) an output has
+    sigma ~ sqrt(K); a flipped large activation moves every output of its row by up to |y| |w| / 8.  Measured on a
+    B200 over four shapes (K = 2048 ... 8192), the largest deviation beyond rtol was 0.030 sqrt(K) for the backends
+    that keep y in fp32 and 0.072 sqrt(K) for those that round it to bf16.  atol = 0.1 sqrt(K) (a tenth of an
+    output's sigma); rtol is two bf16 steps, as for the plain GEMM."""
+    return 0.1 * float(k) ** 0.5, 1.6e-2
 
 
 def _standin_quantize_fp8_row(a, scale_ub=None, zero_start_index_M=None, use_triton=True, output_device=None):
