@@ -3,14 +3,21 @@
 Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline / reference legs may import this
 module, and only as the checker or the timed CPU baseline.  Nothing under tritonbench_b200/ uses it.
 
-PARITY UNPINNED at the kernel boundary: the arithmetic of the reference's backends lives in the
-third-party package fbgemm_gpu (git submodule submodules/FBGEMM of the reference, .gitmodules:1-3,
-an empty directory in the mounted tree with no recorded commit; not installed), and the reference's
-own tests skip this operator wholesale (test/test_gpu/skip_tests_h100_pytorch.yaml:17-18), so there
-are no golden vectors for the GEMM to pin against.  What is pinned: the row quantiser below is checked
-against the reference's own `fp8_row_quantize` (imported from the reference tree by
-tests/golden/make_golden.py, outputs committed as fixtures), and the e4m3 decode table against
-torch.float8_e4m3fn for all 256 byte values.
+PARITY at the kernel boundary.  The arithmetic of the reference's backends lives in the third-party package
+fbgemm_gpu (git submodule submodules/FBGEMM of the reference, .gitmodules:1-3, an empty directory in the mounted
+tree with no recorded commit; not installed), and the reference's own tests skip this operator wholesale
+(test/test_gpu/skip_tests_h100_pytorch.yaml:17-18), so the reference holds no golden vectors for the GEMM.  What
+pins this oracle:
+  * the GEMM (`gemm_rowwise`): on a GPU, against the output of the call the reference itself names as the operator's
+    torch baseline and runs in the sibling operator - `torch._scaled_mm` with rowwise scales
+    (tritonbench/operators/fp8_gemm_rowwise/operator.py:237-246, tritonbench/operators/fp8_gemm/fp8_gemm.py:88-101) -
+    on every benchmark configuration (tests/test_gemm_gpu.py::test_against_torch_scaled_mm_the_call_the_reference_makes).
+    That call runs on CUDA only (on CPU it rejects rowwise scales), so without a GPU the GEMM oracle is checked
+    against the stored fixtures and its plain-C twin only: in a CPU-only run its parity is UNPINNED;
+  * the row quantiser and the block quantiser: against the reference's own `fp8_row_quantize` and
+    `fp8_block_quantize`, imported from the reference tree by tests/golden/make_golden.py (outputs committed as
+    fixtures, rows with NaN and infinity included);
+  * the e4m3 decode table: against torch.float8_e4m3fn for all 256 byte values.
 
 What this restates:
   * `row_quantize_reference`  follows tritonbench/operators/fp8_gemm_rowwise/operator.py:130-145

@@ -359,6 +359,13 @@ def test_against_torch_scaled_mm_the_call_the_reference_makes(cuda_device, case)
     if dist_name == "student_t3":  # per row as well: heavy rows must not hide light ones
         row_rms = ref.double().pow(2).mean(dim=1, keepdim=True).sqrt().float()
         assert bool((diff <= orc.bf16_ulp(ref) + 1e-2 * row_rms).all()), f"{case[0]} per-row bound"
+    # the CPU oracle itself against the same reference-called output (64 sampled rows): this is what ties the
+    # checker every other test uses to code the reference runs
+    rows = torch.randperm(m, generator=torch.Generator().manual_seed(11))[: min(m, 64)].sort().values
+    rows_d = rows.cuda()
+    oracle_rows = orc.gemm_rowwise(xq[rows_d].cpu(), wq.cpu(), xs[rows_d].cpu(), ws.cpu(), decode="cast")
+    res = orc.compare(oracle_rows, want[rows_d])
+    assert res["ok"], f"{case[0]}: oracle vs torch._scaled_mm {res}"
 
 
 def test_reference_builtin_decode_shapes(cuda_device, golden_dir):
