@@ -589,7 +589,7 @@ def e2e_leg(run, m, n, k, xq, xs, wq, ws, steps, flops_step_rank):
         "steps": steps,
         "ms_per_step": t_full * 1e3,
         "api": "b200fp8_gemm_rowwise_host (pinned host buffers in, pinned host buffer out, synchronous; X and W panels "
-               "uploaded alternately, blocks of Y downloaded as they complete)",
+               "uploaded alternately, each newly computable strip of Y multiplied and downloaded at once)",
         "pcie": pcie,
         "pcie_bound_ms": bound_s * 1e3,
         "pcie_frac": bound_s / t_full,

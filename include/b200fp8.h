@@ -262,8 +262,9 @@ int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char*
  * inputs and output live in host memory (pinned for full PCIe speed), device staging
  * buffers belong to the context.  One call = copy in, GEMM, copy out, synchronise; the context's device is
  * made current for the duration of the call.  Larger problems are cut into panels of 1024 rows of X and 2048
- * rows of W that go up alternately; each block of Y is multiplied and sent down (a pitched copy into the host
- * array) as soon as its two panels are on the device, so both PCIe directions and the GPU work at once.
+ * rows of W that go up alternately; after every upload the strip of Y that has just become computable is multiplied
+ * by one GEMM and sent down by one copy (a pitched copy into the host array when the strip is narrower than Y), so
+ * both PCIe directions and the GPU work at once.
  * Whatever the call returns, no copy is in flight on the caller's buffers when it returns.
  * Replaces: `input_cast(.to(device))` + backend call + result read in
  * tritonbench/utils/triton_op.py:846-850,1221-1232.
@@ -285,7 +286,8 @@ int b200fp8_host_ctx_set_weights(b200fp8_host_ctx* ctx, const void* wq, const fl
 /*
  * Tuning knob: panel sizes of the pipeline above (rows of X per panel, rows of W = columns of Y per panel).
  * A panel smaller than its dimension must be a multiple of 128 rows / 256 columns; at most 64 panels per
- * dimension and 1024 blocks.  Any setting gives the same Y.  Replaces: nothing in the reference.
+ * dimension.  Any setting gives a Y within the kernels' tolerance of any other (strips of different shapes may
+ * run different kernel plans).  Replaces: nothing in the reference.
  */
 int b200fp8_host_ctx_set_panels(b200fp8_host_ctx* ctx, int64_t panel_rows, int64_t panel_cols);
 

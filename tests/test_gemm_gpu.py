@@ -672,8 +672,8 @@ def test_host_buffer_entry_point(cuda_device):
                                           ((4096 + 1, 520, 400), None), ((2100, 4352, 1536), None), ((300, 4096 + 8, 2048), (128, 1024))])
 def test_host_buffer_entry_point_panel_pipeline(cuda_device, shape, panels):
     """Larger problems flow through the host-buffer call in panels over three streams (the form the end-to-end
-    benchmark number is measured on): panels of X and of W uploaded alternately, blocks of Y multiplied and
-    downloaded as their panels arrive.  Several panels in both dimensions, ragged last panels (37 rows, one row,
+    benchmark number is measured on): panels of X and of W uploaded alternately, every newly computable strip of Y
+    multiplied and downloaded at once.  Several panels in both dimensions, ragged last panels (37 rows, one row,
     8 columns), bias on and off, pageable as well as pinned host memory, and the weights kept on the device."""
     ops = _ops()
     m, n, k = shape

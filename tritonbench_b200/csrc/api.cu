@@ -883,21 +883,23 @@ int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char*
 // One call = copy in, GEMM, copy out.  The copies are what the call costs (PCIe), so the problem is cut into
 // panels that flow through three streams - uploads, GEMMs, downloads - with both PCIe directions busy at once.
 //
-// A block Y[i][j] (panel i of the rows, panel j of the columns) needs panel i of X and panel j of W.  When W comes
-// from the host with every call, sending all of W before the first X panel would keep the download direction idle
-// for the first third of the call; instead X panels and W panels go up alternately and every block is multiplied
-// and sent down as soon as both of its panels are there, so the blocks ready for download grow with the square of
-// the bytes uploaded.  Blocks of Y are then sub-matrices of the host array (a pitched copy).  When W stays on the
-// device (b200fp8_host_ctx_set_weights) only X goes up and Y comes down in whole row panels (contiguous copies).
+// An element of Y needs its row of X and its row of W.  When W comes from the host with every call, sending all
+// of W before the first X panel would keep the download direction idle for the first third of the call; instead
+// row panels of X and of W go up alternately, and after every upload the strip of Y that has just become
+// computable - the new X panel against all of W that is on the device, or all of X that is on the device against
+// the new W panel - is multiplied by one GEMM and sent down by one copy (a pitched copy into the host array when
+// the strip is narrower than Y).  The part of Y ready for download grows with the square of the bytes uploaded.
+// When W stays on the device (b200fp8_host_ctx_set_weights) only X goes up and every strip is a full-width row
+// panel (contiguous copies).
 namespace {
 constexpr int kMaxPanels = 64;       // per dimension
-constexpr int kMaxBlocks = 1024;     // blocks of Y per call
+constexpr int kMaxCalls = 2 * kMaxPanels;  // GEMMs (= strips of Y) per call
 constexpr int64_t kPanelRows = 1024;
-constexpr int64_t kPanelCols = 2048;
+constexpr int64_t kPanelCols = 2048;  // pitched downloads of narrower strips (2 KiB rows and less) were measured slower
 
 struct HostStep {
-  int kind;  // 0: upload X panel a; 1: upload W panel a; 2: multiply and download block (a, b)
-  int a, b;
+  int kind;   // 0: upload X panel `index`, then the strip rows(panel) x [0, cols uploaded); 1: the same for W
+  int index;
 };
 }  // namespace
 
@@ -907,20 +909,18 @@ struct b200fp8_host_ctx {
   uint32_t flags;
   int64_t panel_rows, panel_cols;  // as configured; W resident: whole rows of Y (one column panel)
   cudaStream_t s_in, s_compute, s_out;
-  cudaEvent_t ev_x[kMaxPanels];
-  cudaEvent_t ev_w[kMaxPanels];
-  cudaEvent_t ev_y[kMaxBlocks];
-  cudaEvent_t ev_done;
+  cudaEvent_t ev_up[kMaxCalls];  // upload of step s has completed
+  cudaEvent_t ev_y[kMaxCalls];   // GEMM of step s has completed
   uint8_t* d_x;
   uint8_t* d_w;
   float* d_xs;
   float* d_ws;
   __nv_bfloat16* d_bias;
   __nv_bfloat16* d_y;
-  uint8_t* d_workspace;    // one workspace per block in flight when the plan needs more than the status word
-  size_t workspace_bytes;  // per block
+  uint8_t* d_workspace;    // one workspace per GEMM in flight when the plan needs more than the status word
+  size_t workspace_bytes;  // per GEMM
   size_t workspace_total;
-  uint32_t* h_status;      // pinned, one word per block
+  uint32_t* h_status;      // pinned, one word per GEMM
   bool weights_resident;
   bool bias_resident;
 };
@@ -942,37 +942,39 @@ struct DeviceGuard {  // the context's device is current inside the call, the ca
 
 int panels_of(int64_t extent, int64_t panel) { return static_cast<int>((extent + panel - 1) / panel); }
 
-// Largest workspace any block of the context's panel grid needs (interior, last row, last column, corner).
-size_t block_workspace_bytes(const b200fp8_host_ctx* c, int64_t panel_rows, int64_t panel_cols) {
-  const int64_t last_rows = c->M - (panels_of(c->M, panel_rows) - 1) * panel_rows;
-  const int64_t last_cols = c->N - (panels_of(c->N, panel_cols) - 1) * panel_cols;
+// Largest workspace any strip of the context's panel grid can need: strips are (one row panel) x (1..pn column
+// panels) or (1..pm row panels) x (one column panel); every such shape is asked for.
+size_t strip_workspace_bytes(const b200fp8_host_ctx* c, int64_t panel_rows, int64_t panel_cols) {
+  const int pm = panels_of(c->M, panel_rows), pn = panels_of(c->N, panel_cols);
+  const int64_t last_rows = c->M - (pm - 1) * panel_rows, last_cols = c->N - (pn - 1) * panel_cols;
   size_t need = 0;
-  const int64_t rows[2] = {panel_rows < c->M ? panel_rows : c->M, last_rows};
-  const int64_t cols[2] = {panel_cols < c->N ? panel_cols : c->N, last_cols};
-  for (int i = 0; i < 2; ++i) {
-    for (int j = 0; j < 2; ++j) {
-      const size_t b = b200fp8_workspace_bytes(rows[i], cols[j], c->K, c->flags);
-      if (b == 0) return 0;
-      if (b > need) need = b;
-    }
+  auto ask = [&](int64_t rows, int64_t cols) {
+    if (rows <= 0 || cols <= 0) return true;
+    const size_t b = b200fp8_workspace_bytes(rows < c->M ? rows : c->M, cols < c->N ? cols : c->N, c->K, c->flags);
+    if (b == 0) return false;
+    if (b > need) need = b;
+    return true;
+  };
+  for (int j = 1; j <= pn; ++j) {
+    const int64_t cols = j < pn ? j * panel_cols : c->N;
+    if (!ask(panel_rows, cols) || !ask(last_rows, cols)) return 0;
+  }
+  for (int i = 1; i <= pm; ++i) {
+    const int64_t rows = i < pm ? i * panel_rows : c->M;
+    if (!ask(rows, panel_cols) || !ask(rows, last_cols)) return 0;
   }
   return (need + 255) / 256 * 256;
 }
 
-// Upload order: always the operand of which the smaller fraction is on the device (X on a tie); after each
-// upload, every block that has just become computable.
+// Upload order: always the operand of which the smaller fraction is on the device (X on a tie).
 int build_schedule(int pm, int pn, bool weights_resident, HostStep* steps) {
   int n = 0, up_x = 0, up_w = weights_resident ? pn : 0;
   while (up_x < pm || up_w < pn) {
     const bool send_x = up_w >= pn || (up_x < pm && up_x * pn <= up_w * pm);
     if (send_x) {
-      steps[n++] = {0, up_x, 0};
-      for (int j = 0; j < up_w; ++j) steps[n++] = {2, up_x, j};
-      ++up_x;
+      steps[n++] = {0, up_x++};
     } else {
-      steps[n++] = {1, up_w, 0};
-      for (int i = 0; i < up_x; ++i) steps[n++] = {2, i, up_w};
-      ++up_w;
+      steps[n++] = {1, up_w++};
     }
   }
   return n;
@@ -1001,12 +1003,8 @@ int b200fp8_host_ctx_destroy(b200fp8_host_ctx* c) {
   cudaFree(c->d_y);
   cudaFree(c->d_workspace);
   if (c->h_status) cudaFreeHost(c->h_status);
-  if (c->ev_done) cudaEventDestroy(c->ev_done);
-  for (int i = 0; i < kMaxPanels; ++i) {
-    if (c->ev_x[i]) cudaEventDestroy(c->ev_x[i]);
-    if (c->ev_w[i]) cudaEventDestroy(c->ev_w[i]);
-  }
-  for (int i = 0; i < kMaxBlocks; ++i) {
+  for (int i = 0; i < kMaxCalls; ++i) {
+    if (c->ev_up[i]) cudaEventDestroy(c->ev_up[i]);
     if (c->ev_y[i]) cudaEventDestroy(c->ev_y[i]);
   }
   if (c->s_in) cudaStreamDestroy(c->s_in);
@@ -1024,16 +1022,14 @@ int b200fp8_host_ctx_set_panels(b200fp8_host_ctx* c, int64_t panel_rows, int64_t
   if (panel_rows < c->M && panel_rows % 128 != 0) return B200FP8_BAD_ARG;
   if (panel_cols < c->N && panel_cols % 256 != 0) return B200FP8_BAD_ARG;
   const int pm = panels_of(c->M, panel_rows), pn = panels_of(c->N, panel_cols);
-  if (pm > kMaxPanels || pn > kMaxPanels || pm * pn > kMaxBlocks) return B200FP8_TOO_LARGE;
+  if (pm > kMaxPanels || pn > kMaxPanels) return B200FP8_TOO_LARGE;
   DeviceGuard guard;
   cudaError_t e = guard.enter(c->device);
   if (e != cudaSuccess) return note_cuda(e);
-  const size_t per_block = block_workspace_bytes(c, panel_rows, panel_cols);
-  const size_t per_row_panel = block_workspace_bytes(c, panel_rows, c->N);  // the grid used while W is resident
-  if (per_block == 0 || per_row_panel == 0) return B200FP8_BAD_ARG;
-  const size_t per = per_block > per_row_panel ? per_block : per_row_panel;
-  // kernels that need only the status word share one workspace; the others get one per block
-  const size_t total = per == B200FP8_WORKSPACE_HEADER_BYTES ? per : per * static_cast<size_t>(pm) * pn;
+  const size_t per = strip_workspace_bytes(c, panel_rows, panel_cols);  // covers the full-width strips of resident weights
+  if (per == 0) return B200FP8_BAD_ARG;
+  // kernels that need only the status word share one workspace; the others get one per GEMM of a call
+  const size_t total = per == B200FP8_WORKSPACE_HEADER_BYTES ? per : per * static_cast<size_t>(pm + pn);
   if (total > c->workspace_total) {
     sync_all(c);
     cudaFree(c->d_workspace);
@@ -1072,10 +1068,9 @@ int b200fp8_host_ctx_create(int64_t M, int64_t N, int64_t K, uint32_t flags, b20
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_compute, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking);
-  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_done, cudaEventDisableTiming);
-  for (int i = 0; i < kMaxPanels && e == cudaSuccess; ++i) {
-    e = cudaEventCreateWithFlags(&c->ev_x[i], cudaEventDisableTiming);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_w[i], cudaEventDisableTiming);
+  for (int i = 0; i < kMaxCalls && e == cudaSuccess; ++i) {
+    e = cudaEventCreateWithFlags(&c->ev_up[i], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_y[i], cudaEventDisableTiming);
   }
   if (e == cudaSuccess) e = cudaMalloc(&c->d_x, static_cast<size_t>(M) * K);
   if (e == cudaSuccess) e = cudaMalloc(&c->d_w, static_cast<size_t>(N) * K);
@@ -1083,7 +1078,7 @@ int b200fp8_host_ctx_create(int64_t M, int64_t N, int64_t K, uint32_t flags, b20
   if (e == cudaSuccess) e = cudaMalloc(&c->d_ws, static_cast<size_t>(N) * sizeof(float));
   if (e == cudaSuccess) e = cudaMalloc(&c->d_bias, static_cast<size_t>(N) * sizeof(__nv_bfloat16));
   if (e == cudaSuccess) e = cudaMalloc(&c->d_y, static_cast<size_t>(M) * N * sizeof(__nv_bfloat16));
-  if (e == cudaSuccess) e = cudaMallocHost(&c->h_status, sizeof(uint32_t) * kMaxBlocks);
+  if (e == cudaSuccess) e = cudaMallocHost(&c->h_status, sizeof(uint32_t) * kMaxCalls);
   if (e != cudaSuccess) {
     b200fp8_host_ctx_destroy(c);
     return note_cuda(e);
@@ -1147,7 +1142,7 @@ int b200fp8_gemm_rowwise_host(b200fp8_host_ctx* c, const void* xq, const void* w
   const int pm = panels_of(c->M, panel_rows), pn = panels_of(c->N, panel_cols);
   const bool shared_workspace = c->workspace_bytes == B200FP8_WORKSPACE_HEADER_BYTES;
   const bool use_bias = resident ? c->bias_resident : bias_bf16 != nullptr;
-  HostStep steps[2 * kMaxPanels + kMaxBlocks];
+  HostStep steps[kMaxCalls];
   const int num_steps = build_schedule(pm, pn, resident, steps);
 
   // the scales and the bias are a few KB: all of them first
@@ -1163,39 +1158,39 @@ int b200fp8_gemm_rowwise_host(b200fp8_host_ctx* c, const void* xq, const void* w
   const uint8_t* w_host = static_cast<const uint8_t*>(wq);
   __nv_bfloat16* y_host = static_cast<__nv_bfloat16*>(y_bf16);
   int status = B200FP8_OK;
-  int blocks = 0;
+  int calls = 0;
+  size_t rows_up = 0, cols_up = resident ? N : 0;  // rows of X / rows of W on the device so far
   for (int s = 0; s < num_steps && e == cudaSuccess && status == B200FP8_OK; ++s) {
     const HostStep& step = steps[s];
+    size_t r0, rows, c0, cols;  // the strip of Y this upload makes computable
     if (step.kind == 0) {
-      const size_t r0 = static_cast<size_t>(step.a) * panel_rows;
-      const size_t rows = r0 + panel_rows <= M ? static_cast<size_t>(panel_rows) : M - r0;
+      r0 = static_cast<size_t>(step.index) * panel_rows;
+      rows = r0 + panel_rows <= M ? static_cast<size_t>(panel_rows) : M - r0;
       e = cudaMemcpyAsync(c->d_x + r0 * K, x_host + r0 * K, rows * K, cudaMemcpyHostToDevice, c->s_in);
-      if (e == cudaSuccess) e = cudaEventRecord(c->ev_x[step.a], c->s_in);
-      continue;
-    }
-    if (step.kind == 1) {
-      const size_t c0 = static_cast<size_t>(step.a) * panel_cols;
-      const size_t cols = c0 + panel_cols <= N ? static_cast<size_t>(panel_cols) : N - c0;
+      rows_up = r0 + rows;
+      c0 = 0;
+      cols = cols_up;
+    } else {
+      c0 = static_cast<size_t>(step.index) * panel_cols;
+      cols = c0 + panel_cols <= N ? static_cast<size_t>(panel_cols) : N - c0;
       e = cudaMemcpyAsync(c->d_w + c0 * K, w_host + c0 * K, cols * K, cudaMemcpyHostToDevice, c->s_in);
-      if (e == cudaSuccess) e = cudaEventRecord(c->ev_w[step.a], c->s_in);
-      continue;
+      cols_up = c0 + cols;
+      r0 = 0;
+      rows = rows_up;
     }
-    const size_t r0 = static_cast<size_t>(step.a) * panel_rows, c0 = static_cast<size_t>(step.b) * panel_cols;
-    const size_t rows = r0 + panel_rows <= M ? static_cast<size_t>(panel_rows) : M - r0;
-    const size_t cols = c0 + panel_cols <= N ? static_cast<size_t>(panel_cols) : N - c0;
-    // the GEMM stream waits for the block's two panels (the scales went up before either)
-    e = cudaStreamWaitEvent(c->s_compute, c->ev_x[step.a], 0);
-    if (e == cudaSuccess && !resident) e = cudaStreamWaitEvent(c->s_compute, c->ev_w[step.b], 0);
+    if (e == cudaSuccess) e = cudaEventRecord(c->ev_up[s], c->s_in);
+    if (e != cudaSuccess || rows == 0 || cols == 0) continue;  // nothing computable yet (the very first upload)
+    // uploads are ordered on one stream: waiting for this one covers every earlier panel and the scales
+    e = cudaStreamWaitEvent(c->s_compute, c->ev_up[s], 0);
     if (e != cudaSuccess) break;
-    uint8_t* ws = c->d_workspace + (shared_workspace ? 0 : static_cast<size_t>(blocks) * c->workspace_bytes);
+    uint8_t* ws = c->d_workspace + (shared_workspace ? 0 : static_cast<size_t>(calls) * c->workspace_bytes);
     status = b200fp8_gemm_rowwise(c->d_x + r0 * K, c->d_w + c0 * K, c->d_xs + r0, c->d_ws + c0,
                                   use_bias ? c->d_bias + c0 : nullptr, c->d_y + r0 * N + c0,
                                   static_cast<int64_t>(rows), static_cast<int64_t>(cols), c->K, c->K, c->K, c->N, ws,
                                   c->workspace_bytes, c->flags, c->s_compute);
     if (status != B200FP8_OK) break;
-    if (c->ev_y[blocks] == nullptr) e = cudaEventCreateWithFlags(&c->ev_y[blocks], cudaEventDisableTiming);
-    if (e == cudaSuccess) e = cudaEventRecord(c->ev_y[blocks], c->s_compute);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->s_out, c->ev_y[blocks], 0);
+    e = cudaEventRecord(c->ev_y[calls], c->s_compute);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(c->s_out, c->ev_y[calls], 0);
     if (e == cudaSuccess) {
       if (cols == N) {
         e = cudaMemcpyAsync(y_host + r0 * N, c->d_y + r0 * N, rows * N * sizeof(__nv_bfloat16), cudaMemcpyDeviceToHost,
@@ -1207,17 +1202,15 @@ int b200fp8_gemm_rowwise_host(b200fp8_host_ctx* c, const void* xq, const void* w
       }
     }
     if (e == cudaSuccess && !shared_workspace) {
-      e = cudaMemcpyAsync(c->h_status + blocks, ws, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->s_out);
+      e = cudaMemcpyAsync(c->h_status + calls, ws, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->s_out);
     }
-    ++blocks;
+    ++calls;
   }
   if (e == cudaSuccess && status == B200FP8_OK && shared_workspace) {
     e = cudaMemcpyAsync(c->h_status, c->d_workspace, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->s_out);
   }
-  // Whatever happened, the caller gets its host buffers back only when no copy is in flight on them.  On
-  // success the download stream finishing last implies the other two have finished (every block's download
-  // waits for its GEMM, which waits for its uploads), but uploads of panels no block needed would not be
-  // covered, so all three are waited for.
+  // Whatever happened, the caller gets its host buffers back only when no copy is in flight on them: all
+  // three streams are waited for.
   const cudaError_t e_in = cudaStreamSynchronize(c->s_in);
   const cudaError_t e_compute = cudaStreamSynchronize(c->s_compute);
   const cudaError_t e_out = cudaStreamSynchronize(c->s_out);
@@ -1230,7 +1223,7 @@ int b200fp8_gemm_rowwise_host(b200fp8_host_ctx* c, const void* xq, const void* w
     c->weights_resident = true;
     c->bias_resident = bias_bf16 != nullptr;
   }
-  const int words = shared_workspace ? 1 : blocks;
+  const int words = shared_workspace ? 1 : calls;
   for (int i = 0; i < words; ++i) {
     if ((c->h_status[i] >> 24) == kDevTimeout) {
       // leave the workspace clean for the next call
