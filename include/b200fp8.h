@@ -49,9 +49,13 @@ typedef enum b200fp8_status {
 #define B200FP8_VARIANT_TC_SPLITK 5u /* few tiles (decode, small M x N): one 128 x BN tile (BN <= 256) per cluster of
                                         1/2/4/8 CTAs that split K and reduce over distributed shared memory, or one
                                         128 x BN tile (BN <= 512) per CTA when that covers the output in one wave */
+#define B200FP8_VARIANT_GEMV 6u      /* M <= 4: CUDA-core GEMV, every warp streams whole rows of W with 128-bit loads and
+                                        finishes them with a warp-shuffle reduction; K a multiple of 16.  Never chosen by
+                                        AUTO: measured slower than TC_SPLITK (the e4m3 conversions and fp32 multiply-adds
+                                        need more issue slots than the memory gives time for)                            */
 #define B200FP8_VARIANT_MASK 0xFu
 #define B200FP8_FLAG_NO_TMA_STORE 0x10u /* tcgen05 variants: write Y with plain stores instead of TMA        */
-/* TC_SPLITK and SKINNY kernels only (what `auto` picks for M <= 128): launch with programmatic stream
+/* TC_SPLITK, SKINNY and GEMV kernels only (TC_SPLITK and SKINNY are what `auto` picks for M <= 128): launch with programmatic stream
  * serialization, so the kernel may start while the kernel before it in the stream still runs.  It reads W
  * (only W) before that kernel has completed, everything else after.  The caller promises that no work still
  * in flight writes W. */

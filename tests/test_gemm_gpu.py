@@ -141,6 +141,57 @@ def test_skinny_kernel_shapes(cuda_device, shape):
     _assert_close(_run("skinny", xq, wq, xs, ws), ref, f"skinny {shape}")
 
 
+GEMV_SHAPES = [(1, 8, 16), (1, 1000, 2320), (2, 520, 400), (3, 2304, 2304), (4, 4096, 6656), (1, 28672, 8192), (2, 9000, 8192),
+               (4, 129, 144), (1, 5000, 16384)]
+
+
+@pytest.mark.parametrize("shape", GEMV_SHAPES)
+def test_gemv_kernel_for_one_to_four_tokens(cuda_device, shape):
+    """The CUDA-core GEMV (128-bit loads of whole rows of W, fp32 accumulation, warp-shuffle reduction): ragged N, K tails
+    of whole 16-byte chunks, bias, fp16 output, a pitched X, and overlapped launches that must not change a bit."""
+    ops = _ops()
+    m, n, k = shape
+    xq, wq, xs, ws = _inputs(m, n, k, seed=11 * m + n, w_std=0.02)
+    bias = (torch.randn(n, generator=torch.Generator().manual_seed(3)) * 0.5).to(torch.bfloat16)
+    ref = orc.gemm_rowwise(xq, wq, xs, ws)
+    y = _run("gemv", xq, wq, xs, ws)
+    _assert_close(y, ref, f"gemv {shape}")
+    _assert_close(_run("gemv", xq, wq, xs, ws, bias=bias), orc.gemm_rowwise(xq, wq, xs, ws, bias), f"gemv {shape} bias")
+    _assert_close(_run("gemv", xq, wq, xs, ws, out_dtype=torch.float16), orc.gemm_rowwise(xq, wq, xs, ws, out_dtype=torch.float16),
+                  f"gemv {shape} fp16")
+    big_x = torch.zeros((m, k + 64), dtype=torch.uint8, device="cuda")
+    big_x[:, :k] = xq.view(torch.uint8).cuda()
+    out_big = torch.zeros((m, n + 8), dtype=torch.bfloat16, device="cuda")
+    got = ops.fp8_gemm_rowwise(big_x[:, :k], wq.cuda(), xs.cuda(), ws.cuda(), out=out_big[:, :n], variant="gemv")
+    assert torch.equal(got, y) and float(out_big[:, n:].abs().max()) == 0.0
+    for _ in range(3):  # back to back with overlapped launches
+        assert torch.equal(ops.fp8_gemm_rowwise(*_gpu(xq, wq, xs, ws), variant="gemv", overlap=True), y)
+    ops.check_device_status()
+    # the tensor-core decode kernel computes the same sums in another order: equal within the tolerance
+    _assert_close(_run("tc_splitk", xq, wq, xs, ws), y.cpu(), f"gemv {shape} vs tc_splitk")
+
+
+def test_gemv_kernel_refuses_what_it_cannot_take(cuda_device):
+    ops = _ops()
+    xq, wq, xs, ws = _gpu(*_inputs(5, 256, 256))
+    with pytest.raises(Exception):
+        ops.fp8_gemm_rowwise(xq, wq, xs, ws, variant="gemv")  # five tokens
+    xq, wq, xs, ws = _inputs(2, 64, 136)  # K is not a multiple of 16
+    big_x = torch.zeros((2, 144), dtype=torch.uint8, device="cuda")
+    big_w = torch.zeros((64, 144), dtype=torch.uint8, device="cuda")
+    with pytest.raises((NotImplementedError, ValueError)):  # no plan: refused when the workspace is sized, or by the call
+        ops.fp8_gemm_rowwise(big_x[:, :136], big_w[:, :136], xs.cuda(), ws.cuda(), variant="gemv")
+    from tritonbench_b200 import lib
+
+    ws256 = torch.zeros(256, dtype=torch.uint8, device="cuda")
+    with pytest.raises(NotImplementedError):
+        ops.fp8_gemm_rowwise(big_x[:, :136], big_w[:, :136], xs.cuda(), ws.cuda(), variant="gemv", workspace=ws256)
+
+    assert lib.describe_plan(1, 28672, 8192).startswith("tc_splitk")  # auto never takes it: measured slower
+    assert lib.describe_plan(1, 28672, 8192, lib.VARIANT_GEMV).startswith("gemv tokens=1 rows_per_warp=7 ctas=256")
+    ops.check_device_status()
+
+
 def test_skinny_workspace_survives_changes_of_geometry(cuda_device):
     """One workspace, problem sizes with different tile counts back to back: the counters a call
     leaves behind must still be zero where the next call looks for its own."""

@@ -96,6 +96,7 @@ struct Plan {
   int group_m;
   SplitPlan splitk;  // one-tile-per-cluster variant
   SkinnyPlan skinny;  // skinny variant
+  GemvPlan gemv;      // GEMV variant
   size_t workspace_bytes;
 };
 
@@ -247,7 +248,8 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
               const DeviceInfo& dev, Plan* out) {
   Plan pl = {};
   uint32_t v = flags & B200FP8_VARIANT_MASK;
-  if (v > B200FP8_VARIANT_TC_SPLITK) return B200FP8_BAD_ARG;
+  if (v > B200FP8_VARIANT_GEMV) return B200FP8_BAD_ARG;
+  const GemvPlan gemv = make_gemv_plan(M, N, K, dev.sm_count);
   if (v == B200FP8_VARIANT_AUTO) {
     if (!operands_tma_ok) {
       v = B200FP8_VARIANT_SIMT;
@@ -281,6 +283,10 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
   } else if (v != B200FP8_VARIANT_SIMT && !operands_tma_ok) {
     return B200FP8_UNSUPPORTED_ALIGNMENT;
   }
+  if (v == B200FP8_VARIANT_GEMV) {
+    if (M > kGemvMaxTokens) return B200FP8_BAD_ARG;
+    if (!gemv.ok) return K % 16 != 0 ? B200FP8_UNSUPPORTED_ALIGNMENT : B200FP8_TOO_LARGE;
+  }
   if (v == B200FP8_VARIANT_SKINNY && M > SkinnyGeometry::kMaxTokens) return B200FP8_BAD_ARG;
   if (v == B200FP8_VARIANT_SKINNY && (N + SkinnyGeometry::kRowsW - 1) / SkinnyGeometry::kRowsW > SkinnyGeometry::kMaxTiles) {
     if ((flags & B200FP8_VARIANT_MASK) != B200FP8_VARIANT_AUTO) return B200FP8_TOO_LARGE;
@@ -309,6 +315,8 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
     // a forced wide tile implies no K split
     pl.splitk = make_split_plan(M, N, K, dev.split_clusters, forced_block_n, forced_block_n > 256 ? 1 : forced_split);
     pl.splitk.overlap_previous_kernel = (flags & B200FP8_FLAG_PDL) != 0;
+  } else if (v == B200FP8_VARIANT_GEMV) {
+    pl.gemv = gemv;
   } else if (v == B200FP8_VARIANT_SKINNY) {
     pl.skinny = make_skinny_plan(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), dev.sm_count);
     pl.skinny.overlap_previous_kernel = (flags & B200FP8_FLAG_PDL) != 0;
@@ -406,6 +414,13 @@ int b200fp8_gemm_rowwise(const void* xq, const void* wq, const float* x_scale, c
                      static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), ldx, ldw, ldy,
                      (flags & B200FP8_FLAG_OUT_FP16) ? 1 : 0};
     return note_cuda(launch_gemm_simt(sp, stream));
+  }
+
+  if (pl.variant == B200FP8_VARIANT_GEMV) {
+    GemvParams gp = {static_cast<const uint8_t*>(xq), static_cast<const uint8_t*>(wq), x_scale, w_scale, bias, y,
+                     static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), ldx, ldw, ldy,
+                     (flags & B200FP8_FLAG_OUT_FP16) ? 1 : 0, (flags & B200FP8_FLAG_PDL) ? 1 : 0, 0};
+    return note_cuda(launch_gemm_gemv(gp, pl.gemv, stream));
   }
 
   if (pl.variant == B200FP8_VARIANT_SKINNY) {
@@ -864,6 +879,10 @@ int b200fp8_describe_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, char*
                pl.splitk.block_n, pl.splitk.split, pl.splitk.rows_a, pl.splitk.stages,
                pl.splitk.tiles * pl.splitk.split, pl.splitk.waves, pl.splitk.smem_bytes, dev.split_clusters[0],
                dev.split_clusters[1], dev.split_clusters[2], dev.split_clusters[3], pl.workspace_bytes);
+      break;
+    case B200FP8_VARIANT_GEMV:
+      snprintf(buf, n, "gemv tokens=%d rows_per_warp=%d ctas=%d threads=512 loads_in_flight=4x16B smem=%zu workspace=%zu",
+               pl.gemv.tokens, pl.gemv.rows_per_warp, pl.gemv.ctas, pl.gemv.smem_bytes, pl.workspace_bytes);
       break;
     case B200FP8_VARIANT_SKINNY:
       snprintf(buf, n,

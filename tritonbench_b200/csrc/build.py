@@ -10,7 +10,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["api.cu", "gemm_tc.cu", "gemm_skinny.cu", "gemm_simt.cu", "quantize.cu", "fused_quantize.cu", "gemm_splitk.cu", "gemm_blockwise.cu"]
+SOURCES = ["api.cu", "gemm_tc.cu", "gemm_skinny.cu", "gemm_simt.cu", "quantize.cu", "fused_quantize.cu", "gemm_splitk.cu", "gemm_blockwise.cu", "gemm_gemv.cu"]
 HEADERS = ["ptx.cuh", "kernels.h", "streamk.cuh", "nanmax.cuh", os.path.join("..", "..", "include", "b200fp8.h")]
 LIB_NAME = "libb200fp8.so"
 

@@ -192,6 +192,32 @@ cudaError_t launch_gemm_skinny(const CUtensorMap& tm_w, const CUtensorMap& tm_x,
 constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB per GPU that loads the library
 cudaError_t skinny_static_scratch(void** device_ptr, size_t* bytes);
 
+// ------------------------ GEMV for one to four tokens (gemm_gemv.cu) ------------------------
+constexpr int kGemvMaxTokens = 4;
+constexpr size_t kGemvMaxSmemBytes = 112 * 1024;  // X as fp16 in shared memory, two CTAs per SM
+struct GemvParams {
+  const uint8_t* xq;
+  const uint8_t* wq;
+  const float* x_scale;
+  const float* w_scale;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* y;
+  int M, N, K;
+  long long ldx, ldw, ldy;
+  int out_fp16;
+  int overlap;        // launched with programmatic stream serialization
+  int rows_per_warp;  // filled in from the plan
+};
+struct GemvPlan {
+  bool ok;            // M <= 4, K a multiple of 16, X fits in shared memory
+  int tokens;         // kernel instance: 1, 2 or 4 rows of X
+  int rows_per_warp;  // rows of W per warp, the same for every warp
+  int ctas;
+  size_t smem_bytes;
+};
+GemvPlan make_gemv_plan(long long M, long long N, long long K, int sm_count);
+cudaError_t launch_gemm_gemv(const GemvParams& p, const GemvPlan& plan, cudaStream_t stream);
+
 // ------------------------------ CUDA-core kernel (gemm_simt.cu) -----------------------------
 struct SimtParams {
   const uint8_t* xq;

@@ -25,6 +25,7 @@ VARIANT_TC_2CTA = 2
 VARIANT_SKINNY = 3
 VARIANT_SIMT = 4
 VARIANT_TC_SPLITK = 5
+VARIANT_GEMV = 6
 FLAG_NO_TMA_STORE = 0x10
 FLAG_PDL = 0x20
 FLAG_OUT_FP16 = 0x40
@@ -45,6 +46,7 @@ VARIANTS = {
     "skinny": VARIANT_SKINNY,
     "simt": VARIANT_SIMT,
     "tc_splitk": VARIANT_TC_SPLITK,
+    "gemv": VARIANT_GEMV,
 }
 WORKSPACE_HEADER_BYTES = 256
 IPC_HANDLE_BYTES = 64
