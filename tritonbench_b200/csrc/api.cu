@@ -211,7 +211,10 @@ SplitPlan make_split_plan(long long M, long long N, long long K, const int* resi
     int candidates[4] = {256, 128, 64, 0};
     if (resident >= tiles_m) {
       const long long tiles_n = resident / tiles_m;                  // tiles along N that fit in one wave
-      long long fit = ((N + tiles_n - 1) / tiles_n + step - 1) / step * step;  // narrowest width that needs no more
+      // narrowest width that needs no more, in whole 32-column steps: MMAs of 144, 176 or 208 columns were measured
+      // at about half the rate of their neighbours of 160, 192 and 224
+      const int fit_step = step < 32 ? 32 : step;
+      long long fit = ((N + tiles_n - 1) / tiles_n + fit_step - 1) / fit_step * fit_step;
       // beyond 256 columns a single CTA multiplies the tile as two halves, no K split then.  Halves that are
       // multiples of 32 columns: an MMA of 144 or 176 columns was measured at half the rate of one of 160.
       if (fit > 256 && split == 1) fit = (fit + 63) / 64 * 64;
