@@ -44,6 +44,27 @@ def test_plugin_through_the_reference_harness_on_gpu(cuda_device):
     assert cells["b200_native"].latency is not None
 
 
+def test_roofline_columns_through_the_reference_harness(cuda_device):
+    """`pct_fp8_peak` and `pct_hbm`: roofline fractions against B200 figures next to the stock metrics."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "tritonbench")):
+        pytest.skip("no installed copy of the tritonbench package on this machine")
+    sys.path.insert(0, ref)
+    from tritonbench_b200 import tritonbench_plugin as plug
+
+    out = plug.run(
+        ["--op", plug.OP_NAME, "--device", "cuda", "--metrics", "latency,tflops,gbps,pct_fp8_peak,pct_hbm", "--only", "b200_native",
+         "--m", "16", "--n", "28672", "--k", "8192"]
+    )
+    text = str(out)
+    assert "b200-pct_fp8_peak" in text and "b200-pct_hbm" in text, text
+    cell = out.result[0][1]["b200_native"]
+    fp8_peak, hbm = plug._b200_peaks()
+    assert abs(cell.extra_metrics["pct_hbm"] - 100.0 * cell.extra_metrics["gbps"] / hbm) < 0.5  # gbps is the operator's own metric
+    assert abs(cell.extra_metrics["pct_fp8_peak"] - 100.0 * cell.tflops / fp8_peak) < 0.5
+    assert 40.0 < cell.extra_metrics["pct_hbm"] < 110.0  # a decode shape: HBM-bound
+
+
 def test_fp8_gemm_operator_backend_through_the_reference_harness(cuda_device):
     """The sibling operator `fp8_gemm`: our column next to its own torch._scaled_mm baseline, both output types."""
     ref = os.path.join(ROOT, "baseline", "_ref")

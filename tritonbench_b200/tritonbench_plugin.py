@@ -102,6 +102,53 @@ def scaled_mm(self, xq, wq, x_scale, w_scale, bias) -> Callable:
     return fn
 
 
+# ------------------------------------------------------------------ roofline metrics
+# The reference's own roofline table has no correct B200 entry (tritonbench/utils/gpu_utils.py:37-46 copies the H100
+# row), so `--metrics ...,pct_fp8_peak,pct_hbm` adds two columns computed against the B200's figures: measured ones
+# from MEASURED_PEAKS.json at the repository root when that file exists (fp8 peak = 2 x the cuBLAS bf16 rate, HBM =
+# the copy bandwidth), else the datasheet's dense FP8 4500 TFLOP/s and 8000 GB/s.
+def _b200_peaks():
+    import json
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return 2.0 * float(p["bf16_tflops"]), float(p["hbm_gbs"])
+    except (OSError, KeyError, ValueError):
+        return 4500.0, 8000.0
+
+
+def _latency_ms(metrics) -> float:
+    """The harness's latency object divides like a number (its p50, components/do_bench/run.py:12-100)."""
+    lat = metrics.latency
+    return float(getattr(lat, "p50", lat))
+
+
+def pct_fp8_peak(self, fn, example_inputs, metrics) -> float:
+    """Per cent of the dense FP8 tensor peak: the operator's own flops (operator.py:248-259) over its latency."""
+    flops = self.flops(fn, example_inputs, metrics)
+    return 100.0 * (flops / _latency_ms(metrics) / 1e12 * 1e3) / _b200_peaks()[0]
+
+
+def pct_hbm(self, fn, example_inputs, metrics) -> float:
+    """Per cent of the HBM bandwidth: the operator's own byte count |a| + |b| + |c| (operator.py:261-271) over its latency."""
+    xq, wq = example_inputs[0], example_inputs[1]
+    nbytes = xq.numel() * xq.element_size() + wq.numel() * wq.element_size() + xq.shape[0] * wq.shape[0] * 2
+    return 100.0 * (nbytes / 1e9 / _latency_ms(metrics) * 1e3) / _b200_peaks()[1]
+
+
+def _register_roofline_metrics(cls) -> None:
+    """register_metric() derives the operator from the function's module (triton_op.py:619-644), so functions
+    defined here are entered into the registry directly and attached to the class."""
+    from tritonbench.utils.triton_op import REGISTERED_METRICS
+
+    for fn in (pct_fp8_peak, pct_hbm):
+        if fn.__name__ not in REGISTERED_METRICS[OP_NAME]:
+            REGISTERED_METRICS[OP_NAME].append(fn.__name__)
+        setattr(cls, fn.__name__, fn)
+
+
 def b200_fp8_gemm(self, a, b) -> Callable:
     """Backend for the sibling operator `fp8_gemm` (tritonbench/operators/fp8_gemm/fp8_gemm.py:47-101): the same
     kernels with unit scales; bf16 output with `--scaling_rowwise`, fp16 output with per-tensor scales, exactly
@@ -396,6 +443,7 @@ def register(with_comparators: bool = True):
         register_benchmark(operator_name=OP_NAME, func_name="torch_dequant_ref", baseline=True)(torch_dequant_ref)
         setattr(cls, "torch_dequant_ref", torch_dequant_ref)
     _wrap_init(cls)
+    _register_roofline_metrics(cls)
     _registered = True
     return cls
 
