@@ -76,6 +76,18 @@ def test_workspace_sizes_and_plans_need_no_device(cdll):
     assert lib.describe_plan(1000, 5120, 3584).startswith("tc_splitk tile=128x320x128 cluster=1")
 
 
+def test_overlapped_launches_of_cache_resident_problems_get_a_ring_for_two_ctas_per_sm(cdll):
+    import re
+
+    smem = lambda plan: int(re.search(r"smem=(\d+)", plan).group(1))  # noqa: E731
+    stages = lambda plan: int(re.search(r"stages=(\d+)", plan).group(1))  # noqa: E731
+    for shape in [(128, 8192, 2304), (4, 13312, 2048), (64, 13312, 2048), (16, 4096, 6656)]:  # W of 19-27 MB
+        deep, shallow = lib.describe_plan(*shape), lib.describe_plan(*shape, lib.FLAG_PDL)
+        assert smem(shallow) <= 227 * 1024 // 2 < smem(deep) and 3 <= stages(shallow) < stages(deep), (shape, deep, shallow)
+    for shape in [(16, 28672, 8192), (32, 8192, 13312)]:  # W of 109-235 MB comes from HBM: the deep ring stays
+        assert lib.describe_plan(*shape, lib.FLAG_PDL).split(" workspace")[0] == lib.describe_plan(*shape).split(" workspace")[0]
+
+
 def test_check_maps_statuses_to_python_exceptions(cdll):
     lib.check(lib.OK, "x")
     with pytest.raises(NotImplementedError):

@@ -188,6 +188,24 @@ static void size_split_plan(long long M, long long K, SplitPlan* p) {
   if (p->smem_bytes < min_smem) p->smem_bytes = min_smem;
 }
 
+// Fewer stages (never fewer than three) until two CTAs fit on an SM by shared memory.
+static void shrink_ring_for_two_ctas(SplitPlan* p) {
+  const int half_sm = SplitGeometry::kSmemPerSm / 2 - 1024;
+  const int bytes_a = p->rows_a * TcGeometry::kBlockK, bytes_b = p->block_n * TcGeometry::kBlockK;
+  while (p->smem_bytes > half_sm && p->stages > 3) {
+    --p->stages;
+    int ring = p->stages * (bytes_a + bytes_b);
+    const int a_overread = p->stages * bytes_a + TcGeometry::kBlockM * TcGeometry::kBlockK;
+    if (ring < a_overread) ring = a_overread;
+    const int exchange = p->split > 1 ? p->block_n * p->rows_a * 4 : 0;
+    if (ring < exchange) ring = exchange;
+    p->ring_bytes = (ring + 1023) / 1024 * 1024;
+    p->smem_bytes = p->ring_bytes + (p->staged_stores ? 32 * 1024 : 0) + split_scale_bytes(p->block_n) + 256 + 1024;
+    const int min_smem = SplitGeometry::min_smem_bytes_for_tmem(split_tmem_cols(p->block_n));
+    if (p->smem_bytes < min_smem) p->smem_bytes = min_smem;
+  }
+}
+
 // CTAs of a configuration that share an SM: by shared memory, and never more than two (168 registers x 192
 // threads).  resident_clusters[] was measured with the largest shared-memory request, one CTA per SM.
 static int split_ctas_per_sm(const SplitPlan& p) {
@@ -318,6 +336,13 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
     // a forced wide tile implies no K split
     pl.splitk = make_split_plan(M, N, K, dev.split_clusters, forced_block_n, forced_block_n > 256 ? 1 : forced_split);
     pl.splitk.overlap_previous_kernel = (flags & B200FP8_FLAG_PDL) != 0;
+    // Overlapped launches of a problem whose W stays in L2 between calls: a ring short enough for two CTAs per
+    // SM lets the next launch's CTAs move in and prefetch W while this launch's CTAs finish (measured, CUDA-graph
+    // replay: 4x13312x2048 8.5 -> 8.0 us, 128x8192x2304 8.1 -> 7.6, 16x4096x6656 8.6 -> 7.6).  When W has to come
+    // from HBM the deep ring matters more (32x8192x13312: 22.7 us deep, 25.3 shallow).
+    if (pl.splitk.overlap_previous_kernel && static_cast<double>(N) * static_cast<double>(K) <= 48.0e6) {
+      shrink_ring_for_two_ctas(&pl.splitk);
+    }
   } else if (v == B200FP8_VARIANT_GEMV) {
     pl.gemv = gemv;
   } else if (v == B200FP8_VARIANT_SKINNY) {
