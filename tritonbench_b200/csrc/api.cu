@@ -87,6 +87,17 @@ int encode_2d(CUtensorMap* tm, CUtensorMapDataType dtype, int elem_bytes, const 
   return B200FP8_OK;
 }
 
+// Height of a rasterisation group of the persistent kernels, in row tiles: the tiles of a group are walked down
+// its rows first, so one column panel of W serves the whole group from L2 and W is read from HBM once per group.
+// 16 row tiles when their X panel (16 x tile_m x K bytes) still leaves room in L2 for the W panels in flight and
+// the problem has at least one full group; 8 otherwise.  Measured, microseconds per launch for heights 8 / 16:
+// 8192^3 377.6 / 370.9, 4096x14336x4096 177.7 / 174.2 (sustained 8192^3 439 / 429); 16384x8192x13312 1225 / 1235,
+// 16384x4096x16384 765 / 770, 3000x7168x2048 41.8 / 42.4 (fewer than 16 row tiles); 24 and more lose everywhere.
+int choose_group_m(int64_t M, int64_t K, int tile_m) {
+  const int64_t tiles_m = (M + tile_m - 1) / tile_m;
+  return tiles_m >= 16 && 16.0 * tile_m * static_cast<double>(K) <= 36.0e6 ? 16 : 8;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 struct Plan {
@@ -315,7 +326,7 @@ int make_plan(int64_t M, int64_t N, int64_t K, uint32_t flags, bool operands_tma
   }
   pl.variant = v;
   pl.tma_store = y_tma_ok && (flags & B200FP8_FLAG_NO_TMA_STORE) == 0;
-  pl.group_m = 8;
+  pl.group_m = choose_group_m(M, K, v == B200FP8_VARIANT_TC_2CTA ? 256 : 128);
   pl.workspace_bytes = B200FP8_WORKSPACE_HEADER_BYTES;
   if (v == B200FP8_VARIANT_TC_1CTA) {
     const int64_t tiles = ((M + 127) / 128) * ((N + 255) / 256);
@@ -574,7 +585,7 @@ int b200fp8_gemm_rowwise_gather(const void* xq, const void* wq, const float* x_s
   tp.ldy = ldy;
   tp.use_tma_store = 1;
   tp.out_fp16 = (flags & B200FP8_FLAG_OUT_FP16) ? 1 : 0;
-  tp.group_m = 8;
+  tp.group_m = choose_group_m(M, K, cta_group == 2 ? 256 : 128);
   tp.num_extra = num_copies - 1;
   tp.status = static_cast<uint32_t*>(workspace);
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
