@@ -289,6 +289,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
     const uint32_t stage_buf = smem_epi + quarter * (2 * Cfg::kStoreRows * Cfg::kStoreCols * 2);
     const uint32_t tmem_empty_remote = kPair ? mapa_cluster(bar_tmem_empty, 0) : bar_tmem_empty;
+    const uint64_t y_policy = l2_policy_evict_first();
     uint32_t local_tile = 0;
     uint32_t store_count = 0;
     bool ok = true;
@@ -392,7 +393,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0 && row0 < row_limit && box_col < p.N) {
-            tma_store_2d(&tm_y, sbuf, box_col, row0);
+            if (p.y_evict_first) {
+              tma_store_2d_hint(&tm_y, sbuf, box_col, row0, y_policy);
+            } else {
+              tma_store_2d(&tm_y, sbuf, box_col, row0);
+            }
             // gathered output: the same box into every other copy of Y (peer GPUs' memory over NVLink); the
             // stores share this box's bulk group, so the staging buffer is reused only when all have read it
             for (int e = 0; e < p.num_extra; ++e) tma_store_2d(&extra.tm[e], sbuf, box_col, row0);

@@ -48,6 +48,7 @@ struct TcParams {
   int num_groups;      // 0: plain GEMM.  >0: rows of X are partitioned into groups (single-CTA variant)
   const int* group_rows;  // [num_groups] rows per group, device memory; group g uses W rows [g*N, (g+1)*N)
   int num_extra;       // copies of Y to write besides `y` (TMA stores only; 0 for the plain GEMM)
+  int y_evict_first;   // TMA stores of Y carry the L2 evict-first hint
   uint32_t* status;    // device status word
 };
 

@@ -177,6 +177,21 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src
                : "memory");
 }
 
+// the same store with an L2 eviction-priority hint (a policy made by l2_policy_evict_first)
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* tm, uint32_t src_smem, int c0, int c1, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+               :
+               : "l"(reinterpret_cast<uint64_t>(tm)), "r"(src_smem), "r"(c0), "r"(c1), "l"(policy)
+               : "memory");
+}
+
+// L2 policy: lines written with it are the first to be evicted (output that nobody re-reads soon)
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 
 template <int kPending>
