@@ -76,6 +76,17 @@ def test_workspace_sizes_and_plans_need_no_device(cdll):
     assert lib.describe_plan(1000, 5120, 3584).startswith("tc_splitk tile=128x320x128 cluster=1")
 
 
+def test_rasterisation_group_height_follows_the_shape(cdll):
+    """16 row tiles per group when their X panel (16 x tile rows x K bytes) is at most 36 MB and M has a full group."""
+    import re
+
+    group = lambda *shape: int(re.search(r"group_m=(\d+)", lib.describe_plan(*shape)).group(1))  # noqa: E731
+    assert group(8192, 8192, 8192) == 16 and group(65536, 8192, 8192) == 16 and group(4096, 14336, 4096) == 16
+    assert group(16384, 8192, 13312) == 8 and group(16384, 4096, 16384) == 8  # 54 and 67 MB X panels
+    assert group(3000, 7168, 2048) == 8 and group(2048, 8192, 2048) == 8  # fewer than 16 row tiles of 256
+    assert group(8192, 8192, 8192, lib.VARIANT_TC_1CTA) == 16 and group(1024, 8192, 8192, lib.VARIANT_TC_1CTA) == 8
+
+
 def test_overlapped_launches_of_cache_resident_problems_get_a_ring_for_two_ctas_per_sm(cdll):
     import re
 
