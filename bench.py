@@ -557,7 +557,15 @@ def e2e_leg(run, m, n, k, xq, xs, wq, ws, steps, flops_step_rank):
         h_w = wq.view(torch.uint8).cpu().contiguous().pin_memory()
         h_xs, h_ws = xs.cpu().pin_memory(), ws.cpu().pin_memory()
         h_out = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
-        pcie = measure_pcie(run.device)
+    # copy rates: every rank at the same time (what the calls below compete for), and rank 0 on its own
+    run.barrier()
+    pcie = measure_pcie(run.device)
+    pcie_alone = None
+    if run.world > 1:
+        run.barrier()
+        if run.rank == 0:
+            pcie_alone = measure_pcie(run.device)
+        run.barrier()
     host = ops.HostGemm(m, n, k)
 
     def loop(send_w: bool):
@@ -591,10 +599,11 @@ def e2e_leg(run, m, n, k, xq, xs, wq, ws, steps, flops_step_rank):
         "api": "b200fp8_gemm_rowwise_host (pinned host buffers in, pinned host buffer out, synchronous; X and W panels "
                "uploaded alternately, each newly computable strip of Y multiplied and downloaded at once)",
         "pcie": pcie,
+        "pcie_one_rank_alone": pcie_alone,
         "pcie_bound_ms": bound_s * 1e3,
         "pcie_frac": bound_s / t_full,
-        "pcie_frac_note": "max(h2d bytes / measured h2d rate, d2h bytes / measured d2h rate) / call time, rank 0's rates; "
-                          "1.0 would need uploads and downloads to overlap completely",
+        "pcie_frac_note": "max(h2d bytes / measured h2d rate, d2h bytes / measured d2h rate) / call time, with rank 0's rates "
+                          "measured while every rank copies at once; 1.0 would need uploads and downloads to overlap completely",
         "aggregate_pcie_gbs": {"h2d": world * h2d / t_full / 1e9, "d2h": world * d2h / t_full / 1e9},
         "numa": binding.note,
         "parity": parity_full,
