@@ -365,6 +365,37 @@ def test_shared_rows_buffer_on_one_rank(cuda_device):
     rows.close()
 
 
+def test_plans_for_random_shapes_agree_with_scaled_mm(cuda_device):
+    """Whatever the planner picks - pair kernel, wide tiles, K split over clusters, short rings under overlapped
+    launches - the result must agree with cuBLASLt's on the same device tensors.  Sixty seeded shapes, with and
+    without the overlap flag, ordinary and Student-t inputs."""
+    import random
+
+    from tritonbench_b200 import lib, quantize
+
+    ops = _ops()
+    rng = random.Random(20240611)
+    seen = set()
+    for i in range(60):
+        m = rng.choice([1, 2, 5, 16, 33, 64, 100, 128, 129, 300, 777, 1000, 1500, 2048, 3000, 4100])
+        n = 16 * rng.randint(1, 1400)
+        k = 16 * rng.randint(1, 600)
+        xq, wq, xs, ws = quantize.make_inputs(m, n, k, device="cuda", x_seed=i, dist="student_t3" if i % 3 == 0 else "normal",
+                                              w_std=0.05)
+        try:
+            want = _scaled_mm_rowwise(xq, wq, xs, ws).float()
+        except RuntimeError:
+            continue
+        tol = orc.bf16_ulp(want) + 1e-2 * want.double().pow(2).mean().sqrt().float()
+        for overlap in (False, True):
+            flags = lib.FLAG_PDL if overlap else 0
+            seen.add(lib.describe_plan(m, n, k, flags).split(" ")[0] + ("+pdl" if overlap else ""))
+            y = ops.fp8_gemm_rowwise(xq, wq, xs, ws, overlap=overlap).float()
+            assert bool(torch.isfinite(y).all()) and bool(((y - want).abs() <= tol).all()), (m, n, k, overlap, lib.describe_plan(m, n, k, flags))
+    ops.check_device_status()
+    assert {"tc_2cta", "tc_splitk", "tc_splitk+pdl"} <= seen, seen
+
+
 # ------------------------------------------------------------------ against the reference's own library call
 def _scaled_mm_rowwise(xq, wq, xs, ws):
     """The torch baseline the operator itself names for this GEMM (tritonbench/operators/fp8_gemm_rowwise/
