@@ -15,8 +15,8 @@
 //
 // A CTA owns a row; what it read stays in registers between the reductions and the quantisation
 // (RMS norm: the packed bf16 row, y is recomputed; SiLU-mul: y in fp32), for rows up to 16384 columns;
-// longer rows recompute the overflow from the inputs.  The common RMS-norm case (aligned rows of at most
-// 8192 columns, no bf16 rounding) runs a persistent form that keeps the weight vector in registers.
+// longer rows recompute the overflow from the inputs.  The common cases (aligned rows, no bf16 rounding; RMS norm
+// up to 16384 columns, SiLU-mul 2561-8192 columns) run persistent forms, described where they are defined.
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -30,6 +30,8 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kVec = 8;      // bf16 elements per 16-byte load
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
@@ -240,79 +242,188 @@ __global__ void __launch_bounds__(kThreads) fused_row_quantize_kernel(const Fuse
   }
 }
 
-// RMS norm, persistent form: a CTA walks over rows blockIdx.x, blockIdx.x + gridDim.x, ... and keeps its
-// slice of the weight vector unpacked in registers for all of them; the next row is requested from memory
-// before the current one is reduced.  Same arithmetic as the kernel above without the bf16 rounding of y.
-// Needs 16-byte aligned rows, cols a multiple of 8 and at most 256 * 8 * kKeep (kKeep <= 4: the weight slice,
-// this row and the next one have to fit in registers).
-template <int kKeep>
-__global__ void __launch_bounds__(kThreads) rms_norm_quantize_persistent_kernel(const FusedQuantParams p) {
-  __shared__ float red[2 * (kThreads / 32)];
+// ---- persistent forms ----
+// A CTA walks over rows blockIdx.x, blockIdx.x + gridDim.x, ...; both need 16-byte aligned rows, cols a multiple
+// of 8 and at most 256 * 8 * kKeep.
+
+// Two fp32 values in one 64-bit register, multiplied / fused-multiply-added two per instruction (sm_100 packed
+// fp32).  Each half rounds as the scalar instruction does, so results do not change.  The values stay in 64-bit
+// registers from the bf16 pair to the e4m3 pair, so that no instruction is spent on packing.
+using pair_t = unsigned long long;
+__device__ __forceinline__ pair_t pack2(float lo, float hi) {
+  pair_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(pair_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ pair_t bf16x2_to_pair(uint32_t h) {  // exact: low half first
+  pair_t r;
+  asm("{\n"
+      ".reg .b32 lo, hi;\n"
+      "shl.b32 lo, %1, 16;\n"
+      "and.b32 hi, %1, 0xffff0000;\n"
+      "mov.b64 %0, {lo, hi};\n"
+      "}\n"
+      : "=l"(r)
+      : "r"(h));
+  return r;
+}
+__device__ __forceinline__ pair_t mul2(pair_t a, pair_t b) {
+  pair_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ pair_t fma2(pair_t a, pair_t b, pair_t c) {
+  pair_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint32_t e4m3x2_of(pair_t v) {  // saturating, low half into the low byte
+  uint16_t r;
+  asm("{\n"
+      ".reg .b32 lo, hi;\n"
+      "mov.b64 {lo, hi}, %1;\n"
+      "cvt.rn.satfinite.e4m3x2.f32 %0, hi, lo;\n"
+      "}\n"
+      : "=h"(r)
+      : "l"(v));
+  return r;
+}
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
+// RMS norm.  At 6.5 TB/s an SM has about 14 issue slots per element, which is what the straightforward kernel
+// spends (it measured 72 % issue-slot utilisation and 0.82 of the HBM bandwidth), so this one saves instructions
+// and waits:
+//   * the rows live in a ring in shared memory instead of registers: each thread copies its own 16-byte vectors
+//     with cp.async and reads back only what it copied itself, so the ring needs no barrier (cp.async.wait_group is
+//     a hardware wait, like a load's); with the rows out of the register file twice as many CTAs fit on an SM;
+//   * multiplications go two per instruction, on values that stay in 64-bit registers;
+//   * one barrier per row: the warps' partial sums alternate between two buffers by row parity, every warp combines
+//     them itself (in a fixed order) and computes the row's scalars.
+// The CTA has one warp per 1024 columns (a thread owns four 16-byte vectors of a row), so a thread's work per row
+// is the same for every row length up to 16384; its slice of the weight vector stays unpacked in registers for
+// all the rows the CTA walks over.  Same arithmetic per element as the one-row-per-CTA kernel without the bf16
+// rounding of y.
+constexpr int kRmsStages = 3;       // this row and the two after it
+constexpr int kRmsVecs = 4;         // 16-byte vectors of a row per thread
+constexpr int kRmsMaxWarps = 16;     // rows of at most 16 * 32 * 4 * 8 = 16384 columns
+__host__ __device__ constexpr int rms_ctas_per_sm(int warps) { return 32 / warps; }                   // 32 warps of these per SM
+__host__ __device__ constexpr int rms_pow2_at_least(int n) { return n <= 1 ? 1 : 2 * rms_pow2_at_least((n + 1) / 2); }
+
+template <int kWarpsT>  // the CTA size is a compile-time constant: index arithmetic costs issue slots too
+__global__ void __launch_bounds__(32 * kWarpsT, rms_ctas_per_sm(kWarpsT)) rms_norm_quantize_persistent_kernel(const FusedQuantParams p) {
+  extern __shared__ uint4 ring[];              // [kRmsStages][kRmsVecs][threads]
+  __shared__ float part[2][2 * kRmsMaxWarps];  // by row parity; per warp: sum of squares, max |x w|
   const __nv_bfloat16* wvec = static_cast<const __nv_bfloat16*>(p.x2);
   const int nvec = p.cols / kVec;
-  float w[kKeep][8];
+  constexpr int threads = 32 * kWarpsT, warps = kWarpsT;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pair_t w[kRmsVecs][4];
 #pragma unroll
-  for (int i = 0; i < kKeep; ++i) {
-    const int v = threadIdx.x + i * kThreads;
-    if (v < nvec) {
-      unpack8(*reinterpret_cast<const uint4*>(wvec + v * kVec), w[i]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) w[i][j] = 0.0f;
-    }
+  for (int k = 0; k < kRmsVecs; ++k) {
+    const int v = threadIdx.x + k * threads;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (v < nvec) raw = *reinterpret_cast<const uint4*>(wvec + v * kVec);
+    w[k][0] = bf16x2_to_pair(raw.x);
+    w[k][1] = bf16x2_to_pair(raw.y);
+    w[k][2] = bf16x2_to_pair(raw.z);
+    w[k][3] = bf16x2_to_pair(raw.w);
   }
-  uint4 cur[kKeep];
+  auto request = [&](long long r, int stage) {  // one group per call, also when there is no such row
+    if (r < p.rows) {
+      const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.x1) + r * p.ld1;
+#pragma unroll
+      for (int k = 0; k < kRmsVecs; ++k) {
+        const int v = threadIdx.x + k * threads;
+        if (v < nvec) cp_async_16(smem_addr(&ring[(stage * kRmsVecs + k) * threads + threadIdx.x]), x + v * kVec);
+      }
+    }
+    cp_async_commit();
+  };
   long long row = blockIdx.x;
-  if (row < p.rows) {
-    const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.x1) + row * p.ld1;
 #pragma unroll
-    for (int i = 0; i < kKeep; ++i) {
-      const int v = threadIdx.x + i * kThreads;
-      cur[i] = v < nvec ? *reinterpret_cast<const uint4*>(x + v * kVec) : make_uint4(0u, 0u, 0u, 0u);
-    }
-  }
+  for (int s = 0; s < kRmsStages - 1; ++s) request(row + static_cast<long long>(s) * gridDim.x, s);
+  int stage = 0, parity = 0;
   for (; row < p.rows; row += gridDim.x) {
-    uint4 nxt[kKeep];
-    const long long next_row = row + gridDim.x;
-    if (next_row < p.rows) {  // in flight while this row is reduced and written
-      const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.x1) + next_row * p.ld1;
+    // refill the stage this thread emptied one row ago, then wait for this row: the newest kRmsStages - 1 groups may
+    // still be on their way
+    request(row + static_cast<long long>(kRmsStages - 1) * gridDim.x, stage == 0 ? kRmsStages - 1 : stage - 1);
+    cp_async_wait<kRmsStages - 1>();
+    pair_t ss = pack2(0.0f, 0.0f);
+    float amax = 0.0f;
 #pragma unroll
-      for (int i = 0; i < kKeep; ++i) {
-        const int v = threadIdx.x + i * kThreads;
-        nxt[i] = v < nvec ? *reinterpret_cast<const uint4*>(x + v * kVec) : make_uint4(0u, 0u, 0u, 0u);
+    for (int k = 0; k < kRmsVecs; ++k) {
+      const int v = threadIdx.x + k * threads;
+      if (v < nvec) {  // vectors beyond the row add nothing
+        const uint4 raw = ring[(stage * kRmsVecs + k) * threads + threadIdx.x];
+        const uint32_t h[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const pair_t a = bf16x2_to_pair(h[j]);
+          ss = fma2(a, a, ss);
+          float lo, hi;
+          unpack2(mul2(a, w[k][j]), lo, hi);
+          amax = max_nan(amax, fabsf(lo));
+          amax = max_nan(amax, fabsf(hi));
+        }
       }
     }
-    float ss = 0.0f, amax_xw = 0.0f;
+    float s_lo, s_hi;
+    unpack2(ss, s_lo, s_hi);
+    float s = s_lo + s_hi;
 #pragma unroll
-    for (int i = 0; i < kKeep; ++i) {  // vectors beyond the row are zeros: they add nothing
-      float a[8];
-      unpack8(cur[i], a);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        ss = fmaf(a[j], a[j], ss);
-        amax_xw = max_nan(amax_xw, fabsf(a[j] * w[i][j]));
-      }
+    for (int o = 16; o > 0; o >>= 1) {
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+      amax = max_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     }
-    block_reduce_sum_max(ss, amax_xw, red);
-    const float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(ss, static_cast<float>(p.cols)) + p.eps));
-    const float scale = __fdiv_rn(max_nan(amax_xw * inv_rms, 1e-12f), 448.0f);
+    if (lane == 0) {
+      part[parity][warp] = s;
+      part[parity][kRmsMaxWarps + warp] = amax;
+    }
+    __syncthreads();  // the only barrier of the row
+    constexpr int kSlots = rms_pow2_at_least(warps);
+    const int src = lane & (kSlots - 1);  // every group of kSlots lanes combines the same slots
+    float t = src < warps ? part[parity][src] : 0.0f;
+    float m = src < warps ? part[parity][kRmsMaxWarps + src] : 0.0f;
+#pragma unroll
+    for (int o = kSlots / 2; o > 0; o >>= 1) {  // a fixed order: the result does not depend on timing
+      t += __shfl_xor_sync(0xffffffffu, t, o);
+      m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, o));
+    }
+    parity ^= 1;
+    const float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(t, static_cast<float>(p.cols)) + p.eps));
+    const float scale = __fdiv_rn(max_nan(m * inv_rms, 1e-12f), 448.0f);
     const float inv_scale = __fdiv_rn(1.0f, scale);
     if (threadIdx.x == 0) p.scale[row] = scale;
+    const pair_t inv_rms2 = pack2(inv_rms, inv_rms), inv_scale2 = pack2(inv_scale, inv_scale);
     uint8_t* q = p.q + row * p.ldq;
 #pragma unroll
-    for (int i = 0; i < kKeep; ++i) {
-      const int v = threadIdx.x + i * kThreads;
+    for (int k = 0; k < kRmsVecs; ++k) {
+      const int v = threadIdx.x + k * threads;
       if (v < nvec) {
-        float a[8], y[8];
-        unpack8(cur[i], a);
+        const uint4 raw = ring[(stage * kRmsVecs + k) * threads + threadIdx.x];
+        const uint32_t h[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t c[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = (a[j] * inv_rms) * w[i][j];
-        *reinterpret_cast<uint2*>(q + v * kVec) = codes8(y, inv_scale);
+        for (int j = 0; j < 4; ++j) {  // q = e4m3(((x / rms) * w) / scale), rounded after every multiplication
+          c[j] = e4m3x2_of(mul2(mul2(mul2(bf16x2_to_pair(h[j]), inv_rms2), w[k][j]), inv_scale2));
+        }
+        *reinterpret_cast<uint2*>(q + v * kVec) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
       }
     }
-#pragma unroll
-    for (int i = 0; i < kKeep; ++i) cur[i] = nxt[i];
+    stage = stage + 1 == kRmsStages ? 0 : stage + 1;
   }
+  cp_async_wait<0>();  // nothing of this CTA's is in flight when it leaves
 }
 
 // SiLU-mul, persistent form: the next row of both inputs is in flight while the current one is reduced
@@ -389,10 +500,43 @@ cudaError_t launch_persistent(Kernel kernel, std::atomic<int>* ctas_per_device, 
   return cudaGetLastError();
 }
 
-template <int kKeep>
-cudaError_t launch_rms_persistent(const FusedQuantParams& p, cudaStream_t stream) {
+// one warp per 1024 columns; the grid fills the GPU with as many CTAs as fit (cached per device)
+template <int kWarpsT>
+cudaError_t launch_rms_persistent_t(const FusedQuantParams& p, cudaStream_t stream) {
   static std::atomic<int> ctas_per_device[64] = {};
-  return launch_persistent(rms_norm_quantize_persistent_kernel<kKeep>, ctas_per_device, p, stream);
+  constexpr int threads = 32 * kWarpsT;
+  constexpr size_t ring_bytes = static_cast<size_t>(kRmsStages) * kRmsVecs * threads * sizeof(uint4);
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  int ctas = ctas_per_device[dev].load();
+  if (ctas == 0) {  // first call on this device (two threads may both get here: they compute the same values)
+    int sms = 0, per_sm = 0;
+    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) return err;
+    err = cudaFuncSetAttribute(rms_norm_quantize_persistent_kernel<kWarpsT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(ring_bytes));
+    if (err != cudaSuccess) return err;
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rms_norm_quantize_persistent_kernel<kWarpsT>, threads,
+                                                        ring_bytes);
+    if (err != cudaSuccess) return err;
+    ctas = sms * (per_sm > 0 ? per_sm : 1);
+    ctas_per_device[dev] = ctas;
+  }
+  const long long grid = p.rows < ctas ? p.rows : ctas;
+  rms_norm_quantize_persistent_kernel<kWarpsT><<<static_cast<unsigned>(grid), threads, ring_bytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+template <int kWarpsT = 1>
+cudaError_t launch_rms_persistent(int warps, const FusedQuantParams& p, cudaStream_t stream) {
+  if constexpr (kWarpsT > kRmsMaxWarps) {
+    return cudaErrorInvalidValue;
+  } else {
+    if (warps == kWarpsT) return launch_rms_persistent_t<kWarpsT>(p, stream);
+    return launch_rms_persistent<kWarpsT + 1>(warps, p, stream);
+  }
 }
 
 template <int kKeep>
@@ -417,9 +561,9 @@ cudaError_t launch_producer(const FusedQuantParams& p, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t launch_fused_row_quantize(const FusedQuantParams& p, cudaStream_t stream) {
-  if (p.producer == kProducerRmsNorm && !p.round_bf16 && p.vector_ok && p.cols % kVec == 0) {
-    if (p.cols <= 2 * kThreads * kVec) return launch_rms_persistent<2>(p, stream);
-    if (p.cols <= 4 * kThreads * kVec) return launch_rms_persistent<4>(p, stream);
+  if (p.producer == kProducerRmsNorm && !p.round_bf16 && p.vector_ok && p.cols % kVec == 0 &&
+      p.cols <= kRmsMaxWarps * 32 * kRmsVecs * kVec) {
+    return launch_rms_persistent((p.cols + 1023) / 1024, p, stream);
   }
   // (rows of up to 2560 columns give a thread too little to do between two block reductions: measured slower)
   if (p.producer == kProducerSiluMul && !p.round_bf16 && p.vector_ok && p.cols % kVec == 0 && p.cols > 2560) {
