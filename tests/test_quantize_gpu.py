@@ -168,7 +168,9 @@ def test_rms_norm_quantiser(cuda_device, shape, round_bf16):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("shape", [(16, 8192), (128, 2304), (3, 1000), (5, 20000), (64, 4104), (7, 33), (1500, 4096), (3000, 2816)])
+@pytest.mark.parametrize("shape", [(16, 8192), (128, 2304), (3, 1000), (5, 20000), (64, 4104), (7, 33), (1500, 4096), (3000, 2816),
+                                   # the persistent kernel with 16, 13 and 1 warps per row, and many rows per CTA
+                                   (300, 16384), (700, 13312), (40000, 512), (4000, 8192)])
 @pytest.mark.parametrize("round_bf16", [False, True])
 def test_silu_mul_quantiser(cuda_device, shape, round_bf16):
     from oracle import fp8_rowwise_oracle as orc

@@ -426,51 +426,93 @@ __global__ void __launch_bounds__(32 * kWarpsT, rms_ctas_per_sm(kWarpsT)) rms_no
   cp_async_wait<0>();  // nothing of this CTA's is in flight when it leaves
 }
 
-// SiLU-mul, persistent form: the next row of both inputs is in flight while the current one is reduced
-// and written.  Same arithmetic as the one-row-per-CTA kernel without the bf16 rounding of y.
-template <int kKeep>
-__global__ void __launch_bounds__(kThreads) silu_mul_quantize_persistent_kernel(const FusedQuantParams p) {
-  __shared__ float red[kThreads / 32];
+// SiLU-mul, persistent form: the next row of both inputs is in flight (in registers: a shared-memory ring made this
+// kernel slower, its exponentials and reciprocals already queue where shared-memory traffic does) while the current
+// one is reduced and written.  Multiplications and the addition go two per instruction, the row's maximum needs one
+// barrier (the warps' results alternate between two buffers by row parity).  Same arithmetic per element as
+// silu_mul(): ex2.approx and rcp.approx, everything else rounded to nearest.
+__device__ __forceinline__ pair_t add2(pair_t a, pair_t b) {
+  pair_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ pair_t silu_mul2(pair_t a, pair_t b) {
+  float t0, t1, e0, e1, d0, d1, r0, r1;
+  unpack2(mul2(a, pack2(-1.4426950408889634f, -1.4426950408889634f)), t0, t1);  // exp(-a) = 2^(-a log2 e)
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(t0));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(t1));
+  unpack2(add2(pack2(e0, e1), pack2(1.0f, 1.0f)), d0, d1);
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(d0));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(d1));
+  return mul2(mul2(a, pack2(r0, r1)), b);
+}
+
+__host__ __device__ constexpr int silu_ctas_per_sm(int warps) { return warps <= 24 ? 24 / warps : 1; }  // 85 registers a thread
+constexpr int kSiluVecs = 4;  // 16-byte vectors of a row (of each input) per thread: one warp per 1024 columns, as above
+
+template <int kWarpsT>
+__global__ void __launch_bounds__(32 * kWarpsT, silu_ctas_per_sm(kWarpsT)) silu_mul_quantize_persistent_kernel(const FusedQuantParams p) {
+  constexpr int kKeep = kSiluVecs, threads = 32 * kWarpsT;
+  __shared__ float red[2][kRmsMaxWarps];
   const int nvec = p.cols / kVec;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint4 cur1[kKeep], cur2[kKeep];
   auto load_row = [&](long long r, uint4 (&a)[kKeep], uint4 (&b)[kKeep]) {
     const __nv_bfloat16* x1 = static_cast<const __nv_bfloat16*>(p.x1) + r * p.ld1;
     const __nv_bfloat16* x2 = static_cast<const __nv_bfloat16*>(p.x2) + r * p.ld2;
 #pragma unroll
     for (int i = 0; i < kKeep; ++i) {
-      const int v = threadIdx.x + i * kThreads;
+      const int v = threadIdx.x + i * threads;
       a[i] = v < nvec ? *reinterpret_cast<const uint4*>(x1 + v * kVec) : make_uint4(0u, 0u, 0u, 0u);
       b[i] = v < nvec ? *reinterpret_cast<const uint4*>(x2 + v * kVec) : make_uint4(0u, 0u, 0u, 0u);
     }
   };
   long long row = blockIdx.x;
+  int parity = 0;
   if (row < p.rows) load_row(row, cur1, cur2);
   for (; row < p.rows; row += gridDim.x) {
     uint4 nxt1[kKeep], nxt2[kKeep];
     const long long next_row = row + gridDim.x;
     if (next_row < p.rows) load_row(next_row, nxt1, nxt2);
-    float y[kKeep][8];
+    pair_t y[kKeep][4];
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < kKeep; ++i) {  // vectors beyond the row are zeros: silu(0) * 0 = 0
-      float a[8], b[8];
-      unpack8(cur1[i], a);
-      unpack8(cur2[i], b);
+      const uint32_t h1[4] = {cur1[i].x, cur1[i].y, cur1[i].z, cur1[i].w};
+      const uint32_t h2[4] = {cur2[i].x, cur2[i].y, cur2[i].z, cur2[i].w};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        y[i][j] = silu_mul(a[j], b[j]);
-        amax = max_nan(amax, fabsf(y[i][j]));
+      for (int j = 0; j < 4; ++j) {
+        y[i][j] = silu_mul2(bf16x2_to_pair(h1[j]), bf16x2_to_pair(h2[j]));
+        float lo, hi;
+        unpack2(y[i][j], lo, hi);
+        amax = max_nan(amax, fabsf(lo));
+        amax = max_nan(amax, fabsf(hi));
       }
     }
-    amax = block_reduce<true>(amax, red);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = max_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) red[parity][warp] = amax;
+    __syncthreads();  // the only barrier of the row
+    constexpr int kSlots = rms_pow2_at_least(kWarpsT);
+    const int src = lane & (kSlots - 1);  // every group of kSlots lanes combines the same slots
+    amax = src < kWarpsT ? red[parity][src] : 0.0f;
+#pragma unroll
+    for (int o = kSlots / 2; o > 0; o >>= 1) amax = max_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    parity ^= 1;
     const float scale = __fdiv_rn(max_nan(amax, 1e-12f), 448.0f);
     const float inv_scale = __fdiv_rn(1.0f, scale);
+    const pair_t inv_scale2 = pack2(inv_scale, inv_scale);
     if (threadIdx.x == 0) p.scale[row] = scale;
     uint8_t* q = p.q + row * p.ldq;
 #pragma unroll
     for (int i = 0; i < kKeep; ++i) {
-      const int v = threadIdx.x + i * kThreads;
-      if (v < nvec) *reinterpret_cast<uint2*>(q + v * kVec) = codes8(y[i], inv_scale);
+      const int v = threadIdx.x + i * threads;
+      if (v < nvec) {
+        uint32_t c[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c[j] = e4m3x2_of(mul2(y[i][j], inv_scale2));
+        *reinterpret_cast<uint2*>(q + v * kVec) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+      }
     }
 #pragma unroll
     for (int i = 0; i < kKeep; ++i) {
@@ -478,26 +520,6 @@ __global__ void __launch_bounds__(kThreads) silu_mul_quantize_persistent_kernel(
       cur2[i] = nxt2[i];
     }
   }
-}
-
-template <typename Kernel>
-cudaError_t launch_persistent(Kernel kernel, std::atomic<int>* ctas_per_device, const FusedQuantParams& p, cudaStream_t stream) {
-  int dev = 0;
-  cudaError_t err = cudaGetDevice(&dev);
-  if (err != cudaSuccess) return err;
-  int ctas = dev < 64 ? ctas_per_device[dev].load() : 0;
-  if (ctas == 0) {
-    int sms = 0, per_sm = 0;
-    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (err != cudaSuccess) return err;
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0);
-    if (err != cudaSuccess) return err;
-    ctas = sms * (per_sm > 0 ? per_sm : 1);
-    if (dev < 64) ctas_per_device[dev] = ctas;
-  }
-  const long long grid = p.rows < ctas ? p.rows : ctas;
-  kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
-  return cudaGetLastError();
 }
 
 // one warp per 1024 columns; the grid fills the GPU with as many CTAs as fit (cached per device)
@@ -539,10 +561,37 @@ cudaError_t launch_rms_persistent(int warps, const FusedQuantParams& p, cudaStre
   }
 }
 
-template <int kKeep>
-cudaError_t launch_silu_persistent(const FusedQuantParams& p, cudaStream_t stream) {
+template <int kWarpsT>
+cudaError_t launch_silu_persistent_t(const FusedQuantParams& p, cudaStream_t stream) {
   static std::atomic<int> ctas_per_device[64] = {};
-  return launch_persistent(silu_mul_quantize_persistent_kernel<kKeep>, ctas_per_device, p, stream);
+  constexpr int threads = 32 * kWarpsT;
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  int ctas = ctas_per_device[dev].load();
+  if (ctas == 0) {
+    int sms = 0, per_sm = 0;
+    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) return err;
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, silu_mul_quantize_persistent_kernel<kWarpsT>, threads, 0);
+    if (err != cudaSuccess) return err;
+    ctas = sms * (per_sm > 0 ? per_sm : 1);
+    ctas_per_device[dev] = ctas;
+  }
+  const long long grid = p.rows < ctas ? p.rows : ctas;
+  silu_mul_quantize_persistent_kernel<kWarpsT><<<static_cast<unsigned>(grid), threads, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+template <int kWarpsT = 1>
+cudaError_t launch_silu_persistent(int warps, const FusedQuantParams& p, cudaStream_t stream) {
+  if constexpr (kWarpsT > kRmsMaxWarps) {
+    return cudaErrorInvalidValue;
+  } else {
+    if (warps == kWarpsT) return launch_silu_persistent_t<kWarpsT>(p, stream);
+    return launch_silu_persistent<kWarpsT + 1>(warps, p, stream);
+  }
 }
 
 template <int kProducer>
@@ -565,10 +614,9 @@ cudaError_t launch_fused_row_quantize(const FusedQuantParams& p, cudaStream_t st
       p.cols <= kRmsMaxWarps * 32 * kRmsVecs * kVec) {
     return launch_rms_persistent((p.cols + 1023) / 1024, p, stream);
   }
-  // (rows of up to 2560 columns give a thread too little to do between two block reductions: measured slower)
-  if (p.producer == kProducerSiluMul && !p.round_bf16 && p.vector_ok && p.cols % kVec == 0 && p.cols > 2560) {
-    if (p.cols <= 2 * kThreads * kVec) return launch_silu_persistent<2>(p, stream);
-    if (p.cols <= 4 * kThreads * kVec) return launch_silu_persistent<4>(p, stream);
+  if (p.producer == kProducerSiluMul && !p.round_bf16 && p.vector_ok && p.cols % kVec == 0 &&
+      p.cols <= kRmsMaxWarps * 32 * kSiluVecs * kVec) {
+    return launch_silu_persistent((p.cols + 1023) / 1024, p, stream);
   }
   if (p.producer == kProducerRmsNorm) return launch_producer<kProducerRmsNorm>(p, stream);
   if (p.producer == kProducerSiluMul) return launch_producer<kProducerSiluMul>(p, stream);

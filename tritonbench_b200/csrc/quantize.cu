@@ -367,6 +367,67 @@ __global__ void __launch_bounds__(kThreads) block_quantize_kernel(const BlockQua
   const T* x = static_cast<const T*>(p.x) + row0 * p.ldx + col;
   uint8_t* q = p.q + row0 * p.ldq + col;
 
+  if constexpr (sizeof(T) == 2) {
+    if (interior) {
+      // 16-bit input, whole block: the 64 values stay packed (32 registers instead of 64, so twice as many CTAs are
+      // resident and in flight), |x| and max work on pairs; same results as the general path below
+      Raw<T> raw[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) raw[i] = load_raw<T>(x + 16ll * i * p.ldx);
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = max_nan(amax, Ops<T, kRecipeFp32>::absmax(raw[i]));
+      amax = block_max(amax, red);
+      float mult = __fmul_rn(__fdiv_rn(1.0f, max_nan(amax, Conv<T>::rnd(1e-12f))), 448.0f);
+      if (isinf(mult)) mult = 1.0f;
+      if (threadIdx.x == 0) p.scale[static_cast<long long>(bm) * p.ld_scale + bk] = __fdiv_rn(1.0f, mult);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const T* h = reinterpret_cast<const T*>(&raw[i].lo);
+        uint32_t w[2];
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+              make_float2(__fmul_rn(Conv<T>::up(h[4 * g]), mult), __fmul_rn(Conv<T>::up(h[4 * g + 1]), mult)), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+              make_float2(__fmul_rn(Conv<T>::up(h[4 * g + 2]), mult), __fmul_rn(Conv<T>::up(h[4 * g + 3]), mult)), __NV_SATFINITE, __NV_E4M3);
+          w[g] = lo | (hi << 16);
+        }
+        *reinterpret_cast<uint2*>(q + 16ll * i * p.ldq) = make_uint2(w[0], w[1]);
+      }
+      return;
+    }
+    // 16-bit input, block on the edge of the matrix (or unaligned rows): element accesses, and the second pass reads
+    // the block again (from L1 / L2) instead of keeping 64 fp32 values, so that this rare path does not set the
+    // kernel's register count
+    float amax = 0.0f;
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i) {
+      if (row0 + 16 * i < p.rows) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (col + j < p.cols) amax = max_nan(amax, fabsf(Conv<T>::up(x[16ll * i * p.ldx + j])));
+        }
+      }
+    }
+    amax = block_max(amax, red);
+    float mult = __fmul_rn(__fdiv_rn(1.0f, max_nan(amax, Conv<T>::rnd(1e-12f))), 448.0f);
+    if (isinf(mult)) mult = 1.0f;
+    if (threadIdx.x == 0) p.scale[static_cast<long long>(bm) * p.ld_scale + bk] = __fdiv_rn(1.0f, mult);
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i) {
+      if (row0 + 16 * i < p.rows) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (col + j < p.cols) {
+            q[16ll * i * p.ldq + j] = to_e4m3(__fmul_rn(Conv<T>::up(x[16ll * i * p.ldx + j]), mult));
+          }
+        }
+      }
+    }
+    return;
+  }
+
   float v[8][8];
   if (interior) {
 #pragma unroll
