@@ -78,10 +78,12 @@ def test_nan_and_infinity_in_every_kernel_form(cuda_device, shape, dtype):
     assert np.array_equal(s.cpu().numpy(), s_want.numpy(), equal_nan=True)
 
 
-# the last eight sit on either side of the boundaries between the three kernels (one warp per row up to 2560 elements and
-# from 64 rows, persistent up to 8192, one CTA per row beyond) and make a persistent CTA walk over many rows
+# the later ones sit on either side of the boundaries between the three kernels (one warp per row up to 2560 elements and
+# from 64 rows, persistent with one warp per 1024 elements up to 16384, one CTA per row beyond) and make a persistent
+# CTA walk over many rows
 @pytest.mark.parametrize("shape", [(1, 16), (3, 7), (17, 130), (64, 8192), (5, 16384), (2, 40000), (300, 1000), (1024, 4096),
-                                   (63, 2048), (64, 2048), (200, 2560), (200, 2568), (3000, 2816), (200, 8200), (77, 512), (5000, 8192)])
+                                   (63, 2048), (64, 2048), (200, 2560), (200, 2568), (3000, 2816), (200, 8200), (77, 512), (5000, 8192),
+                                   (2000, 5120), (900, 13312), (700, 16384), (50, 16392)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 def test_operator_recipe_matches_oracle_on_random_and_ragged_rows(cuda_device, shape, dtype):
     from tritonbench_b200 import ops

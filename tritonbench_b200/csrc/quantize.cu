@@ -208,20 +208,28 @@ __global__ void __launch_bounds__(kThreads) row_quantize_kernel(const QuantParam
   }
 }
 
-// Persistent form for aligned rows of at most 256 * 8 * kKeep elements: a CTA walks over rows blockIdx.x,
+// Persistent form for aligned rows of 2561 to 16384 elements: a CTA of one warp per 1024 elements (a thread owns four
+// vectors of eight, whatever the row length; the CTA size is a compile-time constant) walks over rows blockIdx.x,
 // blockIdx.x + gridDim.x, ... and requests the next row before it reduces and writes the current one, so that
-// memory latency is paid once per CTA instead of once per row.  Same arithmetic, same bits.
-template <typename T, int kRecipe, int kKeep>
-__global__ void __launch_bounds__(kThreads) row_quantize_persistent_kernel(const QuantParams p) {
-  __shared__ float red[kThreads / 32];
+// memory latency is paid once per CTA instead of once per row.  One barrier per row: the warps' maxima alternate
+// between two buffers by row parity and every warp combines them itself.  Same arithmetic, same bits.
+constexpr int kPersistVecs = 4;
+constexpr int kPersistMaxWarps = 16;
+__host__ __device__ constexpr int pow2_at_least(int n) { return n <= 1 ? 1 : 2 * pow2_at_least((n + 1) / 2); }
+
+template <typename T, int kRecipe, int kWarpsT>
+__global__ void __launch_bounds__(32 * kWarpsT) row_quantize_persistent_kernel(const QuantParams p) {
+  constexpr int kKeep = kPersistVecs, threads = 32 * kWarpsT;
+  __shared__ float red[2][kPersistMaxWarps];
   using O = Ops<T, kRecipe>;
   const int nvec = p.cols / kVec;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   Raw<T> cur[kKeep];
   auto load_row = [&](long long r, Raw<T> (&dst)[kKeep]) {
     const T* x = static_cast<const T*>(p.x) + r * p.ldx;
 #pragma unroll
     for (int i = 0; i < kKeep; ++i) {
-      const int v = threadIdx.x + i * kThreads;
+      const int v = threadIdx.x + i * threads;
       if (v < nvec) {
         dst[i] = load_raw<T>(x + v * kVec);
       } else {
@@ -231,6 +239,7 @@ __global__ void __launch_bounds__(kThreads) row_quantize_persistent_kernel(const
     }
   };
   long long row = blockIdx.x;
+  int parity = 0;
   if (row < p.rows) load_row(row, cur);
   for (; row < p.rows; row += gridDim.x) {
     Raw<T> nxt[kKeep];
@@ -239,8 +248,16 @@ __global__ void __launch_bounds__(kThreads) row_quantize_persistent_kernel(const
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < kKeep; ++i) amax = max_nan(amax, O::absmax(cur[i]));
-    __syncthreads();  // the previous row's readers are done with `red`
-    amax = block_max(amax, red);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = max_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) red[parity][warp] = amax;
+    __syncthreads();  // the only barrier of the row
+    constexpr int kSlots = pow2_at_least(kWarpsT);
+    const int src = lane & (kSlots - 1);  // every group of kSlots lanes combines the same slots
+    amax = src < kWarpsT ? red[parity][src] : 0.0f;
+#pragma unroll
+    for (int o = kSlots / 2; o > 0; o >>= 1) amax = max_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    parity ^= 1;
     float mult, scale;
     if constexpr (kRecipe == kRecipeOperator) {
       const float c = max_nan(amax, Conv<T>::rnd(1e-12f));
@@ -255,7 +272,7 @@ __global__ void __launch_bounds__(kThreads) row_quantize_persistent_kernel(const
     uint8_t* q = p.q + row * p.ldq;
 #pragma unroll
     for (int i = 0; i < kKeep; ++i) {
-      const int v = threadIdx.x + i * kThreads;
+      const int v = threadIdx.x + i * threads;
       if (v < nvec) *reinterpret_cast<uint2*>(q + v * kVec) = O::codes(cur[i], mult);
     }
 #pragma unroll
@@ -307,9 +324,10 @@ __global__ void __launch_bounds__(kThreads) row_quantize_short_rows_kernel(const
   }
 }
 
-template <typename T, int kRecipe, int kKeep>
-cudaError_t launch_persistent(const QuantParams& p, cudaStream_t stream) {
+template <typename T, int kRecipe, int kWarpsT>
+cudaError_t launch_persistent_t(const QuantParams& p, cudaStream_t stream) {
   static std::atomic<int> ctas_per_device[64] = {};
+  constexpr int threads = 32 * kWarpsT;
   int dev = 0;
   cudaError_t err = cudaGetDevice(&dev);
   if (err != cudaSuccess) return err;
@@ -318,24 +336,32 @@ cudaError_t launch_persistent(const QuantParams& p, cudaStream_t stream) {
     int sms = 0, per_sm = 0;
     err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (err != cudaSuccess) return err;
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, row_quantize_persistent_kernel<T, kRecipe, kKeep>,
-                                                        kThreads, 0);
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, row_quantize_persistent_kernel<T, kRecipe, kWarpsT>,
+                                                        threads, 0);
     if (err != cudaSuccess) return err;
     ctas = sms * (per_sm > 0 ? per_sm : 1);
     if (dev < 64) ctas_per_device[dev] = ctas;
   }
   const long long grid = p.rows < ctas ? p.rows : ctas;
-  row_quantize_persistent_kernel<T, kRecipe, kKeep><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p);
+  row_quantize_persistent_kernel<T, kRecipe, kWarpsT><<<static_cast<unsigned>(grid), threads, 0, stream>>>(p);
   return cudaGetLastError();
+}
+
+template <typename T, int kRecipe, int kWarpsT = 3>
+cudaError_t launch_persistent(int warps, const QuantParams& p, cudaStream_t stream) {
+  if constexpr (kWarpsT > kPersistMaxWarps) {
+    return cudaErrorInvalidValue;
+  } else {
+    if (warps == kWarpsT) return launch_persistent_t<T, kRecipe, kWarpsT>(p, stream);
+    return launch_persistent<T, kRecipe, kWarpsT + 1>(warps, p, stream);
+  }
 }
 
 template <typename T, int kRecipe>
 cudaError_t launch_recipe(const QuantParams& p, cudaStream_t stream) {
-  // rows of 2561..8192 elements, aligned, a multiple of 8 long: the persistent kernel (shorter rows leave a
-  // thread too little to do between two block reductions)
-  if (p.vector_ok && p.cols % kVec == 0 && p.cols > 2560 && p.cols <= 4 * kThreads * kVec) {
-    if (p.cols <= 2 * kThreads * kVec) return launch_persistent<T, kRecipe, 2>(p, stream);
-    return launch_persistent<T, kRecipe, 4>(p, stream);
+  // rows of 2561..16384 elements, aligned, a multiple of 8 long: the persistent kernel (shorter rows: a warp per row)
+  if (p.vector_ok && p.cols % kVec == 0 && p.cols > 2560 && p.cols <= kPersistMaxWarps * 32 * kPersistVecs * kVec) {
+    return launch_persistent<T, kRecipe>((p.cols + 1023) / 1024, p, stream);
   }
   if (p.vector_ok && p.cols % kVec == 0 && p.cols <= 32 * kVec * kShortRowVecs && p.rows >= 64) {
     const long long ctas = (p.rows + kThreads / 32 - 1) / (kThreads / 32);
