@@ -28,6 +28,13 @@
 namespace b200fp8 {
 namespace {
 
+// A GEMM launched behind one of these kernels with programmatic stream serialization (B200FP8_FLAG_PDL) may start
+// as soon as every CTA here has passed this point: it prefetches W while the quantiser runs and reads what the
+// quantiser wrote only after its own griddepcontrol.wait, i.e. after this grid has completed.  Without such a
+// dependent the instruction does nothing.
+__device__ __forceinline__ void let_dependents_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+
 constexpr int kThreads = 256;
 constexpr int kVec = 8;      // bf16 elements per 16-byte load
 
@@ -101,6 +108,7 @@ __device__ __forceinline__ uint2 codes8(const float (&y)[8], float inv_scale) {
 // kKeep: vectors of 8 elements a thread keeps in registers (rows up to 256 * 8 * kKeep columns stay on chip)
 template <int kProducer, int kKeep>
 __global__ void __launch_bounds__(kThreads) fused_row_quantize_kernel(const FusedQuantParams p) {
+  let_dependents_start();
   __shared__ float red[2 * (kThreads / 32)];
   const long long row = blockIdx.x;
   const __nv_bfloat16* x1 = static_cast<const __nv_bfloat16*>(p.x1) + row * p.ld1;
@@ -322,6 +330,7 @@ __host__ __device__ constexpr int rms_pow2_at_least(int n) { return n <= 1 ? 1 :
 
 template <int kWarpsT>  // the CTA size is a compile-time constant: index arithmetic costs issue slots too
 __global__ void __launch_bounds__(32 * kWarpsT, rms_ctas_per_sm(kWarpsT)) rms_norm_quantize_persistent_kernel(const FusedQuantParams p) {
+  let_dependents_start();
   extern __shared__ uint4 ring[];              // [kRmsStages][kRmsVecs][threads]
   __shared__ float part[2][2 * kRmsMaxWarps];  // by row parity; per warp: sum of squares, max |x w|
   const __nv_bfloat16* wvec = static_cast<const __nv_bfloat16*>(p.x2);
@@ -452,6 +461,7 @@ constexpr int kSiluVecs = 4;  // 16-byte vectors of a row (of each input) per th
 
 template <int kWarpsT>
 __global__ void __launch_bounds__(32 * kWarpsT, silu_ctas_per_sm(kWarpsT)) silu_mul_quantize_persistent_kernel(const FusedQuantParams p) {
+  let_dependents_start();
   constexpr int kKeep = kSiluVecs, threads = 32 * kWarpsT;
   __shared__ float red[2][kRmsMaxWarps];
   const int nvec = p.cols / kVec;

@@ -286,12 +286,16 @@ def _fused_backend(producer: str, round_bf16: bool) -> Callable:
         workspace = ops.get_workspace(x1.device, ops.workspace_bytes(m, n, k))
         w_scale = w_scale.contiguous()
 
+        # decode-sized calls: the GEMM starts while the quantiser runs (it reads W - which nothing writes - early, and
+        # xq / xs only after the quantiser has completed); B200FP8_OVERLAP=0 turns it off
+        overlap = m <= 128 and os.environ.get("B200FP8_OVERLAP", "1") != "0"
+
         def fn():
             if producer == "rms_norm":
                 xq, xs = ops.rms_norm_fp8_rowwise_quant(x1, wd, round_bf16=round_bf16)
             else:
                 xq, xs = ops.silu_mul_fp8_rowwise_quant(x1, x2, round_bf16=round_bf16)
-            return ops.fp8_gemm_rowwise(xq, wq, xs, w_scale, out=out, workspace=workspace)
+            return ops.fp8_gemm_rowwise(xq, wq, xs, w_scale, out=out, workspace=workspace, overlap=overlap)
 
         return fn
 
