@@ -15,8 +15,8 @@
 //
 // A CTA owns a row; what it read stays in registers between the reductions and the quantisation
 // (RMS norm: the packed bf16 row, y is recomputed; SiLU-mul: y in fp32), for rows up to 16384 columns;
-// longer rows recompute the overflow from the inputs.  The common cases (aligned rows, no bf16 rounding; RMS norm
-// up to 16384 columns, SiLU-mul 2561-8192 columns) run persistent forms, described where they are defined.
+// longer rows recompute the overflow from the inputs.  Aligned rows of up to 16384 columns run persistent forms,
+// described where they are defined.
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -288,6 +288,17 @@ __device__ __forceinline__ pair_t fma2(pair_t a, pair_t b, pair_t c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
+__device__ __forceinline__ uint32_t bf16x2_of(pair_t v) {  // round to nearest even, low half into the low 16 bits
+  uint32_t r;
+  asm("{\n"
+      ".reg .b32 lo, hi;\n"
+      "mov.b64 {lo, hi}, %1;\n"
+      "cvt.rn.bf16x2.f32 %0, hi, lo;\n"
+      "}\n"
+      : "=r"(r)
+      : "l"(v));
+  return r;
+}
 __device__ __forceinline__ uint32_t e4m3x2_of(pair_t v) {  // saturating, low half into the low byte
   uint16_t r;
   asm("{\n"
@@ -325,6 +336,7 @@ __device__ __forceinline__ void cp_async_wait() {
 constexpr int kRmsStages = 3;       // this row and the two after it
 constexpr int kRmsVecs = 4;         // 16-byte vectors of a row per thread
 constexpr int kRmsMaxWarps = 16;     // rows of at most 16 * 32 * 4 * 8 = 16384 columns
+__host__ __device__ constexpr int silu_ctas_per_sm(int warps) { return warps <= 24 ? 24 / warps : 1; }  // 24 warps of these per SM: 85 registers a thread
 __host__ __device__ constexpr int rms_ctas_per_sm(int warps) { return 32 / warps; }                   // 32 warps of these per SM
 __host__ __device__ constexpr int rms_pow2_at_least(int n) { return n <= 1 ? 1 : 2 * rms_pow2_at_least((n + 1) / 2); }
 
@@ -435,6 +447,121 @@ __global__ void __launch_bounds__(32 * kWarpsT, rms_ctas_per_sm(kWarpsT)) rms_no
   cp_async_wait<0>();  // nothing of this CTA's is in flight when it leaves
 }
 
+// RMS norm with y rounded to bf16 before the quantisation (`round_bf16`: what a producer kernel followed by a quantiser
+// computes).  The row's maximum must then be taken over the ROUNDED y, so the row needs two reductions: the sum of
+// squares, then max |bf16(y)|; the rounded y is a bf16 value and waits for the second one packed in 16 registers.
+// Otherwise the kernel above: rows in a cp.async ring, one warp per 1024 columns, packed multiplies.
+template <int kWarpsT>
+__global__ void __launch_bounds__(32 * kWarpsT, silu_ctas_per_sm(kWarpsT)) rms_norm_round_quantize_persistent_kernel(const FusedQuantParams p) {
+  let_dependents_start();
+  extern __shared__ uint4 ring[];  // [kRmsStages][kRmsVecs][threads]
+  __shared__ float part_ss[kRmsMaxWarps], part_max[kRmsMaxWarps];
+  const __nv_bfloat16* wvec = static_cast<const __nv_bfloat16*>(p.x2);
+  const int nvec = p.cols / kVec;
+  constexpr int threads = 32 * kWarpsT, warps = kWarpsT;
+  constexpr int kSlots = rms_pow2_at_least(warps);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int src = lane & (kSlots - 1);  // every group of kSlots lanes combines the same slots
+  pair_t w[kRmsVecs][4];
+#pragma unroll
+  for (int k = 0; k < kRmsVecs; ++k) {
+    const int v = threadIdx.x + k * threads;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (v < nvec) raw = *reinterpret_cast<const uint4*>(wvec + v * kVec);
+    w[k][0] = bf16x2_to_pair(raw.x);
+    w[k][1] = bf16x2_to_pair(raw.y);
+    w[k][2] = bf16x2_to_pair(raw.z);
+    w[k][3] = bf16x2_to_pair(raw.w);
+  }
+  auto request = [&](long long r, int stage) {  // one group per call, also when there is no such row
+    if (r < p.rows) {
+      const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.x1) + r * p.ld1;
+#pragma unroll
+      for (int k = 0; k < kRmsVecs; ++k) {
+        const int v = threadIdx.x + k * threads;
+        if (v < nvec) cp_async_16(smem_addr(&ring[(stage * kRmsVecs + k) * threads + threadIdx.x]), x + v * kVec);
+      }
+    }
+    cp_async_commit();
+  };
+  long long row = blockIdx.x;
+#pragma unroll
+  for (int s = 0; s < kRmsStages - 1; ++s) request(row + static_cast<long long>(s) * gridDim.x, s);
+  int stage = 0;
+  for (; row < p.rows; row += gridDim.x) {
+    request(row + static_cast<long long>(kRmsStages - 1) * gridDim.x, stage == 0 ? kRmsStages - 1 : stage - 1);
+    cp_async_wait<kRmsStages - 1>();
+    // ---- sum of squares
+    pair_t ss = pack2(0.0f, 0.0f);
+#pragma unroll
+    for (int k = 0; k < kRmsVecs; ++k) {
+      const int v = threadIdx.x + k * threads;
+      if (v < nvec) {
+        const uint4 raw = ring[(stage * kRmsVecs + k) * threads + threadIdx.x];
+        const uint32_t h[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const pair_t a = bf16x2_to_pair(h[j]);
+          ss = fma2(a, a, ss);
+        }
+      }
+    }
+    float s_lo, s_hi;
+    unpack2(ss, s_lo, s_hi);
+    float s = s_lo + s_hi;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) part_ss[warp] = s;
+    __syncthreads();  // (everybody has also finished reading part_max of the row before)
+    float t = src < warps ? part_ss[src] : 0.0f;
+#pragma unroll
+    for (int o = kSlots / 2; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    const float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(t, static_cast<float>(p.cols)) + p.eps));
+    const pair_t inv_rms2 = pack2(inv_rms, inv_rms);
+    // ---- y = bf16((x / rms) * w), kept packed, and its largest magnitude
+    uint32_t y[kRmsVecs][4];
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kRmsVecs; ++k) {
+      const int v = threadIdx.x + k * threads;
+      const uint4 raw = v < nvec ? ring[(stage * kRmsVecs + k) * threads + threadIdx.x] : make_uint4(0u, 0u, 0u, 0u);
+      const uint32_t h[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        y[k][j] = bf16x2_of(mul2(mul2(bf16x2_to_pair(h[j]), inv_rms2), w[k][j]));
+        float lo, hi;
+        unpack2(bf16x2_to_pair(y[k][j]), lo, hi);
+        amax = max_nan(amax, fabsf(lo));
+        amax = max_nan(amax, fabsf(hi));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = max_nan(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) part_max[warp] = amax;
+    __syncthreads();  // (everybody has also finished reading part_ss of this row)
+    float m = src < warps ? part_max[src] : 0.0f;
+#pragma unroll
+    for (int o = kSlots / 2; o > 0; o >>= 1) m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float scale = __fdiv_rn(max_nan(m, 1e-12f), 448.0f);
+    const float inv_scale = __fdiv_rn(1.0f, scale);
+    const pair_t inv_scale2 = pack2(inv_scale, inv_scale);
+    if (threadIdx.x == 0) p.scale[row] = scale;
+    uint8_t* q = p.q + row * p.ldq;
+#pragma unroll
+    for (int k = 0; k < kRmsVecs; ++k) {
+      const int v = threadIdx.x + k * threads;
+      if (v < nvec) {
+        uint32_t c[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c[j] = e4m3x2_of(mul2(bf16x2_to_pair(y[k][j]), inv_scale2));
+        *reinterpret_cast<uint2*>(q + v * kVec) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+      }
+    }
+    stage = stage + 1 == kRmsStages ? 0 : stage + 1;
+  }
+  cp_async_wait<0>();
+}
+
 // SiLU-mul, persistent form: the next row of both inputs is in flight (in registers: a shared-memory ring made this
 // kernel slower, its exponentials and reciprocals already queue where shared-memory traffic does) while the current
 // one is reduced and written.  Multiplications and the addition go two per instruction, the row's maximum needs one
@@ -456,10 +583,9 @@ __device__ __forceinline__ pair_t silu_mul2(pair_t a, pair_t b) {
   return mul2(mul2(a, pack2(r0, r1)), b);
 }
 
-__host__ __device__ constexpr int silu_ctas_per_sm(int warps) { return warps <= 24 ? 24 / warps : 1; }  // 85 registers a thread
 constexpr int kSiluVecs = 4;  // 16-byte vectors of a row (of each input) per thread: one warp per 1024 columns, as above
 
-template <int kWarpsT>
+template <int kWarpsT, bool kRound>  // kRound: y is rounded to bf16 before the quantisation (`round_bf16`)
 __global__ void __launch_bounds__(32 * kWarpsT, silu_ctas_per_sm(kWarpsT)) silu_mul_quantize_persistent_kernel(const FusedQuantParams p) {
   let_dependents_start();
   constexpr int kKeep = kSiluVecs, threads = 32 * kWarpsT;
@@ -493,6 +619,7 @@ __global__ void __launch_bounds__(32 * kWarpsT, silu_ctas_per_sm(kWarpsT)) silu_
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         y[i][j] = silu_mul2(bf16x2_to_pair(h1[j]), bf16x2_to_pair(h2[j]));
+        if constexpr (kRound) y[i][j] = bf16x2_to_pair(bf16x2_of(y[i][j]));
         float lo, hi;
         unpack2(y[i][j], lo, hi);
         amax = max_nan(amax, fabsf(lo));
@@ -533,8 +660,9 @@ __global__ void __launch_bounds__(32 * kWarpsT, silu_ctas_per_sm(kWarpsT)) silu_
 }
 
 // one warp per 1024 columns; the grid fills the GPU with as many CTAs as fit (cached per device)
-template <int kWarpsT>
+template <int kWarpsT, bool kRound>
 cudaError_t launch_rms_persistent_t(const FusedQuantParams& p, cudaStream_t stream) {
+  const auto kernel = kRound ? rms_norm_round_quantize_persistent_kernel<kWarpsT> : rms_norm_quantize_persistent_kernel<kWarpsT>;
   static std::atomic<int> ctas_per_device[64] = {};
   constexpr int threads = 32 * kWarpsT;
   constexpr size_t ring_bytes = static_cast<size_t>(kRmsStages) * kRmsVecs * threads * sizeof(uint4);
@@ -547,17 +675,17 @@ cudaError_t launch_rms_persistent_t(const FusedQuantParams& p, cudaStream_t stre
     int sms = 0, per_sm = 0;
     err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (err != cudaSuccess) return err;
-    err = cudaFuncSetAttribute(rms_norm_quantize_persistent_kernel<kWarpsT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                static_cast<int>(ring_bytes));
     if (err != cudaSuccess) return err;
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rms_norm_quantize_persistent_kernel<kWarpsT>, threads,
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads,
                                                         ring_bytes);
     if (err != cudaSuccess) return err;
     ctas = sms * (per_sm > 0 ? per_sm : 1);
     ctas_per_device[dev] = ctas;
   }
   const long long grid = p.rows < ctas ? p.rows : ctas;
-  rms_norm_quantize_persistent_kernel<kWarpsT><<<static_cast<unsigned>(grid), threads, ring_bytes, stream>>>(p);
+  kernel<<<static_cast<unsigned>(grid), threads, ring_bytes, stream>>>(p);
   return cudaGetLastError();
 }
 
@@ -566,12 +694,14 @@ cudaError_t launch_rms_persistent(int warps, const FusedQuantParams& p, cudaStre
   if constexpr (kWarpsT > kRmsMaxWarps) {
     return cudaErrorInvalidValue;
   } else {
-    if (warps == kWarpsT) return launch_rms_persistent_t<kWarpsT>(p, stream);
+    if (warps == kWarpsT) {
+      return p.round_bf16 ? launch_rms_persistent_t<kWarpsT, true>(p, stream) : launch_rms_persistent_t<kWarpsT, false>(p, stream);
+    }
     return launch_rms_persistent<kWarpsT + 1>(warps, p, stream);
   }
 }
 
-template <int kWarpsT>
+template <int kWarpsT, bool kRound>
 cudaError_t launch_silu_persistent_t(const FusedQuantParams& p, cudaStream_t stream) {
   static std::atomic<int> ctas_per_device[64] = {};
   constexpr int threads = 32 * kWarpsT;
@@ -584,13 +714,13 @@ cudaError_t launch_silu_persistent_t(const FusedQuantParams& p, cudaStream_t str
     int sms = 0, per_sm = 0;
     err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (err != cudaSuccess) return err;
-    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, silu_mul_quantize_persistent_kernel<kWarpsT>, threads, 0);
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, silu_mul_quantize_persistent_kernel<kWarpsT, kRound>, threads, 0);
     if (err != cudaSuccess) return err;
     ctas = sms * (per_sm > 0 ? per_sm : 1);
     ctas_per_device[dev] = ctas;
   }
   const long long grid = p.rows < ctas ? p.rows : ctas;
-  silu_mul_quantize_persistent_kernel<kWarpsT><<<static_cast<unsigned>(grid), threads, 0, stream>>>(p);
+  silu_mul_quantize_persistent_kernel<kWarpsT, kRound><<<static_cast<unsigned>(grid), threads, 0, stream>>>(p);
   return cudaGetLastError();
 }
 
@@ -599,7 +729,9 @@ cudaError_t launch_silu_persistent(int warps, const FusedQuantParams& p, cudaStr
   if constexpr (kWarpsT > kRmsMaxWarps) {
     return cudaErrorInvalidValue;
   } else {
-    if (warps == kWarpsT) return launch_silu_persistent_t<kWarpsT>(p, stream);
+    if (warps == kWarpsT) {
+      return p.round_bf16 ? launch_silu_persistent_t<kWarpsT, true>(p, stream) : launch_silu_persistent_t<kWarpsT, false>(p, stream);
+    }
     return launch_silu_persistent<kWarpsT + 1>(warps, p, stream);
   }
 }
@@ -620,11 +752,11 @@ cudaError_t launch_producer(const FusedQuantParams& p, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t launch_fused_row_quantize(const FusedQuantParams& p, cudaStream_t stream) {
-  if (p.producer == kProducerRmsNorm && !p.round_bf16 && p.vector_ok && p.cols % kVec == 0 &&
+  if (p.producer == kProducerRmsNorm && p.vector_ok && p.cols % kVec == 0 &&
       p.cols <= kRmsMaxWarps * 32 * kRmsVecs * kVec) {
     return launch_rms_persistent((p.cols + 1023) / 1024, p, stream);
   }
-  if (p.producer == kProducerSiluMul && !p.round_bf16 && p.vector_ok && p.cols % kVec == 0 &&
+  if (p.producer == kProducerSiluMul && p.vector_ok && p.cols % kVec == 0 &&
       p.cols <= kRmsMaxWarps * 32 * kSiluVecs * kVec) {
     return launch_silu_persistent((p.cols + 1023) / 1024, p, stream);
   }
