@@ -600,6 +600,45 @@ def test_overlapped_launch_of_decode_kernels_back_to_back(cuda_device, variant):
     ops.check_device_status()
 
 
+@pytest.mark.parametrize("producer", ["row_quantize", "rms_norm", "silu_mul"])
+def test_decode_gemm_launched_behind_a_quantiser_of_x_starts_early_and_still_sees_its_output(cuda_device, producer):
+    """The quantiser kernels let a dependent launch start while they run.  A decode GEMM with the overlap flag directly
+    behind a quantiser of X prefetches W early but must read xq and x_scale only after the quantiser has completed:
+    every iteration quantises a different activation into the same buffers, so a GEMM that read early would return the
+    previous iteration's result."""
+    ops = _ops()
+    n, k = 2048, 4096
+    gen = torch.Generator().manual_seed(77)
+    w = (torch.randn(n, k, generator=gen) * 0.05).to(torch.bfloat16).cuda()
+    wq, ws = ops.fp8_row_quantize(w)
+    wd = torch.randn(k, generator=gen).to(torch.bfloat16).cuda()
+    torch.cuda.synchronize()
+    for m in (1, 16, 128):
+        xs_in = [(torch.randn(m, k, generator=gen) * (1 + i)).to(torch.bfloat16).cuda() for i in range(4)]
+        x2 = torch.randn(m, k, generator=gen).to(torch.bfloat16).cuda()
+
+        def quantise(x):
+            if producer == "row_quantize":
+                return ops.fp8_row_quantize(x)
+            if producer == "rms_norm":
+                return ops.rms_norm_fp8_rowwise_quant(x, wd)
+            return ops.silu_mul_fp8_rowwise_quant(x, x2)
+
+        want = []
+        for x in xs_in:  # ordinary launches, a synchronisation between the two kernels
+            xq, xs = quantise(x)
+            torch.cuda.synchronize()
+            want.append(ops.fp8_gemm_rowwise(xq, wq, xs, ws).clone())
+        torch.cuda.synchronize()
+        for rep in range(12):
+            x = xs_in[rep % 4]
+            xq, xs = quantise(x)
+            got = ops.fp8_gemm_rowwise(xq, wq, xs, ws, overlap=True)
+            assert torch.equal(got, want[rep % 4]), (producer, m, rep)
+            del xq, xs  # the next iteration's quantiser gets the same memory back from the caching allocator
+    ops.check_device_status()
+
+
 @pytest.mark.parametrize("variant,shape", [("tc_1cta", (300, 520, 400)), ("tc_2cta", (513, 1001, 256)), ("tc_2cta", (512, 1024, 1024)),
                                            ("skinny", (17, 520, 400)), ("skinny", (16, 4096, 2048)), ("simt", (50, 70, 90))])
 def test_fp16_output(cuda_device, variant, shape):
