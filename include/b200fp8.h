@@ -58,9 +58,9 @@ typedef enum b200fp8_status {
 /* TC_SPLITK, SKINNY and GEMV kernels only (TC_SPLITK and SKINNY are what `auto` picks for M <= 128): launch with programmatic stream
  * serialization, so the kernel may start while the kernel before it in the stream still runs.  It reads W
  * (only W) before that kernel has completed, everything else after.  The caller promises that no work still
- * in flight writes W.  The quantiser kernels of this library let such a dependent start as soon as they are running
- * (griddepcontrol.launch_dependents), so a decode GEMM behind a quantiser of X overlaps it; a GEMM behind a quantiser
- * of W must therefore NOT carry this flag. */
+ * in flight writes W.  The producer + quantiser kernels (b200fp8_fused_row_quantize: activations only) let such a
+ * dependent start as soon as they are running (griddepcontrol.launch_dependents), so a decode GEMM behind them
+ * overlaps the quantiser; the plain row and block quantisers, which also serve weights, do not. */
 #define B200FP8_FLAG_PDL 0x20u
 /* Y holds IEEE fp16 instead of bf16 (the output type of TritonBench's `fp8_gemm` operator with per-tensor
  * scales, tritonbench/operators/fp8_gemm/fp8_gemm.py:88-101); same 16-bit storage, same leading dimension. */

@@ -602,8 +602,9 @@ def test_overlapped_launch_of_decode_kernels_back_to_back(cuda_device, variant):
 
 @pytest.mark.parametrize("producer", ["row_quantize", "rms_norm", "silu_mul"])
 def test_decode_gemm_launched_behind_a_quantiser_of_x_starts_early_and_still_sees_its_output(cuda_device, producer):
-    """The quantiser kernels let a dependent launch start while they run.  A decode GEMM with the overlap flag directly
-    behind a quantiser of X prefetches W early but must read xq and x_scale only after the quantiser has completed:
+    """The producer + quantiser kernels let a dependent launch start while they run (the plain row quantiser does not:
+    it also serves weights).  A decode GEMM with the overlap flag directly behind a quantiser of X may prefetch W early
+    but must read xq and x_scale only after the quantiser has completed:
     every iteration quantises a different activation into the same buffers, so a GEMM that read early would return the
     previous iteration's result."""
     ops = _ops()

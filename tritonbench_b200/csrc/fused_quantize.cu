@@ -28,10 +28,12 @@
 namespace b200fp8 {
 namespace {
 
-// A GEMM launched behind one of these kernels with programmatic stream serialization (B200FP8_FLAG_PDL) may start
-// as soon as every CTA here has passed this point: it prefetches W while the quantiser runs and reads what the
-// quantiser wrote only after its own griddepcontrol.wait, i.e. after this grid has completed.  Without such a
-// dependent the instruction does nothing.
+// These kernels produce activations, never weights.  A decode GEMM launched behind one of them with programmatic
+// stream serialization (B200FP8_FLAG_PDL: it may read W, and only W, before its predecessor has completed) may
+// therefore start as soon as every CTA here has passed this point: it prefetches W while the quantiser runs and reads
+// what the quantiser wrote only after its own griddepcontrol.wait, i.e. after this grid has completed.  Without such
+// a dependent the instruction does nothing.  (The plain row and block quantisers, which also quantise weights, do
+// not do this.)
 __device__ __forceinline__ void let_dependents_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 

@@ -24,12 +24,6 @@
 namespace b200fp8 {
 namespace {
 
-// A GEMM launched behind one of these kernels with programmatic stream serialization (B200FP8_FLAG_PDL) may start
-// as soon as every CTA here has passed this point: it prefetches W while the quantiser runs and reads what the
-// quantiser wrote only after its own griddepcontrol.wait, i.e. after this grid has completed.  Without such a
-// dependent the instruction does nothing.
-__device__ __forceinline__ void let_dependents_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
 
 constexpr int kThreads = 256;
 constexpr int kVec = 8;       // elements per vector load (16 bytes of a 16-bit type; two loads for fp32)
@@ -158,7 +152,6 @@ struct Ops<float, kRecipe> {
 
 template <typename T, int kRecipe>
 __global__ void __launch_bounds__(kThreads) row_quantize_kernel(const QuantParams p) {
-  let_dependents_start();
   __shared__ float red[kThreads / 32];
   const long long row = blockIdx.x;
   const T* x = static_cast<const T*>(p.x) + row * p.ldx;
@@ -227,7 +220,6 @@ __host__ __device__ constexpr int pow2_at_least(int n) { return n <= 1 ? 1 : 2 *
 
 template <typename T, int kRecipe, int kWarpsT>
 __global__ void __launch_bounds__(32 * kWarpsT) row_quantize_persistent_kernel(const QuantParams p) {
-  let_dependents_start();
   constexpr int kKeep = kPersistVecs, threads = 32 * kWarpsT;
   __shared__ float red[2][kPersistMaxWarps];
   using O = Ops<T, kRecipe>;
@@ -294,7 +286,6 @@ __global__ void __launch_bounds__(32 * kWarpsT) row_quantize_persistent_kernel(c
 constexpr int kShortRowVecs = 10;  // vectors of 8 elements per lane: 32 * 8 * 10 = 2560 elements
 template <typename T, int kRecipe>
 __global__ void __launch_bounds__(kThreads) row_quantize_short_rows_kernel(const QuantParams p) {
-  let_dependents_start();
   using O = Ops<T, kRecipe>;
   const int lane = threadIdx.x & 31;
   const long long row = static_cast<long long>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
@@ -393,7 +384,6 @@ cudaError_t launch_recipe(const QuantParams& p, cudaStream_t stream) {
 // blocks use vector accesses, edge blocks element accesses.
 template <typename T>
 __global__ void __launch_bounds__(kThreads) block_quantize_kernel(const BlockQuantParams p) {
-  let_dependents_start();
   __shared__ float red[kThreads / 32];
   const int bk = blockIdx.x, bm = blockIdx.y;
   const int r0 = threadIdx.x >> 4;
