@@ -107,10 +107,12 @@ struct Finish {
 
 // Sum (or read), scale and round `kCols` columns starting at `c_in_slice`, then store them: into the
 // staging box (flushed by the caller every 64 columns), or straight to Y.
-template <int kCols>
+// kSplitK / kBoxed / kPlain (no bias, bf16 output) are compile-time: a launch runs this code once, cold, so every
+// instruction of a path it does not take still costs instruction-cache lines on the way.
+template <int kCols, bool kSplitK, bool kBoxed, bool kPlain>
 __device__ __forceinline__ void finish_columns(const Finish& f, int c_in_slice, uint32_t sbuf) {
   float v[kCols];
-  if (f.split == 1) {
+  if constexpr (!kSplitK) {
     uint32_t raw[kCols];
     tmem_ld_cols<kCols>(f.t_addr + c_in_slice, raw);
     tmem_ld_wait();
@@ -140,18 +142,24 @@ __device__ __forceinline__ void finish_columns(const Finish& f, int c_in_slice, 
     v[4 * j + 2] *= f.xs * ws.z;
     v[4 * j + 3] *= f.xs * ws.w;
   }
-  if (f.bias != nullptr) {
+  if constexpr (!kPlain) {
+    if (f.bias != nullptr) {
 #pragma unroll
-    for (int j = 0; j < kCols; ++j) {
-      if (c_in_slice + j < f.cols_valid) v[j] += __bfloat162float(f.bias[c_in_slice + j]);
+      for (int j = 0; j < kCols; ++j) {
+        if (c_in_slice + j < f.cols_valid) v[j] += __bfloat162float(f.bias[c_in_slice + j]);
+      }
     }
   }
   uint32_t packed[kCols / 2];
 #pragma unroll
   for (int j = 0; j < kCols / 2; ++j) {
-    packed[j] = f.out_fp16 ? pack_f16x2(v[2 * j], v[2 * j + 1]) : pack_bf16x2(v[2 * j], v[2 * j + 1]);
+    if constexpr (kPlain) {
+      packed[j] = pack_bf16x2(v[2 * j], v[2 * j + 1]);
+    } else {
+      packed[j] = f.out_fp16 ? pack_f16x2(v[2 * j], v[2 * j + 1]) : pack_bf16x2(v[2 * j], v[2 * j + 1]);
+    }
   }
-  if (f.boxed) {
+  if constexpr (kBoxed) {
     const uint32_t row_addr = sbuf + f.lane * 128;
     const int chunk0 = (c_in_slice % Geo::kStoreCols) / 8;  // 16-byte chunk inside the 128-byte box row
 #pragma unroll
@@ -181,11 +189,12 @@ __device__ __forceinline__ void finish_columns(const Finish& f, int c_in_slice, 
 // need more than its 512 tensor-memory columns (a tcgen05.alloc that had to wait for a peer stuck at a cluster
 // barrier would never return).  With the 168 registers per thread ptxas reports, 192 threads x 168 registers
 // already hold an SM to two CTAs; the shared-memory floor keeps the rule true whatever the compiler does.
+template <bool kSplitK, bool kBoxed, bool kPlain>
 __global__ void __launch_bounds__(Geo::kThreads, 2)
 gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    const __grid_constant__ CUtensorMap tm_y, const TcParams p, const SplitPlan plan) {
   constexpr int kMaxStages = SplitGeometry::kMaxStages;
-  const int split = plan.split;
+  const int split = kSplitK ? plan.split : 1;
   const int stages = plan.stages;
   const int block_n = plan.block_n;
   const bool overlap = plan.overlap_previous_kernel;
@@ -353,7 +362,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   const bool warp_has_rows = row0 < p.M;  // warp-uniform: the whole 32-row group lies beyond M otherwise
   const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
 
-  if (split > 1) {
+  if constexpr (kSplitK) {
     // ---- (A) every CTA of the cluster has finished reading its operand ring ----
     cluster_sync_all();
 
@@ -409,10 +418,9 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     f.row_valid = row < p.M;
     f.bias = p.bias != nullptr ? p.bias + col_first : nullptr;
     f.out_fp16 = p.out_fp16 != 0;
-    f.boxed = p.use_tma_store != 0 && plan.staged_stores && slice_cols % Geo::kStoreCols == 0;
+    f.boxed = kBoxed;  // the host picks the instantiation: TMA stores allowed, staged stores planned, slices of whole boxes
     f.vector_ok = p.use_tma_store != 0;  // same condition: 16-byte aligned rows of Y
     const uint32_t stage_buf = smem_epi + quarter * (2 * Geo::kStoreRows * Geo::kStoreCols * 2);
-    const bool use_tma = f.boxed;
 
     {
       uint32_t store_count = 0;
@@ -420,12 +428,12 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll 1
       for (; c + 64 <= slice_cols; c += 64) {  // 64 columns = one box of the TMA store, when Y leaves in boxes
         const uint32_t sbuf = stage_buf + (store_count & 1u) * (Geo::kStoreRows * Geo::kStoreCols * 2);
-        if (f.boxed) {
+        if constexpr (kBoxed) {
           if (lane == 0) tma_store_wait_read<1>();  // the box used two stores ago has been read
           __syncwarp();
         }
-        finish_columns<64>(f, c, sbuf);
-        if (f.boxed) {
+        finish_columns<64, kSplitK, kBoxed, kPlain>(f, c, sbuf);
+        if constexpr (kBoxed) {
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0 && col_first + c < p.N) tma_store_2d(&tm_y, sbuf, col_first + c, row0);
@@ -435,12 +443,12 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       }
       // what is left of a slice that is not a multiple of 64 columns (never boxed)
       if (c + 32 <= slice_cols) {
-        finish_columns<32>(f, c, 0u);
+        finish_columns<32, kSplitK, false, kPlain>(f, c, 0u);
         c += 32;
       }
-      if (c < slice_cols) finish_columns<16>(f, c, 0u);  // never boxed: a boxed slice is a multiple of 64 columns
+      if (c < slice_cols) finish_columns<16, kSplitK, false, kPlain>(f, c, 0u);  // never boxed: a boxed slice is a multiple of 64 columns
       // the CTA may end once the boxes have been read out of shared memory; the writes complete with the kernel
-      if (use_tma && lane == 0) tma_store_wait_read<0>();
+      if (kBoxed && lane == 0) tma_store_wait_read<0>();
     }
   }
 
@@ -451,15 +459,30 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   if (warp == 1) tmem_dealloc<1>(tmem_base, tmem_cols);
 }
 
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const TcParams, const SplitPlan);
+
+// [split-K][boxed stores][plain: no bias, bf16]
+KernelFn kernel_for(bool split_k, bool boxed, bool plain) {
+  static const KernelFn table[2][2][2] = {
+      {{gemm_splitk_kernel<false, false, false>, gemm_splitk_kernel<false, false, true>},
+       {gemm_splitk_kernel<false, true, false>, gemm_splitk_kernel<false, true, true>}},
+      {{gemm_splitk_kernel<true, false, false>, gemm_splitk_kernel<true, false, true>},
+       {gemm_splitk_kernel<true, true, false>, gemm_splitk_kernel<true, true, true>}}};
+  return table[split_k ? 1 : 0][boxed ? 1 : 0][plain ? 1 : 0];
+}
+
 cudaError_t configure(int dev) {
   static bool configured[64] = {};
   static std::mutex mutex;
   std::lock_guard<std::mutex> lock(mutex);
   if (dev >= 0 && dev < 64 && configured[dev]) return cudaSuccess;
-  const cudaError_t err =
-      cudaFuncSetAttribute(gemm_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-  if (err == cudaSuccess && dev >= 0 && dev < 64) configured[dev] = true;
-  return err;
+  for (int i = 0; i < 8; ++i) {
+    const cudaError_t err = cudaFuncSetAttribute(kernel_for((i & 4) != 0, (i & 2) != 0, (i & 1) != 0),
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (err != cudaSuccess) return err;
+  }
+  if (dev >= 0 && dev < 64) configured[dev] = true;
+  return cudaSuccess;
 }
 
 }  // namespace
@@ -482,7 +505,7 @@ int splitk_resident_clusters(int split, cudaError_t* err) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int clusters = 0;
-  *err = cudaOccupancyMaxActiveClusters(&clusters, gemm_splitk_kernel, &cfg);
+  *err = cudaOccupancyMaxActiveClusters(&clusters, kernel_for(split > 1, true, false), &cfg);
   return *err == cudaSuccess ? clusters : 0;
 }
 
@@ -520,7 +543,10 @@ cudaError_t launch_gemm_splitk(const CUtensorMap& tm_x, const CUtensorMap& tm_w,
   }
   cfg.attrs = attr;
   cfg.numAttrs = num_attrs;
-  return cudaLaunchKernelEx(&cfg, gemm_splitk_kernel, tm_x, tm_w, tm_y, p, plan);
+  const int slice_cols = plan.block_n / plan.split;
+  const bool boxed = p.use_tma_store != 0 && plan.staged_stores != 0 && slice_cols % Geo::kStoreCols == 0;
+  const bool plain = p.bias == nullptr && p.out_fp16 == 0;
+  return cudaLaunchKernelEx(&cfg, kernel_for(plan.split > 1, boxed, plain), tm_x, tm_w, tm_y, p, plan);
 }
 
 }  // namespace b200fp8
