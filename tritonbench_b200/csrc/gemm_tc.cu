@@ -324,39 +324,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         for (int box = 0; box < Cfg::kBlockN / Cfg::kStoreCols; ++box) {
           const int box_col = col0 + box * Cfg::kStoreCols;
           const uint32_t sbuf = stage_buf + (store_count & 1u) * (Cfg::kStoreRows * Cfg::kStoreCols * 2);
+          // both 32-column reads of the box and its 64 column scales are requested before anything is waited for
+          uint32_t acc[Cfg::kStoreCols];
+          tmem_ld_32x32(t_addr + box * Cfg::kStoreCols, *reinterpret_cast<uint32_t(*)[32]>(&acc[0]));
+          tmem_ld_32x32(t_addr + box * Cfg::kStoreCols + 32, *reinterpret_cast<uint32_t(*)[32]>(&acc[32]));
+          const float4* ws4 = reinterpret_cast<const float4*>(w_scale + box_col);
+          float4 ws[Cfg::kStoreCols / 4];
+#pragma unroll
+          for (int j = 0; j < Cfg::kStoreCols / 4; ++j) ws[j] = __ldg(ws4 + j);
           if (lane == 0) tma_store_wait_read<1>();  // the buffer about to be rewritten: source of the store before last
           __syncwarp();
           const uint32_t row_addr = sbuf + lane * 128;
-#pragma unroll 1
-          for (int half = 0; half < 2; ++half) {
-            uint32_t acc[32];
-            tmem_ld_32x32(t_addr + box * Cfg::kStoreCols + half * 32, acc);
-            const float4* ws4 = reinterpret_cast<const float4*>(w_scale + box_col + half * 32);
-            float4 ws[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) ws[j] = __ldg(ws4 + j);
-            tmem_ld_wait();
-            if (box == Cfg::kBlockN / Cfg::kStoreCols - 1 && half == 1) {
-              tc_fence_before_sync();  // accumulator fully read: hand the TMEM buffer back to the MMA issuer
-              __syncwarp();
-              if (lane == 0) {
-                if constexpr (kPair) {
-                  mbar_arrive_cluster(tmem_empty_remote + 8 * buf);
-                } else {
-                  mbar_arrive(bar_tmem_empty + 8 * buf);
-                }
+          tmem_ld_wait();
+          if (box == Cfg::kBlockN / Cfg::kStoreCols - 1) {
+            tc_fence_before_sync();  // accumulator fully read: hand the TMEM buffer back to the MMA issuer
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (kPair) {
+                mbar_arrive_cluster(tmem_empty_remote + 8 * buf);
+              } else {
+                mbar_arrive(bar_tmem_empty + 8 * buf);
               }
             }
+          }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float4 wa = ws[2 * j], wb = ws[2 * j + 1];
-              const uint32_t chunk = static_cast<uint32_t>((half * 4 + j) ^ (lane & 7));
-              st_shared_v4(row_addr + chunk * 16,
-                           pack_bf16x2(__uint_as_float(acc[8 * j + 0]) * (xs * wa.x), __uint_as_float(acc[8 * j + 1]) * (xs * wa.y)),
-                           pack_bf16x2(__uint_as_float(acc[8 * j + 2]) * (xs * wa.z), __uint_as_float(acc[8 * j + 3]) * (xs * wa.w)),
-                           pack_bf16x2(__uint_as_float(acc[8 * j + 4]) * (xs * wb.x), __uint_as_float(acc[8 * j + 5]) * (xs * wb.y)),
-                           pack_bf16x2(__uint_as_float(acc[8 * j + 6]) * (xs * wb.z), __uint_as_float(acc[8 * j + 7]) * (xs * wb.w)));
-            }
+          for (int j = 0; j < Cfg::kStoreCols / 8; ++j) {
+            const float4 wa = ws[2 * j], wb = ws[2 * j + 1];
+            const uint32_t chunk = static_cast<uint32_t>(j ^ (lane & 7));
+            st_shared_v4(row_addr + chunk * 16,
+                         pack_bf16x2(__uint_as_float(acc[8 * j + 0]) * (xs * wa.x), __uint_as_float(acc[8 * j + 1]) * (xs * wa.y)),
+                         pack_bf16x2(__uint_as_float(acc[8 * j + 2]) * (xs * wa.z), __uint_as_float(acc[8 * j + 3]) * (xs * wa.w)),
+                         pack_bf16x2(__uint_as_float(acc[8 * j + 4]) * (xs * wb.x), __uint_as_float(acc[8 * j + 5]) * (xs * wb.y)),
+                         pack_bf16x2(__uint_as_float(acc[8 * j + 6]) * (xs * wb.z), __uint_as_float(acc[8 * j + 7]) * (xs * wb.w)));
           }
           fence_proxy_async_smem();
           __syncwarp();
